@@ -1,0 +1,147 @@
+/*
+ * neuzip_b200 - C ABI of the B200 (sm_100a) NeuZip codec library.
+ *
+ * Every entry point takes raw device pointers and sizes, enqueues its work on
+ * the CUDA stream passed by the caller (a cudaStream_t cast to void*; NULL is
+ * the legacy default stream) and returns an int status: 0 on success, a
+ * negative NZ_E_* code otherwise, with a text in nz_last_error().  The library
+ * owns no tensor memory and never terminates the process.  Unless stated
+ * otherwise a call does not synchronise with the host.
+ *
+ * "Reference" citations name files of BorealisAI/neuzip, whose native side is
+ * the pybind11 module neuzip._cuda (cuda/neuzip.cu:19-106); the functions here
+ * are what a binding for that module's Manager_f{precision}_n0 classes calls.
+ *
+ * Vocabulary.  precision s in {0,1,3,7} = mantissa bits kept.  A bf16 tensor
+ * of N elements is stored as
+ *   - a packed "fraction" stream of ceil(N*(s+1)/8) bytes (sign + s mantissa
+ *     bits per element, MSB first), and
+ *   - an NZR1 container holding the rANS-coded stream of N exponent bytes.
+ * The container format is specified in oracle/nz_oracle.c.
+ */
+#ifndef NEUZIP_B200_H_
+#define NEUZIP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NZ_OK 0
+#define NZ_E_ARG (-1)      /* invalid argument (precision, size, alignment, null) */
+#define NZ_E_CUDA (-2)     /* a CUDA runtime call failed */
+#define NZ_E_CAPACITY (-3) /* an output or scratch buffer is too small */
+#define NZ_E_FORMAT (-4)   /* malformed container */
+#define NZ_E_DEVICE (-5)   /* the current device is not sm_100 */
+
+/* Bits set by the decode kernels in the caller's 32-bit device status word. */
+#define NZ_STATUS_BAD_HEADER 0x1u  /* magic / version / sizes do not match    */
+#define NZ_STATUS_BAD_OFFSETS 0x2u /* unit offsets out of range / not monotone */
+#define NZ_STATUS_BAD_LANES 0x4u   /* lane lengths inconsistent with the unit  */
+#define NZ_STATUS_BAD_STATE 0x8u   /* a lane did not end in the initial state  */
+#define NZ_STATUS_TIMEOUT 0x10u    /* a bounded wait on a bulk copy ran out    */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int nz_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *nz_last_error(void);
+
+/* 0 when the current CUDA device can run the kernels (compute capability
+ * 10.x), NZ_E_DEVICE otherwise.  The kernels are built for sm_100a only. */
+int nz_device_check(void);
+
+/* ---- sizes ------------------------------------------------------------- */
+
+/* Bytes of the packed fraction stream: ceil(N*(s+1)/8).
+ * Reference: cuda/high_level.cu:81-83. */
+uint64_t nz_frac_bytes(uint64_t n, int precision);
+
+/* Symbols per lane stream the library picks for a precision. */
+uint32_t nz_default_lane_symbols(int precision);
+
+/* Upper bound of the container size for n exponent bytes.
+ * Reference: nvcomp CompressionConfig::max_compressed_buffer_size,
+ * cuda/high_level.cu:103-108. */
+uint64_t nz_container_bound(uint64_t n, uint32_t lane_symbols);
+
+/* Bytes of device scratch nz_encode_exponents needs. */
+uint64_t nz_encode_scratch_bytes(uint64_t n, uint32_t lane_symbols);
+
+/* Bytes of device scratch nz_compress_bf16 needs (the encode scratch plus the
+ * intermediate exponent stream). */
+uint64_t nz_compress_scratch_bytes(uint64_t n, uint32_t lane_symbols);
+
+/* ---- split / merge ------------------------------------------------------ */
+
+/* bf16[N] -> exponent bytes u8[N] + packed fractions, with the reference's
+ * round-half-up of the magnitude at the cut and carry into the exponent.
+ * Reference: kernel_aligned_split, cuda/kernels.cuh:53-156 (normalized=false),
+ * launched at cuda/high_level.cu:95-101 and :289-296. */
+int nz_split_bf16(const void *in_bf16, uint64_t n, int precision, void *exp_out,
+                  void *frac_out, void *stream);
+
+/* Inverse of nz_split_bf16 on an uncompressed exponent stream; dropped
+ * mantissa bits are zero.  canonical_nan != 0 writes 0x7FFF for every NaN
+ * pattern, as the float->bf16 store of the reference does.
+ * Reference: kernel_aligned_merge, cuda/kernels.cuh:158-217. */
+int nz_merge_bf16(const void *exp_in, const void *frac_in, uint64_t n,
+                  int precision, int canonical_nan, void *out_bf16,
+                  void *stream);
+
+/* ---- entropy stage ------------------------------------------------------ */
+
+/* 256-bin histogram of n bytes into hist_u32[256] (device; cleared first). */
+int nz_histogram_u8(const void *sym, uint64_t n, void *hist_u32, void *stream);
+
+/* rANS-encode n exponent bytes into an NZR1 container (device buffer of at
+ * least nz_container_bound bytes, 16-byte aligned).  `scratch` is device
+ * memory of nz_encode_scratch_bytes bytes, 16-byte aligned.  The container
+ * length is written into its header; read it with nz_container_bytes.
+ * Reference: nvcomp ANSManager::configure_compression + compress,
+ * cuda/high_level.cu:103-112. */
+int nz_encode_exponents(const void *exp_in, uint64_t n, uint32_t lane_symbols,
+                        void *container, uint64_t container_cap, void *scratch,
+                        uint64_t scratch_bytes, void *stream);
+
+/* Copies the container header to the host and returns the container length
+ * in *total_bytes and the largest coded unit (16-bit words) in
+ * *max_unit_words.  Synchronises the stream (the one host sync of a write).
+ * Reference: nvcomp get_compressed_output_size, cuda/high_level.cu:114-115. */
+int nz_container_bytes(const void *container, uint64_t *total_bytes,
+                       uint32_t *max_unit_words, void *stream);
+
+/* Decode the container into n exponent bytes.  `status` is a device u32 the
+ * kernel ORs NZ_STATUS_* bits into (may be NULL).  max_unit_words is the
+ * value nz_container_bytes returned (0 = assume the worst case).
+ * Reference: nvcomp ANSManager::decompress, cuda/high_level.cu:184-192. */
+int nz_decode_exponents(const void *container, uint64_t container_bytes,
+                        uint64_t n, uint32_t lane_symbols,
+                        uint32_t max_unit_words, void *exp_out, void *status,
+                        void *stream);
+
+/* ---- whole-tensor paths -------------------------------------------------- */
+
+/* split + histogram + table + encode in one call: bf16[N] -> fractions +
+ * container.  Buffers as for nz_split_bf16 / nz_encode_exponents, scratch of
+ * nz_compress_scratch_bytes bytes.
+ * Reference: Manager::_write_to_cache, cuda/high_level.cu:71-130. */
+int nz_compress_bf16(const void *in_bf16, uint64_t n, int precision,
+                     uint32_t lane_symbols, void *frac_out, void *container,
+                     uint64_t container_cap, void *scratch,
+                     uint64_t scratch_bytes, void *stream);
+
+/* Decode the container and merge with the fractions straight into bf16[N];
+ * the exponent bytes never travel through global memory.  No host sync.
+ * Reference: Manager::_decompress_and_merge, cuda/high_level.cu:164-206. */
+int nz_decompress_bf16(const void *container, uint64_t container_bytes,
+                       const void *frac_in, uint64_t n, int precision,
+                       uint32_t lane_symbols, uint32_t max_unit_words,
+                       int canonical_nan, void *out_bf16, void *status,
+                       void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEUZIP_B200_H_ */

@@ -1,0 +1,101 @@
+"""ctypes loader of ``libneuzip_b200.so`` (the C-ABI library declared in
+``include/neuzip_b200.h``).
+
+There is no CPU fallback: if the shared library is missing or the current
+device is not a B200-class GPU, the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import threading
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_SO_PATH = os.path.join(_PKG_DIR, "libneuzip_b200.so")
+_CSRC = os.path.join(_PKG_DIR, "csrc")
+
+NZ_OK = 0
+NZ_E_ARG, NZ_E_CUDA, NZ_E_CAPACITY, NZ_E_FORMAT, NZ_E_DEVICE = -1, -2, -3, -4, -5
+STATUS_BITS = {
+    0x1: "bad header",
+    0x2: "bad unit offsets",
+    0x4: "bad lane lengths",
+    0x8: "bad final state",
+    0x10: "bulk-copy wait timed out",
+}
+
+# name -> (restype, argtypes); mirrors include/neuzip_b200.h one to one
+_vp, _u64, _u32, _int = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int
+SIGNATURES = {
+    "nz_version": (_int, []),
+    "nz_last_error": (ctypes.c_char_p, []),
+    "nz_device_check": (_int, []),
+    "nz_frac_bytes": (_u64, [_u64, _int]),
+    "nz_default_lane_symbols": (_u32, [_int]),
+    "nz_container_bound": (_u64, [_u64, _u32]),
+    "nz_encode_scratch_bytes": (_u64, [_u64, _u32]),
+    "nz_compress_scratch_bytes": (_u64, [_u64, _u32]),
+    "nz_split_bf16": (_int, [_vp, _u64, _int, _vp, _vp, _vp]),
+    "nz_merge_bf16": (_int, [_vp, _vp, _u64, _int, _int, _vp, _vp]),
+    "nz_histogram_u8": (_int, [_vp, _u64, _vp, _vp]),
+    "nz_encode_exponents": (_int, [_vp, _u64, _u32, _vp, _u64, _vp, _u64, _vp]),
+    "nz_container_bytes": (_int, [_vp, ctypes.POINTER(_u64), ctypes.POINTER(_u32), _vp]),
+    "nz_decode_exponents": (_int, [_vp, _u64, _u64, _u32, _u32, _vp, _vp, _vp]),
+    "nz_compress_bf16": (_int, [_vp, _u64, _int, _u32, _vp, _vp, _u64, _vp, _u64, _vp]),
+    "nz_decompress_bf16": (_int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _vp, _vp, _vp]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def build(verbose: bool = False) -> str:
+    """Compile the CUDA sources for sm_100a with the Makefile in ``csrc``."""
+    proc = subprocess.run(["make", "-C", _CSRC, "-j4"], stdout=subprocess.PIPE,
+                          stderr=subprocess.STDOUT, text=True)
+    if verbose or proc.returncode != 0:
+        print(proc.stdout)
+    if proc.returncode != 0:
+        raise RuntimeError("building libneuzip_b200.so failed")
+    return _SO_PATH
+
+
+def library_path() -> str:
+    return _SO_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Load the library (once) and attach the prototypes."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(_SO_PATH):
+                raise ImportError(
+                    f"{_SO_PATH} is not built; run `python -c 'import __graft_entry__ as g; "
+                    "g.build()'` or `make -C neuzip_b200/csrc`. There is no CPU fallback.")
+            lib = ctypes.CDLL(_SO_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype = res
+                fn.argtypes = args
+            _lib = lib
+    return _lib
+
+
+class NeuzipError(RuntimeError):
+    pass
+
+
+def check(rc: int) -> None:
+    """Turn a status code of the library into a Python exception."""
+    if rc == NZ_OK:
+        return
+    msg = load().nz_last_error().decode("utf-8", "replace")
+    if rc == NZ_E_ARG:
+        raise ValueError(msg)
+    raise NeuzipError(f"neuzip_b200 error {rc}: {msg}")
+
+
+def describe_status(word: int) -> str:
+    return ", ".join(txt for bit, txt in STATUS_BITS.items() if word & bit) or "ok"

@@ -1,0 +1,214 @@
+"""Python stand-in for the reference's native module ``neuzip._cuda``
+(cuda/neuzip.cu:19-106): an ``Algorithm`` enum and the backend classes
+``Manager_f{precision}_n{normalizer}`` with ``read / write / size / linear /
+linear_without_bias / split`` (cuda/neuzip.cu:28-37).
+
+Where the reference keeps its compressed tensors in a C++ map inside the
+extension (cuda/high_level.cu:35-43), this backend keeps torch tensors in a
+Python dict and calls the stateless C-ABI kernels of ``libneuzip_b200.so`` on
+the caller's current CUDA stream.  Only the rANS ("ans") algorithm, bf16
+tensors and ``normalizer_size == 0`` are implemented; the other combinations
+raise ``NotImplementedError`` when constructed.
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from . import _lib
+
+PRECISIONS = (0, 1, 3, 7)
+NORMALIZER_SIZES = (0, 1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024)
+
+
+class Algorithm(enum.Enum):
+    """Same members, same order as the extension enum (cuda/algorithms.cuh:8)."""
+    ans = 0
+    bitcomp = 1
+    lz4 = 2
+    zstd = 3
+    gdeflate = 4
+
+
+@dataclass
+class _Entry:
+    numel: int
+    dtype: torch.dtype
+    lane_symbols: int
+    max_unit_words: int
+    container: torch.Tensor   # uint8, right-sized NZR1 container
+    fractions: torch.Tensor   # uint8, packed sign+mantissa stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _as_flat_bf16_cuda(tensor: torch.Tensor) -> torch.Tensor:
+    if tensor.dtype != torch.bfloat16:
+        # the reference dispatches fp32/fp16 as well (cuda/high_level.cu:144-158) but
+        # truncates their mantissa to 8 bits (cuda/kernels.cuh:123); only bf16 is sound
+        raise RuntimeError("Unsupported data type")
+    if not tensor.is_cuda:
+        tensor = tensor.cuda()
+    flat = tensor.detach().contiguous().view(-1)
+    if flat.data_ptr() % 16:
+        flat = flat.clone()
+    return flat
+
+
+class CodecBackend:
+    """One (precision, normalizer) instantiation of the reference's C++
+    ``Manager`` template (cuda/high_level.cu:26-322)."""
+
+    precision: int = 7
+    normalizer_size: int = 0
+
+    def __init__(self, algorithm: Algorithm = Algorithm.ans, chunk_size: int = 1 << 16) -> None:
+        if not isinstance(algorithm, Algorithm):
+            algorithm = Algorithm(algorithm)
+        if algorithm is not Algorithm.ans:
+            raise NotImplementedError(
+                f"algorithm {algorithm.name!r}: only the rANS coder ('ans') is implemented")
+        if self.normalizer_size != 0:
+            raise NotImplementedError("the block normaliser (normalizer_size > 0) is not implemented")
+        self._lib = _lib.load()
+        self.chunk_size = int(chunk_size)   # kept for API parity; the unit size follows precision
+        self.lane_symbols = int(self._lib.nz_default_lane_symbols(self.precision))
+        self._cache: Dict[str, _Entry] = {}
+        self._scratch: Optional[torch.Tensor] = None
+        self._status: Optional[torch.Tensor] = None
+        self.canonical_nan = True           # NaN -> 0x7FFF like cuda/kernels.cuh:214-216
+
+    # -- helpers ---------------------------------------------------------
+    def _ensure_device(self) -> None:
+        if self._status is None:
+            _lib.check(self._lib.nz_device_check())
+            self._status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def _scratch_for(self, nbytes: int) -> torch.Tensor:
+        if self._scratch is None or self._scratch.numel() < nbytes:
+            self._scratch = None
+            self._scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        return self._scratch
+
+    def release_scratch(self) -> None:
+        self._scratch = None
+
+    def status(self) -> int:
+        """Decode status word accumulated so far (synchronises)."""
+        return 0 if self._status is None else int(self._status.item()) & 0xFFFFFFFF
+
+    def check(self) -> None:
+        word = self.status()
+        if word:
+            raise _lib.NeuzipError("decode reported: " + _lib.describe_status(word))
+
+    # -- the six methods of the extension class ----------------------------
+    def write(self, name: str, tensor: torch.Tensor) -> None:
+        """cuda/high_level.cu:132-162 (+ _write_to_cache :71-130)."""
+        self._ensure_device()
+        flat = _as_flat_bf16_cuda(tensor)
+        n = flat.numel()
+        L, S = self._lib, self.lane_symbols
+        self._cache.pop(name, None)
+        frac = torch.empty(int(L.nz_frac_bytes(n, self.precision)), dtype=torch.uint8, device="cuda")
+        cap = int(L.nz_container_bound(n, S))
+        staging = torch.empty(cap, dtype=torch.uint8, device="cuda")
+        scratch_bytes = int(L.nz_compress_scratch_bytes(n, S))
+        scratch = self._scratch_for(scratch_bytes)
+        st = _stream()
+        _lib.check(L.nz_compress_bf16(_ptr(flat), n, self.precision, S, _ptr(frac), _ptr(staging),
+                                      cap, _ptr(scratch), scratch.numel(), st))
+        total = _lib._u64(0)
+        max_words = _lib._u32(0)
+        _lib.check(L.nz_container_bytes(_ptr(staging), total, max_words, st))
+        container = staging[: total.value].clone()
+        self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac)
+
+    def read(self, name: str) -> torch.Tensor:
+        """cuda/high_level.cu:223-250 (+ _decompress_and_merge :164-206); no host sync."""
+        entry = self._cache.get(name)
+        if entry is None:
+            raise RuntimeError("Data not found")
+        out = torch.empty(entry.numel, dtype=torch.bfloat16, device="cuda")
+        self.read_into(name, out)
+        return out
+
+    def read_into(self, name: str, out: torch.Tensor) -> None:
+        entry = self._cache[name]
+        _lib.check(self._lib.nz_decompress_bf16(
+            _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
+            self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
+            _ptr(out), _ptr(self._status), _stream()))
+
+    def size(self, name: str) -> int:
+        """cuda/high_level.cu:208-221: stored bytes, 0 for an unknown name."""
+        entry = self._cache.get(name)
+        if entry is None:
+            return 0
+        return entry.container.numel() + entry.fractions.numel()
+
+    def linear(self, name: str, input: torch.Tensor, shape: Sequence[int],
+               bias: torch.Tensor) -> torch.Tensor:
+        """cuda/high_level.cu:252-257."""
+        weight = self.read(name).view(*shape)
+        return torch.nn.functional.linear(input, weight, bias)
+
+    def linear_without_bias(self, name: str, input: torch.Tensor,
+                            shape: Sequence[int]) -> torch.Tensor:
+        """cuda/high_level.cu:259-263."""
+        weight = self.read(name).view(*shape)
+        return torch.matmul(input, weight.t())
+
+    def split(self, tensor: torch.Tensor) -> List[torch.Tensor]:
+        """cuda/high_level.cu:301-321: always full mantissa (f_bits_save = 7, :289);
+        returns [exponents, fractions], one byte per element each."""
+        self._ensure_device()
+        flat = _as_flat_bf16_cuda(tensor)
+        n = flat.numel()
+        exp = torch.empty(n, dtype=torch.uint8, device="cuda")
+        frac = torch.empty(n, dtype=torch.uint8, device="cuda")
+        _lib.check(self._lib.nz_split_bf16(_ptr(flat), n, 7, _ptr(exp), _ptr(frac), _stream()))
+        return [exp, frac]
+
+    # -- extras -----------------------------------------------------------
+    def erase(self, name: str) -> None:
+        self._cache.pop(name, None)
+
+    def entry(self, name: str) -> _Entry:
+        return self._cache[name]
+
+    def names(self):
+        return list(self._cache)
+
+
+def _make_backend(precision: int, normalizer_size: int):
+    cls_name = f"Manager_f{precision}_n{normalizer_size}"
+    return type(cls_name, (CodecBackend,), {
+        "precision": precision,
+        "normalizer_size": normalizer_size,
+        "__doc__": f"Backend for precision={precision}, normalizer_size={normalizer_size} "
+                   f"(cuda/neuzip.cu:47-105).",
+    })
+
+
+class _CudaNamespace:
+    """Attribute access like the extension module: ``_cuda.Manager_f7_n0``."""
+    Algorithm = Algorithm
+
+    def __init__(self) -> None:
+        for p in PRECISIONS:
+            for nsz in NORMALIZER_SIZES:
+                cls = _make_backend(p, nsz)
+                setattr(self, cls.__name__, cls)
+
+
+_cuda = _CudaNamespace()

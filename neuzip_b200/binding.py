@@ -1,0 +1,112 @@
+"""The user-facing ``Manager`` and ``Algorithm`` (reference: neuzip/binding.py).
+
+``Manager`` hands out string handles for compressed tensors, remembers their
+shapes and forwards to a backend object that has the six methods of the
+reference's extension classes.  The backend is either the pass-through
+``DummyBackend`` (``Algorithm.dummy``) or a ``Manager_f{precision}_n{normalizer}``
+class from :mod:`neuzip_b200.backend`, looked up by name exactly as the
+reference does (neuzip/binding.py:69-70).
+"""
+from __future__ import annotations
+
+import enum
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import backend as _backend
+from .backend import _cuda
+
+
+class Algorithm(enum.Enum):
+    """neuzip/binding.py:23-27.  Only ``ans`` and ``dummy`` are implemented."""
+    ans = _cuda.Algorithm.ans
+    gdeflate = _cuda.Algorithm.gdeflate
+    zstd = _cuda.Algorithm.zstd
+    dummy = "dummy"
+
+
+class DummyBackend:
+    """Stores tensors uncompressed on the GPU (neuzip/binding.py:35-52).  Unlike
+    the reference's, it also answers ``linear_without_bias`` and ``split``-less
+    callers get a clear error instead of an AttributeError deep in a forward."""
+
+    def __init__(self) -> None:
+        self._store: Dict[str, torch.Tensor] = {}
+
+    def write(self, handle: str, tensor: torch.Tensor) -> None:
+        self._store[handle] = tensor.cuda()
+
+    def read(self, handle: str) -> torch.Tensor:
+        return self._store[handle]
+
+    def size(self, handle: str) -> int:
+        t = self._store[handle]
+        return t.numel() * t.element_size()
+
+    @torch.no_grad()
+    def linear(self, handle: str, inputs: torch.Tensor, shape, bias=None) -> torch.Tensor:
+        return torch.nn.functional.linear(inputs, self.read(handle).reshape(shape), bias)
+
+    def linear_without_bias(self, handle: str, inputs: torch.Tensor, shape) -> torch.Tensor:
+        return self.linear(handle, inputs, shape, None)
+
+    def split(self, tensor: torch.Tensor):
+        raise NotImplementedError("Algorithm.dummy has no split()")
+
+
+class Manager:
+    """neuzip/binding.py:55-115, same constructor and methods."""
+
+    def __init__(self, algorithm: Algorithm = Algorithm.ans, precision: int = 7,
+                 normalizer_size: Optional[int] = None, chunk_size: int = 2 ** 16) -> None:
+        normalizer_size = 0 if normalizer_size is None else normalizer_size
+        if algorithm == Algorithm.dummy:
+            self._be = DummyBackend()
+        else:
+            if precision not in _backend.PRECISIONS:
+                raise ValueError(f"precision must be one of {_backend.PRECISIONS}, got {precision}")
+            if normalizer_size not in _backend.NORMALIZER_SIZES:
+                raise ValueError(f"normalizer_size must be one of {_backend.NORMALIZER_SIZES}")
+            factory = getattr(_cuda, f"Manager_f{precision}_n{normalizer_size}")
+            self._be = factory(algorithm.value, chunk_size)
+        self.meta_dict: Dict[str, torch.Size] = {}
+
+    def write(self, tensor: torch.Tensor, handle: Optional[str] = None) -> str:
+        """Compress ``tensor`` and return its handle; an existing handle is replaced."""
+        if handle is None:
+            handle = str(len(self.meta_dict))
+        self.meta_dict[handle] = tensor.shape
+        self._be.write(handle, tensor)
+        return handle
+
+    def read(self, handle: str) -> torch.Tensor:
+        """Decompress to a CUDA tensor of the original shape (no grad)."""
+        shape = self.meta_dict[handle]
+        return self._be.read(handle).requires_grad_(False).reshape(shape)
+
+    def size(self, handle: str) -> int:
+        return self._be.size(handle)
+
+    def linear(self, handle: str, inputs: torch.Tensor, bias=None) -> torch.Tensor:
+        shape = self.meta_dict[handle]
+        if bias is None:
+            return self._be.linear_without_bias(handle, inputs, shape)
+        return self._be.linear(handle, inputs, shape, bias)
+
+    def convert(self, module: torch.nn.Module) -> torch.nn.Module:
+        from .utils import _convert
+        return _convert(self, module)
+
+    def split(self, tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        exp, frac = self._be.split(tensor)
+        return exp.reshape(tensor.shape), frac.reshape(tensor.shape)
+
+    # extras (not in the reference)
+    def check(self) -> None:
+        """Raise if any decode so far flagged a malformed container."""
+        if hasattr(self._be, "check"):
+            self._be.check()
+
+    def total_size(self) -> int:
+        return sum(self.size(h) for h in self.meta_dict)

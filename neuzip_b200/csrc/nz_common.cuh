@@ -1,0 +1,77 @@
+// Shared definitions of the neuzip_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/neuzip_b200.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "neuzip_b200 kernels are written for sm_100a (B200) only"
+#endif
+
+namespace nz {
+
+constexpr uint32_t kProbBits = 12;
+constexpr uint32_t kProbScale = 1u << kProbBits;
+constexpr uint32_t kStateLow = 1u << 16;
+constexpr uint32_t kMagic = 0x31525A4Eu;  // "NZR1"
+constexpr uint32_t kHeaderBytes = 64;
+constexpr uint32_t kFreqOffset = 64;
+constexpr uint32_t kOffsetsOffset = 576;
+constexpr uint32_t kRawFlag = 0x80000000u;
+constexpr uint32_t kMaxLaneSymbols = 1024;
+
+// Container header; must match struct nzo_header of the specification.
+struct Header {
+  uint32_t magic;
+  uint32_t version;
+  uint64_t n_symbols;
+  uint32_t lane_symbols;
+  uint32_t len_quantum;
+  uint32_t n_units;
+  uint32_t pad_symbol;
+  uint64_t payload_offset;
+  uint64_t payload_words;
+  uint64_t total_bytes;
+  uint32_t n_raw_units;
+  uint32_t max_coded_unit_words;
+};
+static_assert(sizeof(Header) == kHeaderBytes, "header layout");
+
+__host__ __device__ inline uint64_t align16(uint64_t x) { return (x + 15) & ~uint64_t(15); }
+__host__ __device__ inline uint32_t len_quantum(uint32_t S) { return (S + 511) / 512; }
+__host__ __device__ inline uint32_t lane_cap_words(uint32_t S) {
+  uint32_t a = 255u * len_quantum(S), b = S / 2;
+  return a < b ? a : b;
+}
+__host__ __device__ inline uint64_t unit_count(uint64_t n, uint32_t S) {
+  uint64_t U = 32ull * S;
+  return (n + U - 1) / U;
+}
+__host__ __device__ inline uint64_t payload_offset(uint64_t n_units) {
+  return align16(kOffsetsOffset + 4 * (n_units + 1));
+}
+inline bool valid_precision(int s) { return s == 0 || s == 1 || s == 3 || s == 7; }
+inline bool valid_lane_symbols(uint32_t S) { return S != 0 && (S & 7) == 0 && S <= kMaxLaneSymbols; }
+
+// Per-thread last-error text.
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t err, const char *what);
+
+#define NZ_CUDA_TRY(expr)                                   \
+  do {                                                      \
+    cudaError_t nz_err__ = (expr);                          \
+    if (nz_err__ != cudaSuccess) return ::nz::cuda_fail(nz_err__, #expr); \
+  } while (0)
+
+#define NZ_LAUNCH_CHECK(name)                               \
+  do {                                                      \
+    cudaError_t nz_err__ = cudaGetLastError();              \
+    if (nz_err__ != cudaSuccess) return ::nz::cuda_fail(nz_err__, name); \
+  } while (0)
+
+int sm_count();
+
+}  // namespace nz

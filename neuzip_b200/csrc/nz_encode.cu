@@ -1,0 +1,474 @@
+// Entropy-encoder side of the codec: histogram of the exponent bytes, integer
+// normalisation to 12-bit frequencies, lane-interleaved rANS encoding, and
+// compaction of the coded units into the NZR1 container.
+//
+// Replaces the nvcomp ANS manager calls of the reference's write path
+// (cuda/high_level.cu:103-124: configure_compression, compress,
+// get_compressed_output_size, right-sizing copy).  The byte format and the
+// arithmetic are specified by the CPU oracle; containers produced here are
+// byte-identical to the oracle's.
+//
+// Scratch layout (device, caller-provided):
+//   [0, 1024)            u32 hist[256]
+//   [1024, 1536)         u16 freq[256]
+//   [1536, 2560)         u32 enc_tab[256]   (freq | cum << 16)
+//   [2560, 2576)         u32 misc[4]        (pad symbol, max unit words, raw units, -)
+//   [4096, 4096+4*(nu+1))           u32 unit_words[nu]  (bit 31 = raw)
+//   [.., + 64*nu)                   u16 lane_len[nu][32]   (words; 0 = unit raw)
+//   [.., + nu*32*cap*2)             u16 lane_words[nu][32][cap]   cap = lane_cap_words(S)
+#include "nz_common.cuh"
+
+namespace nz {
+
+constexpr uint32_t kScratchHist = 0;
+constexpr uint32_t kScratchFreq = 1024;
+constexpr uint32_t kScratchTab = 1536;
+constexpr uint32_t kScratchMisc = 2560;
+constexpr uint32_t kScratchUnits = 4096;
+
+struct ScratchLayout {
+  uint64_t unit_words, lane_len, lane_words, total;
+};
+
+__host__ __device__ inline ScratchLayout scratch_layout(uint64_t n, uint32_t S) {
+  const uint64_t nu = unit_count(n, S);
+  ScratchLayout L;
+  L.unit_words = kScratchUnits;
+  L.lane_len = align16(L.unit_words + 4 * (nu + 1));
+  L.lane_words = align16(L.lane_len + 64 * nu);
+  L.total = align16(L.lane_words + nu * 32ull * lane_cap_words(S) * 2) + 16;
+  return L;
+}
+
+// ---------------------------------------------------------------- histogram
+// One 256-bin histogram per warp in shared memory (the exponent distribution
+// is so peaked that a block-wide histogram would serialise on two bins), folded
+// into the global histogram with one atomic per non-empty bin.
+constexpr int kHistThreads = 256;
+constexpr int kHistWarps = kHistThreads / 32;
+
+__global__ void __launch_bounds__(kHistThreads)
+histogram_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t *__restrict__ hist) {
+  __shared__ uint32_t sh[kHistWarps][256];
+  for (int i = threadIdx.x; i < kHistWarps * 256; i += kHistThreads) (&sh[0][0])[i] = 0;
+  __syncthreads();
+  uint32_t *mine = sh[threadIdx.x >> 5];
+  const uint64_t n_vec = n / 16;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint4 *v = reinterpret_cast<const uint4 *>(sym);
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    const uint4 q = __ldcs(v + i);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      // runs of equal bytes inside a word are common: count them locally
+      const uint32_t b0 = w[k] & 0xFF, b1 = (w[k] >> 8) & 0xFF, b2 = (w[k] >> 16) & 0xFF,
+                     b3 = w[k] >> 24;
+      if (b0 == b1 && b1 == b2 && b2 == b3) {
+        atomicAdd(&mine[b0], 4u);
+      } else {
+        atomicAdd(&mine[b0], 1u);
+        atomicAdd(&mine[b1], 1u);
+        atomicAdd(&mine[b2], 1u);
+        atomicAdd(&mine[b3], 1u);
+      }
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (uint64_t i = n_vec * 16; i < n; ++i) atomicAdd(&mine[sym[i]], 1u);
+  __syncthreads();
+  for (int b = threadIdx.x; b < 256; b += kHistThreads) {
+    uint32_t s = 0;
+#pragma unroll
+    for (int w = 0; w < kHistWarps; ++w) s += sh[w][b];
+    if (s) atomicAdd(&hist[b], s);
+  }
+}
+
+// ------------------------------------------------------------ normalisation
+// Integer-only, identical to nzo_normalize of the specification.  The counts
+// are 32-bit here (a tensor of 2^32 or more elements is rejected by the host
+// code), the products 64-bit.
+__global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__restrict__ freq,
+                                 uint32_t *__restrict__ enc_tab, uint32_t *__restrict__ misc,
+                                 uint16_t *__restrict__ container_freq) {
+  __shared__ int32_t f[256];
+  __shared__ uint64_t total_sh;
+  const int t = threadIdx.x;  // 256 threads
+  if (t == 0) {
+    uint64_t total = 0;
+    for (int i = 0; i < 256; ++i) total += hist[i];
+    total_sh = total;
+  }
+  __syncthreads();
+  const uint64_t total = total_sh;
+  {
+    const uint64_t h = hist[t];
+    int32_t v = 0;
+    if (total == 0) {
+      v = (t == 0) ? (int32_t)kProbScale : 0;
+    } else if (h) {
+      const uint64_t q = (h * kProbScale + total / 2) / total;
+      v = q ? (int32_t)q : 1;
+    }
+    f[t] = v;
+  }
+  __syncthreads();
+  if (t == 0) {
+    int32_t sum = 0;
+    for (int i = 0; i < 256; ++i) sum += f[i];
+    int32_t d = (int32_t)kProbScale - sum;
+    while (d != 0) {
+      int top = 0;
+      for (int i = 1; i < 256; ++i)
+        if (f[i] > f[top]) top = i;
+      if (d > 0) {
+        f[top] += d;
+        d = 0;
+      } else {
+        const int32_t room = f[top] - 1;
+        const int32_t take = (-d < room) ? -d : room;
+        f[top] -= take;
+        d += take;
+      }
+    }
+    for (int i = 0; i < 256; ++i) {
+      if (f[i] == (int32_t)kProbScale) {
+        f[i] = kProbScale - 1;
+        f[(i + 1) & 255] = 1;
+        break;
+      }
+    }
+    uint32_t cum = 0, pad = 0;
+    for (int i = 0; i < 256; ++i) {
+      if (f[i] > f[pad]) pad = i;
+      enc_tab[i] = (uint32_t)f[i] | (cum << 16);
+      cum += f[i];
+    }
+    misc[0] = pad;
+    misc[1] = 0;  // max coded unit words
+    misc[2] = 0;  // raw units
+  }
+  __syncthreads();
+  freq[t] = (uint16_t)f[t];
+  container_freq[t] = (uint16_t)f[t];
+}
+
+// ------------------------------------------------------------------ encoder
+// One warp per unit, one lane per lane stream.  A lane walks its S symbols
+// backwards (8 consecutive exponent bytes per 64-bit load), emits 16-bit
+// renormalisation words backwards into its slice of the scratch area and
+// finally its 32-bit state, so that the slice read forwards is the stream in
+// decoder order.
+constexpr int kEncWarps = 4;
+
+__global__ void __launch_bounds__(kEncWarps * 32)
+encode_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t n_units,
+              const uint32_t *__restrict__ enc_tab_g, const uint32_t *__restrict__ misc,
+              uint32_t *__restrict__ unit_words, uint16_t *__restrict__ lane_len,
+              uint16_t *__restrict__ lane_words) {
+  __shared__ uint32_t tab[256];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) tab[i] = enc_tab_g[i];
+  __syncthreads();
+  const uint32_t pad = misc[0];
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t lenq = len_quantum(S);
+  const uint32_t cap = lane_cap_words(S);
+  const uint64_t U = 32ull * S;
+  for (uint32_t u = blockIdx.x * kEncWarps + (threadIdx.x >> 5); u < n_units;
+       u += gridDim.x * kEncWarps) {
+    const uint64_t first = (uint64_t)u * U;
+    const uint64_t count = (n - first < U) ? (n - first) : U;
+    uint16_t *mine = lane_words + ((uint64_t)u * 32 + lane) * cap;
+    uint32_t x = kStateLow;
+    uint32_t emitted = 0;
+    bool overflow = false;
+    for (int32_t blk = (int32_t)(S / 8) - 1; blk >= 0; --blk) {
+      const uint64_t e0 = first + (uint64_t)blk * 256 + lane * 8;
+      uint32_t lo, hi;
+      if (e0 + 8 <= n) {
+        const uint2 q = *reinterpret_cast<const uint2 *>(sym + e0);
+        lo = q.x;
+        hi = q.y;
+      } else {
+        lo = hi = 0;
+        for (int t = 0; t < 8; ++t) {
+          const uint32_t s = (e0 + t < n) ? sym[e0 + t] : pad;
+          if (t < 4) lo |= s << (8 * t); else hi |= s << (8 * (t - 4));
+        }
+      }
+#pragma unroll
+      for (int t = 7; t >= 0; --t) {
+        const uint32_t s = ((t < 4 ? lo : hi) >> (8 * (t & 3))) & 0xFFu;
+        const uint32_t ent = tab[s];
+        const uint32_t fr = ent & 0xFFFFu, cum = ent >> 16;
+        if (x >= (fr << (32 - kProbBits))) {
+          // words beyond the capacity are dropped; the unit is then stored raw
+          if (emitted + 2 < cap) mine[cap - 1 - emitted] = (uint16_t)(x & 0xFFFFu);
+          else overflow = true;
+          ++emitted;
+          x >>= 16;
+        }
+        x = ((x / fr) << kProbBits) + (x % fr) + cum;
+      }
+    }
+    uint32_t words = emitted + 2;
+    if (words > cap) overflow = true;
+    const uint32_t q = (words + lenq - 1) / lenq;
+    if (!overflow) {
+      // state in front of the emitted words
+      mine[cap - emitted - 2] = (uint16_t)(x & 0xFFFFu);
+      mine[cap - emitted - 1] = (uint16_t)(x >> 16);
+    }
+    const bool any_overflow = __any_sync(0xFFFFFFFFu, overflow);
+    uint32_t tot = q * lenq;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xFFFFFFFFu, tot, o);
+    const uint64_t coded = 16ull + tot;
+    const uint64_t raw_words = (count + 1) / 2;
+    const bool raw = any_overflow || coded >= raw_words;
+    lane_len[(uint64_t)u * 32 + lane] = raw ? 0 : (uint16_t)words;
+    if (lane == 0) unit_words[u] = raw ? ((uint32_t)raw_words | kRawFlag) : (uint32_t)coded;
+  }
+}
+
+// Exclusive scan of the unit sizes -> offset table in the container, plus the
+// header.  One block; the unit count is small (N / (32 S)).
+__global__ void __launch_bounds__(1024)
+scan_kernel(const uint32_t *__restrict__ unit_words, uint32_t n_units, uint64_t n, uint32_t S,
+            const uint32_t *__restrict__ misc, uint8_t *__restrict__ container) {
+  __shared__ uint64_t part[1024];
+  __shared__ uint32_t raw_cnt[1024];
+  __shared__ uint32_t max_w[1024];
+  const uint32_t t = threadIdx.x;
+  const uint32_t per = (n_units + 1023) / 1024;
+  const uint32_t lo = t * per < n_units ? t * per : n_units;
+  const uint32_t hi = lo + per < n_units ? lo + per : n_units;
+  uint64_t s = 0;
+  uint32_t r = 0, m = 0;
+  for (uint32_t u = lo; u < hi; ++u) {
+    const uint32_t w = unit_words[u];
+    s += w & ~kRawFlag;
+    if (w & kRawFlag) ++r; else if (w > m) m = w;
+  }
+  part[t] = s;
+  raw_cnt[t] = r;
+  max_w[t] = m;
+  __syncthreads();
+  if (t == 0) {
+    uint64_t run = 0;
+    uint32_t rr = 0, mm = 0;
+    for (int i = 0; i < 1024; ++i) {
+      const uint64_t v = part[i];
+      part[i] = run;
+      run += v;
+      rr += raw_cnt[i];
+      if (max_w[i] > mm) mm = max_w[i];
+    }
+    const uint64_t pay_off = payload_offset(n_units);
+    Header h;
+    h.magic = kMagic;
+    h.version = 1;
+    h.n_symbols = n;
+    h.lane_symbols = S;
+    h.len_quantum = len_quantum(S);
+    h.n_units = n_units;
+    h.pad_symbol = misc[0];
+    h.payload_offset = pay_off;
+    h.payload_words = run;
+    h.total_bytes = align16(pay_off + run * 2);
+    h.n_raw_units = rr;
+    h.max_coded_unit_words = mm;
+    *reinterpret_cast<Header *>(container) = h;
+    uint32_t *offsets = reinterpret_cast<uint32_t *>(container + kOffsetsOffset);
+    offsets[n_units] = (uint32_t)run;
+    // zero the gaps: after the offset table and after the payload
+    for (uint64_t b = kOffsetsOffset + 4ull * (n_units + 1); b < pay_off; ++b) container[b] = 0;
+    for (uint64_t b = pay_off + run * 2; b < h.total_bytes; ++b) container[b] = 0;
+  }
+  __syncthreads();
+  uint64_t run = part[t];
+  uint32_t *offsets = reinterpret_cast<uint32_t *>(container + kOffsetsOffset);
+  for (uint32_t u = lo; u < hi; ++u) {
+    const uint32_t w = unit_words[u];
+    offsets[u] = (uint32_t)run | (w & kRawFlag);
+    run += w & ~kRawFlag;
+  }
+}
+
+// Copy each unit to its place in the payload: one warp per unit.
+__global__ void __launch_bounds__(256)
+compact_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t n_units,
+               const uint16_t *__restrict__ lane_len, const uint16_t *__restrict__ lane_words,
+               uint8_t *__restrict__ container) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t lenq = len_quantum(S);
+  const uint32_t cap = lane_cap_words(S);
+  const uint64_t U = 32ull * S;
+  const uint32_t *offsets = reinterpret_cast<const uint32_t *>(container + kOffsetsOffset);
+  uint16_t *payload = reinterpret_cast<uint16_t *>(container + payload_offset(n_units));
+  for (uint32_t u = blockIdx.x * 8 + (threadIdx.x >> 5); u < n_units; u += gridDim.x * 8) {
+    const uint32_t off = offsets[u];
+    uint16_t *dst = payload + (off & ~kRawFlag);
+    const uint64_t first = (uint64_t)u * U;
+    const uint64_t count = (n - first < U) ? (n - first) : U;
+    if (off & kRawFlag) {
+      uint8_t *d8 = reinterpret_cast<uint8_t *>(dst);
+      for (uint64_t i = lane; i < count; i += 32) d8[i] = sym[first + i];
+      if ((count & 1) && lane == 0) d8[count] = 0;
+      continue;
+    }
+    const uint32_t my_words = lane_len[(uint64_t)u * 32 + lane];
+    const uint32_t my_q = (my_words + lenq - 1) / lenq;
+    reinterpret_cast<uint8_t *>(dst)[lane] = (uint8_t)my_q;
+    uint32_t p = 16;
+    for (uint32_t j = 0; j < 32; ++j) {
+      const uint32_t words = __shfl_sync(0xFFFFFFFFu, my_words, j);
+      const uint32_t padded = __shfl_sync(0xFFFFFFFFu, my_q, j) * lenq;
+      // the lane's words sit at the end of its scratch slice, in decoder order
+      const uint16_t *src = lane_words + ((uint64_t)u * 32 + j + 1) * cap - words;
+      for (uint32_t k = lane; k < padded; k += 32) dst[p + k] = (k < words) ? src[k] : (uint16_t)0;
+      p += padded;
+    }
+  }
+}
+
+
+// ------------------------------------------------------------------- host
+int histogram_u8(const void *sym, uint64_t n, void *hist, cudaStream_t st) {
+  NZ_CUDA_TRY(cudaMemsetAsync(hist, 0, 1024, st));
+  if (n == 0) return NZ_OK;
+  uint64_t blocks = (n / 16 + kHistThreads - 1) / kHistThreads;
+  const uint64_t cap = (uint64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  histogram_kernel<<<(unsigned)blocks, kHistThreads, 0, st>>>((const uint8_t *)sym, n, (uint32_t *)hist);
+  NZ_LAUNCH_CHECK("histogram_kernel");
+  return NZ_OK;
+}
+
+uint64_t container_bound(uint64_t n, uint32_t S) {
+  const uint64_t U = 32ull * S;
+  const uint64_t nu = unit_count(n, S);
+  return align16(kOffsetsOffset + 4 * (nu + 1)) + align16(nu * U + 2 * nu) + 16;
+}
+
+int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container,
+                     uint64_t container_cap, void *scratch, uint64_t scratch_bytes,
+                     cudaStream_t st) {
+  const ScratchLayout L = scratch_layout(n, S);
+  if (scratch_bytes < L.total) {
+    set_error("encode: scratch of %llu bytes is smaller than the %llu required",
+              (unsigned long long)scratch_bytes, (unsigned long long)L.total);
+    return NZ_E_CAPACITY;
+  }
+  if (container_cap < container_bound(n, S)) {
+    set_error("encode: container capacity %llu is below the bound %llu",
+              (unsigned long long)container_cap, (unsigned long long)container_bound(n, S));
+    return NZ_E_CAPACITY;
+  }
+  uint8_t *sc = (uint8_t *)scratch;
+  uint8_t *cont = (uint8_t *)container;
+  const uint32_t nu = (uint32_t)unit_count(n, S);
+  int rc = histogram_u8(exp_in, n, sc + kScratchHist, st);
+  if (rc) return rc;
+  normalize_kernel<<<1, 256, 0, st>>>((const uint32_t *)(sc + kScratchHist),
+                                      (uint16_t *)(sc + kScratchFreq),
+                                      (uint32_t *)(sc + kScratchTab),
+                                      (uint32_t *)(sc + kScratchMisc),
+                                      (uint16_t *)(cont + kFreqOffset));
+  NZ_LAUNCH_CHECK("normalize_kernel");
+  if (nu) {
+    uint32_t blocks = (nu + kEncWarps - 1) / kEncWarps;
+    encode_kernel<<<blocks, kEncWarps * 32, 0, st>>>(
+        (const uint8_t *)exp_in, n, S, nu, (const uint32_t *)(sc + kScratchTab),
+        (const uint32_t *)(sc + kScratchMisc), (uint32_t *)(sc + L.unit_words),
+        (uint16_t *)(sc + L.lane_len), (uint16_t *)(sc + L.lane_words));
+    NZ_LAUNCH_CHECK("encode_kernel");
+  }
+  scan_kernel<<<1, 1024, 0, st>>>((const uint32_t *)(sc + L.unit_words), nu, n, S,
+                                  (const uint32_t *)(sc + kScratchMisc), cont);
+  NZ_LAUNCH_CHECK("scan_kernel");
+  if (nu) {
+    uint32_t blocks = (nu + 7) / 8;
+    const uint32_t capb = (uint32_t)sm_count() * 8;
+    if (blocks > capb) blocks = capb;
+    compact_kernel<<<blocks, 256, 0, st>>>((const uint8_t *)exp_in, n, S, nu,
+                                           (const uint16_t *)(sc + L.lane_len),
+                                           (const uint16_t *)(sc + L.lane_words), cont);
+    NZ_LAUNCH_CHECK("compact_kernel");
+  }
+  return NZ_OK;
+}
+
+}  // namespace nz
+
+static int check_encode_args(const char *who, uint64_t n, uint32_t S) {
+  if (!nz::valid_lane_symbols(S)) {
+    nz::set_error("%s: lane_symbols must be a multiple of 8 in [8, %u] (got %u)", who,
+                  nz::kMaxLaneSymbols, S);
+    return NZ_E_ARG;
+  }
+  if (n >= (1ull << 32)) {
+    nz::set_error("%s: tensors of 2^32 or more elements are not supported", who);
+    return NZ_E_ARG;
+  }
+  return NZ_OK;
+}
+
+extern "C" uint64_t nz_container_bound(uint64_t n, uint32_t lane_symbols) {
+  if (!nz::valid_lane_symbols(lane_symbols)) return 0;
+  return nz::container_bound(n, lane_symbols);
+}
+
+extern "C" uint64_t nz_encode_scratch_bytes(uint64_t n, uint32_t lane_symbols) {
+  if (!nz::valid_lane_symbols(lane_symbols)) return 0;
+  return nz::scratch_layout(n, lane_symbols).total;
+}
+
+extern "C" int nz_histogram_u8(const void *sym, uint64_t n, void *hist_u32, void *stream) {
+  if (!hist_u32 || (n && !sym) || ((uintptr_t)sym & 15)) {
+    nz::set_error("nz_histogram_u8: null or misaligned pointer (input must be 16-byte aligned)");
+    return NZ_E_ARG;
+  }
+  if (n >= (1ull << 32)) {
+    nz::set_error("nz_histogram_u8: 2^32 or more symbols are not supported");
+    return NZ_E_ARG;
+  }
+  return nz::histogram_u8(sym, n, hist_u32, (cudaStream_t)stream);
+}
+
+extern "C" int nz_encode_exponents(const void *exp_in, uint64_t n, uint32_t lane_symbols,
+                                   void *container, uint64_t container_cap, void *scratch,
+                                   uint64_t scratch_bytes, void *stream) {
+  int rc = check_encode_args("nz_encode_exponents", n, lane_symbols);
+  if (rc) return rc;
+  if (!container || !scratch || (n && !exp_in)) {
+    nz::set_error("nz_encode_exponents: null pointer");
+    return NZ_E_ARG;
+  }
+  if (((uintptr_t)exp_in & 15) || ((uintptr_t)container & 15) || ((uintptr_t)scratch & 15)) {
+    nz::set_error("nz_encode_exponents: buffers must be 16-byte aligned");
+    return NZ_E_ARG;
+  }
+  return nz::encode_exponents(exp_in, n, lane_symbols, container, container_cap, scratch,
+                              scratch_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int nz_container_bytes(const void *container, uint64_t *total_bytes,
+                                  uint32_t *max_unit_words, void *stream) {
+  if (!container || !total_bytes) {
+    nz::set_error("nz_container_bytes: null pointer");
+    return NZ_E_ARG;
+  }
+  nz::Header h;
+  NZ_CUDA_TRY(cudaMemcpyAsync(&h, container, sizeof(h), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  NZ_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  if (h.magic != nz::kMagic || h.version != 1) {
+    nz::set_error("nz_container_bytes: not an NZR1 container");
+    return NZ_E_FORMAT;
+  }
+  *total_bytes = h.total_bytes;
+  if (max_unit_words) *max_unit_words = h.max_coded_unit_words;
+  return NZ_OK;
+}

@@ -1,0 +1,28 @@
+"""Linear layer with a compressed weight (reference: neuzip/nn/linear.py:14-35)."""
+import torch
+
+from ..ops import CompressedLinear
+from .module import Parameter
+
+
+class Linear(torch.nn.Module):
+    def __init__(self, manager, linear: torch.nn.Linear) -> None:
+        super().__init__()
+        self.manager = manager
+        self.in_features, self.out_features = linear.in_features, linear.out_features
+        self._p = Parameter(manager, linear.weight.data)
+        if linear.bias is None:
+            self.register_parameter("bias", None)
+        else:
+            self.bias = torch.nn.Parameter(linear.bias.data)
+
+    @property
+    def weight(self) -> Parameter:
+        return self._p
+
+    def forward(self, x):
+        return CompressedLinear.apply(x, self._p, self.bias)
+
+    def extra_repr(self) -> str:
+        return (f"! in_features={self.in_features}, out_features={self.out_features}, "
+                f"bias={self.bias is not None}")

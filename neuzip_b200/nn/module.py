@@ -1,0 +1,26 @@
+"""Compressed parameter (reference: neuzip/nn/module.py:11-28)."""
+import torch
+
+
+class Parameter(torch.nn.Parameter):
+    """An ``nn.Parameter`` whose own storage is empty; the values live in the
+    manager under ``_handle``.  Calling the parameter decompresses it.  The
+    real weight gradient is collected in ``_gradient`` by the autograd function,
+    ``.grad`` only ever holds a zero-size placeholder."""
+
+    def __new__(cls, manager, data, requires_grad=True):
+        placeholder = torch.zeros(0, dtype=data.dtype, device=data.device)
+        self = super().__new__(cls, placeholder, requires_grad)
+        self._manager = manager
+        self._shape = data.shape
+        self._gradient = None
+        self._handle = manager.write(data)
+        return self
+
+    @torch.no_grad()
+    def __call__(self) -> torch.Tensor:
+        w = self._manager.read(self._handle).reshape(self._shape)
+        return w.to(self.device).requires_grad_(False)
+
+    def linear(self, inputs, bias=None):
+        return self._manager.linear(self._handle, inputs, bias).to(self.device)

@@ -1,0 +1,66 @@
+"""Model surgery (reference: neuzip/utils.py:19-68)."""
+import logging
+
+import torch
+
+from .nn import Embedding, Linear
+
+logger = logging.getLogger(__name__)
+
+
+def _hf_conv1d_type():
+    try:
+        from transformers.pytorch_utils import Conv1D
+        return Conv1D
+    except Exception:   # transformers is optional for the codec itself
+        return ()
+
+
+def _set_module_by_name(parent_module, name, child_module):
+    """Replace the sub-module at the dotted path ``name`` (neuzip/utils.py:19-31)."""
+    *path, leaf = name.split(".")
+    node = parent_module
+    for part in path:
+        node = node[int(part)] if part.isnumeric() else getattr(node, part)
+    setattr(node, leaf, child_module)
+
+
+def _delete_module(module):
+    """Drop the parameters of a replaced module so their memory can be freed
+    (neuzip/utils.py:34-38)."""
+    for pname, _ in list(module.named_parameters()):
+        setattr(module, pname, None)
+
+
+def _unroll_convert(manager, module):
+    """Flat variant that also converts embeddings (neuzip/utils.py:41-54; unused by
+    ``Manager.convert``)."""
+    for name, m in list(module.named_modules()):
+        if isinstance(m, torch.nn.Linear):
+            replacement = Linear(manager, m)
+        elif isinstance(m, torch.nn.Embedding):
+            replacement = Embedding(manager, m)
+        else:
+            continue
+        logger.debug("Quantizing %s: %s", name, m)
+        _set_module_by_name(module, name, replacement)
+        _delete_module(m)
+    return module
+
+
+def _convert(manager, module, prefix=""):
+    """Recursively replace ``nn.Linear`` (and HF ``Conv1D``) children by compressed
+    Linears; any child whose name contains ``lm_head`` is left alone and not
+    descended into (neuzip/utils.py:57-68)."""
+    convertible = (torch.nn.Linear,) + ((_hf_conv1d_type(),) if _hf_conv1d_type() else ())
+    for name, child in list(module.named_children()):
+        full_name = f"{prefix}.{name}" if prefix else name
+        if "lm_head" in name:
+            continue
+        if isinstance(child, convertible):
+            logger.debug("Converting %s: %s", full_name, child)
+            setattr(module, name, Linear(manager, child))
+            _delete_module(child)
+        else:
+            _convert(manager, child, full_name)
+    return module

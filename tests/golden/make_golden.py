@@ -1,0 +1,76 @@
+"""Generates tests/golden/config1.json from the CPU oracle.
+
+Run from the repository root:  python tests/golden/make_golden.py
+
+The input is BASELINE config 1: torch.manual_seed(0) on the CPU generator,
+(randn(4096, 4096) * 0.02).to(bfloat16).  `input_crc32`, `exp_crc32` and
+`frac_crc32` were first derived independently (from cuda/kernels.cuh:120-155 of
+the reference) when the reference was surveyed; `expected_from_survey` below
+holds those values and the script refuses to write the file if the oracle
+disagrees with them.  Container values pin this project's own NZR1 format.
+The reference cannot be run (no CPU path, nvcomp absent), so none of these
+numbers is reference-run.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from oracle import oracle as O  # noqa: E402
+
+expected_from_survey = {
+    "input_crc32": "0x510377ef",
+    "first_four": ["0xbcb8", "0xbcbd", "0xbba4", "0xbc0e"],
+    "0": ("0x7b2cfc89", "0x483194aa"),
+    "1": ("0xf28d35bb", "0x2e5581d6"),
+    "3": ("0x1a0859a8", "0x20c62915"),
+    "7": ("0xc089ba1b", "0x4b33adee"),
+    "roundtrip_identical_patterns": {"0": 512, "1": 1024, "3": 4096, "7": 65536},
+}
+
+
+def main():
+    torch.manual_seed(0)
+    w = (torch.randn(4096, 4096, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    bits = w.view(torch.int16).numpy().view(np.uint16).reshape(-1)
+    n = bits.size
+    out = {"n": n, "input_crc32": hex(O.crc32(bits)),
+           "first_four": [hex(int(v)) for v in bits[:4]], "precision": {}}
+    assert out["input_crc32"] == expected_from_survey["input_crc32"]
+    assert out["first_four"] == expected_from_survey["first_four"]
+    allp = np.arange(65536, dtype=np.uint16)
+    for s in (0, 1, 3, 7):
+        exp, frac = O.split(bits, s)
+        assert (hex(O.crc32(exp)), hex(O.crc32(frac))) == expected_from_survey[str(s)]
+        ea, fa = O.split(allp, s)
+        same = int((O.merge(ea, fa, s) == allp).sum())
+        assert same == expected_from_survey["roundtrip_identical_patterns"][str(s)]
+        S = O.default_lane_symbols(s)
+        cont = O.encode(exp, S)
+        rt = O.decompress_bf16(cont, frac, n, s, canonical_nan=True)
+        h = O.histogram(exp).astype(np.float64)
+        p = h[h > 0] / h.sum()
+        entropy = float(-(p * np.log2(p)).sum())
+        ideal = entropy * n / 8 + O.frac_bytes(n, s) + (n + 1023) // 1024
+        err = np.abs(torch.from_numpy(rt.view(np.int16)).view(torch.bfloat16).float()
+                     - w.view(-1).float()).max().item()
+        out["precision"][str(s)] = {
+            "exp_crc32": hex(O.crc32(exp)), "frac_crc32": hex(O.crc32(frac)),
+            "lane_symbols": S, "container_bytes": int(cont.size),
+            "container_crc32": hex(O.crc32(cont)), "roundtrip_crc32": hex(O.crc32(rt)),
+            "roundtrip_identical_patterns": same, "exponent_entropy_bits": entropy,
+            "ideal_bytes": ideal, "stored_bytes": int(cont.size + frac.size),
+            "max_abs_error": err,
+        }
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "config1.json")
+    with open(path, "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+    print("wrote", path)
+
+
+if __name__ == "__main__":
+    main()

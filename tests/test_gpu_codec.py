@@ -1,0 +1,230 @@
+"""GPU parity tests: every C-ABI kernel against the CPU oracle, bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests import nzabi as A
+
+pytestmark = pytest.mark.gpu
+
+PRECISIONS = (0, 1, 3, 7)
+SIZES = (1, 7, 8, 9, 63, 64, 65, 255, 256, 257, 1000, 4095, 8192, 8193, 65536, 100003, 300000)
+
+
+def weights(n, seed, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(n, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+def all_patterns():
+    return np.arange(65536, dtype=np.uint16)
+
+
+# ---------------------------------------------------------------- split / merge
+@pytest.mark.parametrize("s", PRECISIONS)
+def test_split_all_patterns(s):
+    bits = all_patterns()
+    x = A.from_bits(bits)
+    exp, frac = A.split(x, s)
+    e_ref, f_ref = O.split(bits, s, literal=True)
+    assert np.array_equal(exp.cpu().numpy(), e_ref)
+    assert np.array_equal(frac.cpu().numpy(), f_ref)
+
+
+@pytest.mark.parametrize("s", PRECISIONS)
+@pytest.mark.parametrize("canon", (False, True))
+def test_merge_all_patterns(s, canon):
+    bits = all_patterns()
+    e_ref, f_ref = O.split(bits, s)
+    out = A.merge(A.dev_u8(e_ref), A.dev_u8(f_ref), bits.size, s, canon)
+    ref = O.merge(e_ref, f_ref, s, canonical_nan=canon)
+    assert np.array_equal(A.to_bits(out), ref)
+
+
+@pytest.mark.parametrize("s", PRECISIONS)
+@pytest.mark.parametrize("n", SIZES)
+def test_split_merge_ragged_sizes(s, n):
+    x = weights(n, 100 + n).cuda()
+    bits = A.to_bits(x)
+    exp, frac = A.split(x, s)
+    e_ref, f_ref = O.split(bits, s)
+    assert np.array_equal(exp.cpu().numpy(), e_ref)
+    assert np.array_equal(frac.cpu().numpy(), f_ref)
+    out = A.merge(exp, frac, n, s)
+    assert np.array_equal(A.to_bits(out), O.merge(e_ref, f_ref, s))
+
+
+def test_empty_inputs_are_accepted():
+    L = A.lib()
+    assert L.nz_split_bf16(0, 0, 7, 0, 0, A.stream()) == 0
+    assert L.nz_merge_bf16(0, 0, 0, 7, 0, 0, A.stream()) == 0
+    assert L.nz_decompress_bf16(0, 0, 0, 0, 7, 256, 0, 0, 0, 0, A.stream()) == 0
+
+
+# ------------------------------------------------------------------- histogram
+@pytest.mark.parametrize("n", (1, 15, 16, 17, 4096, 100003, 1 << 20))
+def test_histogram(n):
+    rng = np.random.default_rng(n)
+    sym = rng.choice(np.arange(110, 126, dtype=np.uint8), size=n,
+                     p=np.array([1, 1, 2, 3, 5, 8, 13, 21, 34, 55, 89, 144, 233, 120, 30, 5]) / 764)
+    d = A.dev_u8(sym)
+    hist = torch.full((256,), 7, dtype=torch.int32, device="cuda")
+    from neuzip_b200 import _lib
+    _lib.check(A.lib().nz_histogram_u8(d.data_ptr(), n, hist.data_ptr(), A.stream()))
+    assert np.array_equal(hist.cpu().numpy().astype(np.uint64), O.histogram(sym))
+
+
+# ------------------------------------------------------------ entropy coder
+def exponent_streams():
+    rng = np.random.default_rng(7)
+    yield "gauss", O.split(A.to_bits(weights(70000, 3)), 7)[0]
+    yield "gauss_big", O.split(A.to_bits(weights(1 << 20, 4)), 7)[0]
+    yield "constant", np.full(20000, 121, np.uint8)
+    yield "two_symbols", rng.choice(np.array([3, 250], np.uint8), size=33333, p=[0.9, 0.1])
+    yield "uniform_incompressible", rng.integers(0, 256, size=50000, dtype=np.uint8)
+    yield "all_256_skewed", np.concatenate(
+        [np.arange(256, dtype=np.uint8), np.full(90000, 17, np.uint8)])
+    yield "single_element", np.array([200], np.uint8)
+    yield "half_raw_half_coded", np.concatenate(
+        [rng.integers(0, 256, size=32768, dtype=np.uint8), np.full(32768, 9, np.uint8)])
+
+
+@pytest.mark.parametrize("S", (8, 64, 256, 384, 512, 1024))
+def test_encode_matches_oracle_bytes(S):
+    for name, sym in exponent_streams():
+        cont, mw = A.encode(A.dev_u8(sym), S)
+        ref = O.encode(sym, S)
+        got = cont.cpu().numpy()
+        assert got.size == ref.size, (name, S, got.size, ref.size)
+        assert np.array_equal(got, ref), (name, S)
+        assert mw == O.parse_header(ref)["max_coded_unit_words"]
+
+
+@pytest.mark.parametrize("S", (8, 64, 256, 384, 512, 1024))
+def test_decode_oracle_containers(S):
+    for name, sym in exponent_streams():
+        ref = O.encode(sym, S)
+        hdr = O.parse_header(ref)
+        for mw in (0, hdr["max_coded_unit_words"]):
+            exp, status = A.decode_exponents(A.dev_u8(ref), sym.size, S, mw)
+            assert status == 0, (name, S, status)
+            assert np.array_equal(exp.cpu().numpy(), sym), (name, S)
+
+
+@pytest.mark.parametrize("s", PRECISIONS)
+@pytest.mark.parametrize("n", SIZES)
+def test_compress_decompress_roundtrip(s, n):
+    S = O.default_lane_symbols(s)
+    x = weights(n, 500 + n).cuda()
+    bits = A.to_bits(x)
+    cont, frac, mw = A.compress(x, s, S)
+    c_ref, f_ref = O.compress_bf16(bits, s, S)
+    assert np.array_equal(cont.cpu().numpy(), c_ref)
+    assert np.array_equal(frac.cpu().numpy(), f_ref)
+    out, status = A.decompress(cont, frac, n, s, S, mw)
+    assert status == 0
+    ref = O.decompress_bf16(c_ref, f_ref, n, s)
+    assert np.array_equal(A.to_bits(out), ref)
+    if s == 7:
+        assert np.array_equal(A.to_bits(out), bits)      # lossless = bit exact
+
+
+@pytest.mark.parametrize("s", PRECISIONS)
+@pytest.mark.parametrize("canon", (False, True))
+def test_decompress_all_patterns_including_nan(s, canon):
+    bits = np.tile(all_patterns(), 3)          # NaN / inf / denormal / -0 patterns included
+    S = O.default_lane_symbols(s)
+    x = A.from_bits(bits)
+    cont, frac, mw = A.compress(x, s, S)
+    out, status = A.decompress(cont, frac, bits.size, s, S, mw, canon)
+    assert status == 0
+    e_ref, f_ref = O.split(bits, s, literal=True)
+    assert np.array_equal(A.to_bits(out), O.merge(e_ref, f_ref, s, canonical_nan=canon))
+
+
+def test_incompressible_tensor_is_stored_raw_and_round_trips():
+    rng = np.random.default_rng(11)
+    bits = rng.integers(0, 65536, size=200000, dtype=np.uint16)
+    bits = bits[(bits & 0x7F80) != 0x7F80]            # keep it NaN/inf free
+    x = A.from_bits(bits)
+    cont, frac, mw = A.compress(x, 7, 256)
+    assert O.parse_header(cont.cpu().numpy())["n_raw_units"] > 0
+    out, status = A.decompress(cont, frac, bits.size, 7, 256, mw)
+    assert status == 0 and np.array_equal(A.to_bits(out), bits)
+
+
+# ---------------------------------------------------- config 1 of the baseline
+def test_config1_seed0_matrix_matches_golden():
+    import json, os
+    golden = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "config1.json")))
+    torch.manual_seed(0)
+    w = (torch.randn(4096, 4096, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    bits = A.to_bits(w)
+    assert O.crc32(bits) == int(golden["input_crc32"], 16)
+    x = w.cuda().view(-1)
+    for s in PRECISIONS:
+        g = golden["precision"][str(s)]
+        exp, frac = A.split(x, s)
+        assert O.crc32(exp.cpu().numpy()) == int(g["exp_crc32"], 16)
+        assert O.crc32(frac.cpu().numpy()) == int(g["frac_crc32"], 16)
+        S = g["lane_symbols"]
+        cont, frac2, mw = A.compress(x, s, S)
+        assert cont.numel() == g["container_bytes"]
+        assert O.crc32(cont.cpu().numpy()) == int(g["container_crc32"], 16)
+        out, status = A.decompress(cont, frac2, x.numel(), s, S, mw, canon=True)
+        assert status == 0
+        assert O.crc32(A.to_bits(out)) == int(g["roundtrip_crc32"], 16)
+        stored = cont.numel() + frac2.numel()
+        assert stored <= 1.02 * g["ideal_bytes"], (s, stored, g["ideal_bytes"])
+    # lossless: bit exact
+    cont, frac, mw = A.compress(x, 7, 256)
+    out, _ = A.decompress(cont, frac, x.numel(), 7, 256, mw)
+    assert torch.equal(out.view(torch.int16), x.view(torch.int16))
+
+
+# -------------------------------------------------------- malformed containers
+def _corrupt(cont_np, where, value):
+    c = cont_np.copy()
+    c[where] = value
+    return c
+
+
+def test_malformed_containers_set_status_and_do_not_touch_guards():
+    sym = O.split(A.to_bits(weights(40000, 9)), 7)[0]
+    S = 256
+    ref = O.encode(sym, S)
+    hdr = O.parse_header(ref)
+    n = sym.size
+    cases = {
+        "magic": (_corrupt(ref, 0, 0), 0x1),
+        "n_symbols": (_corrupt(ref, 8, (ref[8] + 1) & 0xFF), 0x1),
+        "freq_sum": (_corrupt(ref, 64 + 2 * 121, (ref[64 + 2 * 121] + 1) & 0xFF), 0x1),
+        "offset_backwards": (_corrupt(ref, 576 + 4 + 3, 0x7F), 0x2),
+        "lane_length": (_corrupt(ref, hdr["payload_offset"] + 5, 1), 0x4),
+    }
+    for name, (bad, bit) in cases.items():
+        _, status = A.decode_exponents(A.dev_u8(bad), n, S, 0)
+        assert status & bit, (name, status)
+    # a flipped payload word decodes to garbage but must end in a wrong state
+    bad = _corrupt(ref, hdr["payload_offset"] + 32 + 9, ref[hdr["payload_offset"] + 32 + 9] ^ 0x55)
+    _, status = A.decode_exponents(A.dev_u8(bad), n, S, 0)
+    assert status & 0x8
+    # truncated buffer is refused on the host
+    from neuzip_b200 import _lib
+    L = A.lib()
+    out = torch.empty(n, dtype=torch.uint8, device="cuda")
+    d = A.dev_u8(ref[:512])
+    assert L.nz_decode_exponents(d.data_ptr(), 512, n, S, 0, out.data_ptr(), 0, A.stream()) == _lib.NZ_E_FORMAT
+
+
+def test_argument_errors():
+    from neuzip_b200 import _lib
+    L = A.lib()
+    x = torch.zeros(64, dtype=torch.bfloat16, device="cuda")
+    e = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    assert L.nz_split_bf16(x.data_ptr(), 64, 5, e.data_ptr(), e.data_ptr(), 0) == _lib.NZ_E_ARG
+    assert b"precision" in L.nz_last_error()
+    assert L.nz_split_bf16(x.data_ptr() + 2, 8, 7, e.data_ptr(), e.data_ptr(), 0) == _lib.NZ_E_ARG
+    assert L.nz_decode_exponents(e.data_ptr(), 64, 64, 12, 0, e.data_ptr(), 0, 0) == _lib.NZ_E_ARG
+    assert L.nz_encode_exponents(e.data_ptr(), 64, 256, e.data_ptr(), 64, e.data_ptr(), 64, 0) == _lib.NZ_E_CAPACITY
