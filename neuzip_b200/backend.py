@@ -51,11 +51,15 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _as_flat_bf16_cuda(tensor: torch.Tensor) -> torch.Tensor:
+def _require_bf16(tensor: torch.Tensor) -> None:
     if tensor.dtype != torch.bfloat16:
         # the reference dispatches fp32/fp16 as well (cuda/high_level.cu:144-158) but
         # truncates their mantissa to 8 bits (cuda/kernels.cuh:123); only bf16 is sound
         raise RuntimeError("Unsupported data type")
+
+
+def _as_flat_bf16_cuda(tensor: torch.Tensor) -> torch.Tensor:
+    _require_bf16(tensor)
     if not tensor.is_cuda:
         tensor = tensor.cuda()
     flat = tensor.detach().contiguous().view(-1)
@@ -114,6 +118,7 @@ class CodecBackend:
     # -- the six methods of the extension class ----------------------------
     def write(self, name: str, tensor: torch.Tensor) -> None:
         """cuda/high_level.cu:132-162 (+ _write_to_cache :71-130)."""
+        _require_bf16(tensor)
         self._ensure_device()
         flat = _as_flat_bf16_cuda(tensor)
         n = flat.numel()
@@ -171,6 +176,7 @@ class CodecBackend:
     def split(self, tensor: torch.Tensor) -> List[torch.Tensor]:
         """cuda/high_level.cu:301-321: always full mantissa (f_bits_save = 7, :289);
         returns [exponents, fractions], one byte per element each."""
+        _require_bf16(tensor)
         self._ensure_device()
         flat = _as_flat_bf16_cuda(tensor)
         n = flat.numel()

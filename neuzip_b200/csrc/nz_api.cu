@@ -72,7 +72,7 @@ extern "C" uint32_t nz_default_lane_symbols(int precision) {
     case 7: return 256;
     case 3: return 384;
     case 1: return 512;
-    case 0: return 512;
+    case 0: return 640;
     default: return 0;
   }
 }

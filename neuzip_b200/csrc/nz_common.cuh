@@ -13,8 +13,8 @@
 
 namespace nz {
 
-constexpr uint32_t kProbBits = 12;
-constexpr uint32_t kProbScale = 1u << kProbBits;
+constexpr uint32_t kMinProbBits = 10;
+constexpr uint32_t kMaxProbBits = 12;
 constexpr uint32_t kStateLow = 1u << 16;
 constexpr uint32_t kMagic = 0x31525A4Eu;  // "NZR1"
 constexpr uint32_t kHeaderBytes = 64;
@@ -31,7 +31,7 @@ struct Header {
   uint32_t lane_symbols;
   uint32_t len_quantum;
   uint32_t n_units;
-  uint32_t pad_symbol;
+  uint32_t prob_bits;
   uint64_t payload_offset;
   uint64_t payload_words;
   uint64_t total_bytes;
@@ -41,7 +41,7 @@ struct Header {
 static_assert(sizeof(Header) == kHeaderBytes, "header layout");
 
 __host__ __device__ inline uint64_t align16(uint64_t x) { return (x + 15) & ~uint64_t(15); }
-__host__ __device__ inline uint32_t len_quantum(uint32_t S) { return (S + 511) / 512; }
+__host__ __device__ inline uint32_t len_quantum(uint32_t S) { return (S + 767) / 768; }
 __host__ __device__ inline uint32_t lane_cap_words(uint32_t S) {
   uint32_t a = 255u * len_quantum(S), b = S / 2;
   return a < b ? a : b;

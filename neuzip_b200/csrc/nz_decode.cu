@@ -13,8 +13,15 @@
 // so a renormalisation costs one predicated 16-bit shared load and no
 // warp-wide vote.  A lane produces 8 consecutive tensor elements per step and
 // writes them with one 128-bit store; the warp's stores are 512 contiguous
-// bytes.  The 4096-entry decode table (symbol | freq << 8 | bias << 20) is
-// built once per CTA from the container's frequency table.
+// bytes.
+//
+// Decode table.  One entry per slot (symbol | bias << 8 | freq << 20), built
+// once per CTA from the container's frequency table.  Random table lookups by
+// 32 lanes would collide in the 32 shared-memory banks (3.5 wavefronts per
+// lookup on average, which made the shared-memory pipe the limiter), so the
+// table is replicated: with 2^10 slots every lane reads its own copy in its own
+// bank (always one wavefront), with 2^11 slots two lanes share a copy, with 2^12
+// four.  The replicated table always fills 128 KB; one CTA runs per SM.
 //
 // Robustness.  Header, offset table and lane lengths are validated before
 // use; a malformed container sets bits in the caller's status word and the
@@ -26,7 +33,6 @@
 
 namespace nz {
 
-constexpr uint32_t kLutBytes = kProbScale * 4;
 constexpr uint32_t kMaxWaitIters = 1u << 20;
 
 // ------------------------------------------------------------- PTX helpers
@@ -83,15 +89,43 @@ struct LaneState {
   uint32_t w;     // that word, already loaded
 };
 
-// One symbol.  Returns the table entry; the symbol is its low byte.
-__device__ __forceinline__ uint32_t decode_step(LaneState &st, uint32_t lut) {
-  const uint32_t ent = lds_u32(lut + ((st.x & (kProbScale - 1)) << 2));
-  st.x = ((ent >> 8) & 0xFFFu) * (st.x >> kProbBits) + (ent >> 20);
-  if (st.x < kStateLow) {
-    st.x = (st.x << 16) | st.w;
-    st.p += 2;
-    st.w = lds_u16(st.p);
-  }
+// Per-lane constants of the replicated decode table.
+struct LutView {
+  uint32_t base;    // shared address of this lane's copy (table base + bank offset)
+  uint32_t mask;    // 2^pb - 1
+  uint32_t stride;  // bytes between slots (4 x copies)
+  uint32_t pb;      // probability bits
+  uint32_t one, two, k64k;  // 1, 2 and 65536 in registers the compiler cannot fold
+};
+
+// One symbol.  Returns the table entry (symbol | bias << 8 | freq << 20); the
+// symbol is its low byte.  Written in PTX so that the renormalisation stays
+// predicated (no divergent branch), the 16-bit stream word is loaded straight
+// into a 32-bit register, and the address / shift-in / pointer arithmetic is
+// expressed as integer multiply-adds: the integer ALU pipe (64 lanes per clock
+// per SM) is this kernel's limiter, the FMA pipe that runs IMAD is idle.
+__device__ __forceinline__ uint32_t decode_step(LaneState &st, const LutView &lv) {
+  uint32_t ent;
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 a, q, f, b;\n\t"
+      ".reg .pred r;\n\t"
+      "and.b32 a, %1, %5;\n\t"
+      "mad.lo.u32 a, a, %6, %4;\n\t"         // slot * stride + lane's table base
+      "ld.shared.u32 %0, [a];\n\t"
+      "shr.u32 q, %1, %7;\n\t"
+      "shr.u32 f, %0, 20;\n\t"
+      "shr.u32 b, %0, 8;\n\t"
+      "and.b32 b, b, 4095;\n\t"
+      "mad.lo.u32 %1, f, q, b;\n\t"
+      "setp.lt.u32 r, %1, 65536;\n\t"
+      "@r mad.lo.u32 %1, %1, %9, %3;\n\t"    // x = x * 65536 + w
+      "@r mad.lo.u32 %2, %8, %10, %2;\n\t"   // p += 2
+      "@r ld.shared.u16 %3, [%2];\n\t"
+      "}"
+      : "=&r"(ent), "+r"(st.x), "+r"(st.p), "+r"(st.w)
+      : "r"(lv.base), "r"(lv.mask), "r"(lv.stride), "r"(lv.pb), "r"(lv.one), "r"(lv.k64k),
+        "r"(lv.two));
   return ent;
 }
 
@@ -133,17 +167,27 @@ __device__ __forceinline__ uint32_t merge_pair_s7(uint32_t ea, uint32_t eb, uint
   return (e & 0x7F807F80u) | (g & 0x807F807Fu);
 }
 
+// A lane's packed fractions for one block (8 elements = s+1 bytes), streaming
+// (evict-first) and volatile so that the loads stay where the code puts them:
+// several blocks ahead of their use.
 template <int S>
 __device__ __forceinline__ uint64_t load_frac(const uint8_t *p) {
   if (S == 7) {
-    const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(p));
-    return ((uint64_t)v.y << 32) | v.x;
+    uint32_t lo, hi;
+    asm volatile("ld.global.cs.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "l"(p));
+    return ((uint64_t)hi << 32) | lo;
   } else if (S == 3) {
-    return __ldcs(reinterpret_cast<const uint32_t *>(p));
+    uint32_t v;
+    asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
   } else if (S == 1) {
-    return __ldcs(reinterpret_cast<const uint16_t *>(p));
+    uint32_t v;
+    asm volatile("ld.global.cs.u16 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
   } else {
-    return __ldcs(p);
+    uint32_t v;
+    asm volatile("ld.global.cs.u8 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
   }
 }
 
@@ -175,6 +219,9 @@ struct DecodeArgs {
   uint32_t S;
   uint32_t n_units;
   uint32_t slot_bytes;
+  uint32_t lut_shift;   // log2 of the bytes per slot row for a 2^12-slot table (2..5)
+  uint32_t lut_bytes;   // 4096 << lut_shift
+  uint32_t ring_offset; // byte offset of the fraction rings in shared memory
   int canon;
   uint16_t *out_bf16;
   uint8_t *out_exp;
@@ -185,29 +232,64 @@ __device__ __forceinline__ void raise(uint32_t *status, uint32_t bits) {
   if (status) atomicOr(status, bits);
 }
 
-// Decode the `n_blocks` full blocks of one unit for this lane.
+// Exponent-only output: the 8 symbols of a lane's block as one 64-bit store.
+__device__ __forceinline__ void store_exp_block(const uint32_t (&ent)[8], uint8_t *exp) {
+  const uint32_t lo = __byte_perm(__byte_perm(ent[0], ent[1], 0x0040),
+                                  __byte_perm(ent[2], ent[3], 0x0040), 0x5410);
+  const uint32_t hi = __byte_perm(__byte_perm(ent[4], ent[5], 0x0040),
+                                  __byte_perm(ent[6], ent[7], 0x0040), 0x5410);
+  __stcs(reinterpret_cast<uint2 *>(exp), make_uint2(lo, hi));
+}
+
 template <int S, bool MERGE, bool CANON>
-__device__ __forceinline__ void decode_blocks(LaneState &st, uint32_t lut, uint32_t n_blocks,
+__device__ __forceinline__ void decode_one_block(LaneState &st, const LutView &lut, uint64_t fbits,
+                                                 uint16_t *out, uint8_t *exp) {
+  uint32_t ent[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) ent[t] = decode_step(st, lut);
+  if (MERGE) {
+    store_block<S, CANON>(ent, fbits, out);
+  } else {
+    store_exp_block(ent, exp);
+  }
+}
+
+// Decode the `n_blocks` full blocks of one unit for this lane.  The packed
+// fractions are fetched four blocks ahead of their use.
+template <int S, bool MERGE, bool CANON>
+__device__ __forceinline__ void decode_blocks(LaneState &st, const LutView &lut, uint32_t n_blocks,
                                               const uint8_t *frac_lane, uint16_t *out_lane,
                                               uint8_t *exp_lane) {
   constexpr uint32_t kFracStride = 32u * (S + 1);  // bytes of fractions per 256 elements
-  uint64_t fnext = 0;
-  if (MERGE && n_blocks) fnext = load_frac<S>(frac_lane);
-  for (uint32_t b = 0; b < n_blocks; ++b) {
-    const uint64_t fbits = fnext;
-    if (MERGE && b + 1 < n_blocks) fnext = load_frac<S>(frac_lane + (uint64_t)(b + 1) * kFracStride);
-    uint32_t ent[8];
+  constexpr int kAhead = 4;
+  uint64_t f[kAhead] = {0, 0, 0, 0};
+  if (MERGE) {
 #pragma unroll
-    for (int t = 0; t < 8; ++t) ent[t] = decode_step(st, lut);
-    if (MERGE) {
-      store_block<S, CANON>(ent, fbits, out_lane + (uint64_t)b * 256);
-    } else {
-      const uint32_t lo = __byte_perm(__byte_perm(ent[0], ent[1], 0x0040),
-                                      __byte_perm(ent[2], ent[3], 0x0040), 0x5410);
-      const uint32_t hi = __byte_perm(__byte_perm(ent[4], ent[5], 0x0040),
-                                      __byte_perm(ent[6], ent[7], 0x0040), 0x5410);
-      __stcs(reinterpret_cast<uint2 *>(exp_lane + (uint64_t)b * 256), make_uint2(lo, hi));
+    for (int k = 0; k < kAhead; ++k)
+      if ((uint32_t)k < n_blocks) f[k] = load_frac<S>(frac_lane + k * kFracStride);
+  }
+  uint32_t b = 0;
+  for (; b + kAhead <= n_blocks; b += kAhead) {
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) {
+      const uint64_t fbits = f[k];
+      if (MERGE && b + kAhead + k < n_blocks)
+        f[k] = load_frac<S>(frac_lane + (kAhead + k) * kFracStride);
+      decode_one_block<S, MERGE, CANON>(st, lut, fbits, MERGE ? out_lane + k * 256 : nullptr,
+                                        MERGE ? nullptr : exp_lane + k * 256);
     }
+    if (MERGE) {
+      frac_lane += kAhead * kFracStride;
+      out_lane += kAhead * 256;
+    } else {
+      exp_lane += kAhead * 256;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kAhead - 1; ++k) {
+    if (b + k < n_blocks)
+      decode_one_block<S, MERGE, CANON>(st, lut, f[k], MERGE ? out_lane + k * 256 : nullptr,
+                                        MERGE ? nullptr : exp_lane + k * 256);
   }
 }
 
@@ -226,48 +308,325 @@ __device__ __forceinline__ void emit_guarded(uint32_t sym, uint64_t e, const Dec
   }
 }
 
+// Asynchronous per-lane copy of one block's packed fractions (4 or 8 bytes)
+// from global to this lane's place in the warp's shared-memory ring.  Unlike a
+// register load this occupies no register scoreboard while in flight, so the
+// table and stream loads of the decode chain never wait behind it.
+template <int S>
+__device__ __forceinline__ void frac_async(uint32_t dst, const uint8_t *src) {
+  if (S == 7)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void frac_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void frac_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+template <int S>
+__device__ __forceinline__ uint64_t frac_from_ring(uint32_t addr) {
+  if (S == 7) {
+    uint32_t lo, hi;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(addr));
+    return ((uint64_t)hi << 32) | lo;
+  }
+  return lds_u32(addr);
+}
+
+constexpr uint32_t kRingSlots = 4;        // blocks of fractions in flight per unit + 1
+constexpr uint32_t kRingSlotBytes = 512;  // 2 units x 32 lanes x 8 bytes
+constexpr uint32_t kRingBytes = kRingSlots * kRingSlotBytes;
+
+// Two units interleaved in one lane: the two rANS chains are independent, so
+// one hides the shared-memory and multiply latency of the other.  For
+// precisions 3 and 7 the packed fractions travel through a small ring in shared
+// memory, fetched three blocks ahead with per-lane asynchronous copies; the
+// narrower fractions of precisions 0 and 1 (1 and 2 bytes per lane and block)
+// are loaded into registers.
+template <int S, bool MERGE, bool CANON>
+__device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb, const LutView &lut,
+                                                   uint32_t n_blocks, const uint8_t *frac_a,
+                                                   const uint8_t *frac_b, uint16_t *out_a,
+                                                   uint16_t *out_b, uint8_t *exp_a, uint8_t *exp_b,
+                                                   uint32_t ring) {
+  constexpr uint32_t kFracStride = 32u * (S + 1);
+  constexpr bool kAsync = MERGE && (S == 7 || S == 3);
+  constexpr int kAhead = 4;
+  uint64_t fa[kAhead] = {0, 0, 0, 0}, fb[kAhead] = {0, 0, 0, 0};
+  if (kAsync) {
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      if ((uint32_t)k < n_blocks) {
+        frac_async<S>(ring + k * kRingSlotBytes, frac_a + k * kFracStride);
+        frac_async<S>(ring + k * kRingSlotBytes + 256, frac_b + k * kFracStride);
+      }
+      frac_commit();
+    }
+  } else if (MERGE) {
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k)
+      if ((uint32_t)k < n_blocks) {
+        fa[k] = load_frac<S>(frac_a + k * kFracStride);
+        fb[k] = load_frac<S>(frac_b + k * kFracStride);
+      }
+  }
+  for (uint32_t b = 0; b < n_blocks; b += kAhead) {
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) {
+      if (b + k < n_blocks) {
+        uint64_t bits_a = fa[k], bits_b = fb[k];
+        if (kAsync) {
+          // block b+k+3 goes into the ring slot that block b+k-1 has left
+          if (b + k + 3 < n_blocks) {
+            frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes, frac_a + (k + 3) * kFracStride);
+            frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes + 256,
+                          frac_b + (k + 3) * kFracStride);
+          }
+          frac_commit();
+          frac_wait<3>();
+          bits_a = frac_from_ring<S>(ring + k * kRingSlotBytes);
+          bits_b = frac_from_ring<S>(ring + k * kRingSlotBytes + 256);
+        } else if (MERGE && b + kAhead + k < n_blocks) {
+          fa[k] = load_frac<S>(frac_a + (kAhead + k) * kFracStride);
+          fb[k] = load_frac<S>(frac_b + (kAhead + k) * kFracStride);
+        }
+        uint32_t ea[8], eb[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          ea[t] = decode_step(sa, lut);
+          eb[t] = decode_step(sb, lut);
+        }
+        if (MERGE) {
+          store_block<S, CANON>(ea, bits_a, out_a + k * 256);
+          store_block<S, CANON>(eb, bits_b, out_b + k * 256);
+        } else {
+          store_exp_block(ea, exp_a + k * 256);
+          store_exp_block(eb, exp_b + k * 256);
+        }
+      }
+    }
+    if (MERGE) {
+      frac_a += kAhead * kFracStride;
+      frac_b += kAhead * kFracStride;
+      out_a += kAhead * 256;
+      out_b += kAhead * 256;
+    } else {
+      exp_a += kAhead * 256;
+      exp_b += kAhead * 256;
+    }
+  }
+  if (kAsync) frac_wait<0>();
+}
+
+// What a warp knows about a unit it has planned.
+struct UnitPlan {
+  uint32_t kind;       // 0 = nothing to do, 1 = raw, 2 = coded
+  uint32_t head;       // byte offset of the unit inside its slot (coded)
+  uint32_t words;      // unit length in words
+  uint32_t copy_bytes; // size of the widened bulk copy (coded)
+  uint64_t byte0;      // byte offset of the unit inside the payload
+};
+constexpr uint32_t kUnitSkip = 0, kUnitRaw = 1, kUnitCoded = 2;
+
+// Look up unit u in the offset table and validate it against the buffer limits
+// the host passed (not against anything read from the container).  All lanes
+// return the same plan.
+__device__ __forceinline__ UnitPlan plan_unit(const DecodeArgs &a, uint32_t u, uint64_t pay_off,
+                                              uint64_t max_words, uint32_t lane) {
+  UnitPlan pl;
+  pl.kind = kUnitSkip;
+  pl.head = 0;
+  pl.words = 0;
+  pl.copy_bytes = 0;
+  pl.byte0 = 0;
+  if (u >= a.n_units) return pl;
+  const uint32_t *offsets = reinterpret_cast<const uint32_t *>(a.container + kOffsetsOffset);
+  const uint32_t off0 = __ldg(offsets + u), off1 = __ldg(offsets + u + 1);
+  const uint64_t w0 = off0 & ~kRawFlag, w1 = off1 & ~kRawFlag;
+  const uint64_t U = 32ull * a.S;
+  const uint64_t first = (uint64_t)u * U;
+  const uint64_t count = (a.n - first < U) ? (a.n - first) : U;
+  if (w1 < w0 || w1 > max_words) {
+    if (lane == 0) raise(a.status, NZ_STATUS_BAD_OFFSETS);
+    return pl;
+  }
+  pl.words = (uint32_t)(w1 - w0);
+  pl.byte0 = w0 * 2;
+  if (off0 & kRawFlag) {
+    if ((w1 - w0) * 2 < count) {
+      if (lane == 0) raise(a.status, NZ_STATUS_BAD_OFFSETS);
+      return pl;
+    }
+    pl.kind = kUnitRaw;
+    return pl;
+  }
+  const uint64_t b0 = w0 * 2, b1 = w1 * 2;
+  const uint64_t c0 = b0 & ~uint64_t(15), c1 = (b1 + 15) & ~uint64_t(15);
+  const uint32_t bytes = (uint32_t)(c1 - c0);
+  // the copy is widened to 16-byte boundaries: it must still end inside the buffer
+  if (w1 - w0 < 16 + 2 * 32 || bytes > a.slot_bytes ||
+      pay_off + c1 > (a.container_bytes & ~uint64_t(15))) {
+    if (lane == 0) raise(a.status, NZ_STATUS_BAD_OFFSETS);
+    return pl;
+  }
+  pl.head = (uint32_t)(b0 - c0);
+  pl.copy_bytes = bytes;
+  pl.kind = kUnitCoded;
+  return pl;
+}
+
+// Lane 0 arms the warp's mbarrier with the bytes of both copies and starts them.
+// Returns true when at least one copy was issued.
+__device__ __forceinline__ bool stage_units(const DecodeArgs &a, const UnitPlan &pa,
+                                            const UnitPlan &pb, uint64_t pay_off, uint32_t slot_a,
+                                            uint32_t slot_b, uint32_t bar, uint32_t lane) {
+  const uint32_t bytes = pa.copy_bytes + pb.copy_bytes;
+  if (bytes == 0) return false;
+  if (lane == 0) {
+    mbar_expect_tx(bar, bytes);
+    if (pa.copy_bytes)
+      bulk_g2s(slot_a, a.container + pay_off + (pa.byte0 & ~uint64_t(15)), pa.copy_bytes, bar);
+    if (pb.copy_bytes)
+      bulk_g2s(slot_b, a.container + pay_off + (pb.byte0 & ~uint64_t(15)), pb.copy_bytes, bar);
+  }
+  return true;
+}
+
+// Bounded wait for the warp's bulk copies.  Returns false when it ran out.
+__device__ __forceinline__ bool wait_staged(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kMaxWaitIters; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// Read the 32 lane lengths of a staged unit, check them against the unit
+// length and set up this lane's state.  Returns false (same for all lanes)
+// when the lengths are inconsistent.
+__device__ __forceinline__ bool open_unit(const UnitPlan &pl, uint32_t slot, uint32_t lenq,
+                                          uint32_t lane, LaneState &st) {
+  const uint32_t ub = slot + pl.head;            // shared address of the unit
+  const uint32_t q = lds_u8(ub + lane) * lenq;   // my stream length in words
+  uint32_t incl = q;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= (uint32_t)o) incl += v;
+  }
+  const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+  if (__any_sync(0xFFFFFFFFu, q < 2) || 16u + total != pl.words) return false;
+  const uint32_t sw = ub + 2 * (16 + incl - q);
+  st.x = lds_u16(sw) | (lds_u16(sw + 2) << 16);
+  st.p = sw + 4;
+  st.w = lds_u16(st.p);
+  return true;
+}
+
+// Decode one unit on its own (raw units, the tensor's last unit, odd counts).
 template <int S, bool MERGE>
-__global__ void __launch_bounds__(512)
+__device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPlan &pl, uint32_t u,
+                                              uint32_t slot, const LutView &lv, bool canon,
+                                              const uint8_t *payload, uint32_t lenq,
+                                              uint32_t lane) {
+  const uint64_t U = 32ull * a.S;
+  const uint64_t first = (uint64_t)u * U;
+  const uint64_t count = (a.n - first < U) ? (a.n - first) : U;
+  if (pl.kind == kUnitRaw) {
+    const uint8_t *src = payload + pl.byte0;
+    for (uint64_t i = lane; i < count; i += 32) emit_guarded<S, MERGE>(src[i], first + i, a);
+    return;
+  }
+  if (pl.kind != kUnitCoded) return;
+  LaneState st;
+  if (!open_unit(pl, slot, lenq, lane, st)) {
+    if (lane == 0) raise(a.status, NZ_STATUS_BAD_LANES);
+    return;
+  }
+  const uint32_t full_blocks = (uint32_t)(count / 256);
+  const uint64_t e_lane = first + lane * 8;
+  const uint8_t *frac_lane = MERGE ? a.frac + e_lane * (S + 1) / 8 : nullptr;
+  uint16_t *out_lane = MERGE ? a.out_bf16 + e_lane : nullptr;
+  uint8_t *exp_lane = MERGE ? nullptr : a.out_exp + e_lane;
+  if (canon)
+    decode_blocks<S, MERGE, true>(st, lv, full_blocks, frac_lane, out_lane, exp_lane);
+  else
+    decode_blocks<S, MERGE, false>(st, lv, full_blocks, frac_lane, out_lane, exp_lane);
+  if (count == U) {
+    if (__any_sync(0xFFFFFFFFu, st.x != kStateLow) && lane == 0)
+      raise(a.status, NZ_STATUS_BAD_STATE);
+  } else if (count & 255) {
+    // the partial block that ends the tensor
+    const uint64_t e0 = e_lane + (uint64_t)full_blocks * 256;
+    for (int t = 0; t < 8; ++t) {
+      const uint32_t ent = decode_step(st, lv);
+      emit_guarded<S, MERGE>(ent & 0xFFu, e0 + t, a);
+    }
+  }
+}
+
+template <int S, bool MERGE>
+__global__ void __launch_bounds__(640, 1)
 decode_kernel(const DecodeArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t n_warps = blockDim.x >> 5;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint32_t *lut_p = reinterpret_cast<uint32_t *>(smem);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kLutBytes);
-  uint16_t *cum_sh = reinterpret_cast<uint16_t *>(smem + kLutBytes + 8 * 32);  // 257 entries
-  uint32_t *flag_sh = reinterpret_cast<uint32_t *>(smem + kLutBytes + 8 * 32 + 520);
-  uint8_t *slots = smem + kLutBytes + 1024;
-  const uint32_t lut = smem_u32(lut_p);
+  const uint32_t lut_bytes = 4096u << a.lut_shift;           // 2^pb slots would need 4 << shift each
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + a.lut_bytes);
+  uint16_t *cum_sh = reinterpret_cast<uint16_t *>(smem + a.lut_bytes + 8 * 32);  // 257 entries
+  uint32_t *flag_sh = reinterpret_cast<uint32_t *>(smem + a.lut_bytes + 8 * 32 + 520);
+  uint32_t *pb_sh = flag_sh + 1;
+  uint8_t *slots = smem + a.lut_bytes + 1024;
+  (void)lut_bytes;
+  const uint32_t bar = smem_u32(&bars[warp]);
+  const uint32_t slot_a = smem_u32(slots + (uint64_t)(2 * warp) * a.slot_bytes);
+  const uint32_t slot_b = slot_a + a.slot_bytes;
+  // per-warp ring for the packed fractions, behind all slots and their guard band
+  const uint32_t ring = smem_u32(smem) + a.ring_offset + warp * kRingBytes + lane * (S == 7 ? 8 : 4);
 
-  // ---- header + table validation, decode-table build
+  // Each warp owns one mbarrier; its lane 0 initialises it and is the only
+  // thread that ever arms it.
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (threadIdx.x == 0) *flag_sh = 0;
+  __syncwarp();
+  // Programmatic dependent launch: let the next kernel of the stream start its
+  // own launch now, and do not touch global memory before the previous kernel
+  // has completed.  Both are no-ops for an ordinary launch.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- start fetching the first pair of units, build the decode table meanwhile
   const Header *h = reinterpret_cast<const Header *>(a.container);
   const uint64_t pay_off = payload_offset(a.n_units);
-  if (threadIdx.x == 0) {
-    uint32_t bad = 0;
-    if (h->magic != kMagic || h->version != 1 || h->n_symbols != a.n || h->lane_symbols != a.S ||
-        h->n_units != a.n_units || h->len_quantum != len_quantum(a.S) ||
-        h->payload_offset != pay_off || pay_off + h->payload_words * 2 > a.container_bytes ||
-        h->payload_words >= kRawFlag)
-      bad = NZ_STATUS_BAD_HEADER;
-    *flag_sh = bad;
-  }
-  if (threadIdx.x < n_warps) mbar_init(smem_u32(&bars[threadIdx.x]), 1);
+  const uint64_t max_words = (a.container_bytes - pay_off) / 2;   // host checked bytes >= pay_off
+  const uint32_t stride = 2 * gridDim.x * n_warps;
+  uint32_t u = 2 * (blockIdx.x * n_warps + warp);
+  uint32_t parity = 0;
+  UnitPlan pa = plan_unit(a, u, pay_off, max_words, lane);
+  UnitPlan pb2 = plan_unit(a, u + 1, pay_off, max_words, lane);
+  bool staged = stage_units(a, pa, pb2, pay_off, slot_a, slot_b, bar, lane);
+
   const uint16_t *freq_g = reinterpret_cast<const uint16_t *>(a.container + kFreqOffset);
   if (warp == 0) {
     // inclusive scan of the 256 frequencies, 8 per lane
-    uint32_t f[8], s = 0;
+    const uint4 fv = __ldg(reinterpret_cast<const uint4 *>(freq_g) + lane);
+    const uint32_t fw[4] = {fv.x, fv.y, fv.z, fv.w};
+    uint32_t f[8], sum = 0;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      f[k] = freq_g[lane * 8 + k];
-      s += f[k];
+      f[k] = (fw[k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
+      sum += f[k];
     }
-    uint32_t incl = s;
+    uint32_t incl = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
       if (lane >= (uint32_t)o) incl += v;
     }
-    uint32_t run = incl - s;
+    uint32_t run = incl - sum;
     if (lane == 0) cum_sh[0] = 0;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -275,163 +634,159 @@ decode_kernel(const DecodeArgs a) {
       cum_sh[lane * 8 + k + 1] = (uint16_t)(run > 0xFFFF ? 0xFFFF : run);
     }
   }
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (threadIdx.x == (n_warps > 1 ? 32u : 0u)) {
+    if (h->magic != kMagic || h->version != 1 || h->n_symbols != a.n || h->lane_symbols != a.S ||
+        h->n_units != a.n_units || h->len_quantum != len_quantum(a.S) ||
+        h->payload_offset != pay_off || h->payload_words > max_words ||
+        h->prob_bits < kMinProbBits || h->prob_bits > kMaxProbBits)
+      atomicOr(flag_sh, NZ_STATUS_BAD_HEADER);
+    *pb_sh = h->prob_bits;
+  }
   __syncthreads();
-  if (threadIdx.x == 0 && cum_sh[256] != kProbScale) *flag_sh |= NZ_STATUS_BAD_HEADER;
-  __syncthreads();
-  if (*flag_sh) {
-    if (threadIdx.x == 0 && blockIdx.x == 0) raise(a.status, *flag_sh);
+  // nothing writes the flag or the table after this barrier, so every thread
+  // computes the same verdict
+  const uint32_t pb = *pb_sh;
+  uint32_t bad = *flag_sh;
+  if (pb < kMinProbBits || pb > kMaxProbBits || cum_sh[256] != (1u << (pb & 15)))
+    bad |= NZ_STATUS_BAD_HEADER;
+  if (bad) {
+    // copies may be in flight into this warp's slots: let them land before leaving
+    if (staged) wait_staged(bar, parity);
+    if (threadIdx.x == 0 && blockIdx.x == 0) raise(a.status, bad);
     return;
   }
-  for (uint32_t slot = threadIdx.x; slot < kProbScale; slot += blockDim.x) {
-    // largest symbol whose cumulative start is <= slot
-    uint32_t lo = 0, hi = 256;
-#pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const uint32_t mid = (lo + hi) >> 1;
-      if (cum_sh[mid] <= slot) lo = mid; else hi = mid;
-    }
-    const uint32_t start = cum_sh[lo];
-    const uint32_t fr = cum_sh[lo + 1] - start;
-    lut_p[slot] = lo | (fr << 8) | ((slot - start) << 20);
+  // Decode table: warps take symbols in turn; a symbol's slot range is a run of
+  // rows (all copies of a slot hold the same word).
+  // The host sized the table for 2^12 slots x 2^(lut_shift-2) copies; with fewer
+  // probability bits the spare room becomes more copies.
+  LutView lv;
+  lv.pb = pb;
+  lv.mask = (1u << pb) - 1u;
+  uint32_t row_shift = a.lut_shift + (kMaxProbBits - pb);   // log2 of the bytes per slot row
+  if (row_shift > 7) row_shift = 7;                         // 32 copies are enough
+  lv.stride = 1u << row_shift;
+  lv.base = smem_u32(smem) + ((lane << 2) & (lv.stride - 1u));
+  lv.one = a.S ? 1u : 0u;
+  lv.two = lv.one << 1;
+  lv.k64k = lv.one << 16;
+  uint32_t *lut_w = reinterpret_cast<uint32_t *>(smem);
+  const uint32_t wsh = row_shift - 2;                     // log2 of the words per slot row
+  for (uint32_t sym = warp; sym < 256; sym += n_warps) {
+    const uint32_t start = cum_sh[sym], end = cum_sh[sym + 1];
+    const uint32_t hi = (end - start) << 20;
+    const uint32_t words = (end - start) << wsh;
+    uint32_t *dst = lut_w + (start << wsh);
+    for (uint32_t k = lane; k < words; k += 32) dst[k] = sym | ((k >> wsh) << 8) | hi;
   }
-  const bool canon = MERGE && a.canon && (freq_g[255] != 0);
+  const bool canon = MERGE && a.canon && (cum_sh[256] != cum_sh[255]);
   __syncthreads();
 
-  // ---- units
-  const uint32_t *offsets = reinterpret_cast<const uint32_t *>(a.container + kOffsetsOffset);
+  // ---- units, two at a time
   const uint8_t *payload = a.container + pay_off;
-  const uint64_t payload_words = h->payload_words;
   const uint32_t lenq = len_quantum(a.S);
   const uint64_t U = 32ull * a.S;
-  const uint32_t bar = smem_u32(&bars[warp]);
-  uint8_t *slot_p = slots + (uint64_t)warp * a.slot_bytes;
-  const uint32_t slot = smem_u32(slot_p);
-  uint32_t parity = 0;
 
-  for (uint32_t u = blockIdx.x * n_warps + warp; u < a.n_units; u += gridDim.x * n_warps) {
-    const uint32_t off0 = __ldg(offsets + u), off1 = __ldg(offsets + u + 1);
-    const uint64_t w0 = off0 & ~kRawFlag, w1 = off1 & ~kRawFlag;
-    const uint64_t first = (uint64_t)u * U;
-    const uint64_t count = (a.n - first < U) ? (a.n - first) : U;
-    if (w1 < w0 || w1 > payload_words) {
-      if (lane == 0) raise(a.status, NZ_STATUS_BAD_OFFSETS);
-      continue;
-    }
-    if (off0 & kRawFlag) {
-      if ((w1 - w0) * 2 < count) {
-        if (lane == 0) raise(a.status, NZ_STATUS_BAD_OFFSETS);
-        continue;
+  for (; u < a.n_units; u += stride) {
+    if (staged) {
+      const bool arrived = wait_staged(bar, parity);
+      parity ^= 1;
+      if (!__all_sync(0xFFFFFFFFu, arrived)) {
+        // The copies may still be in flight, so the slots cannot be reused: flag it,
+        // give them one more bounded chance to land and leave.
+        if (lane == 0) raise(a.status, NZ_STATUS_TIMEOUT);
+        if (!arrived) wait_staged(bar, parity ^ 1);
+        return;
       }
-      const uint8_t *src = payload + w0 * 2;
-      for (uint64_t i = lane; i < count; i += 32) emit_guarded<S, MERGE>(src[i], first + i, a);
-      continue;
     }
-    const uint64_t b0 = w0 * 2, b1 = w1 * 2;
-    const uint64_t c0 = b0 & ~uint64_t(15), c1 = (b1 + 15) & ~uint64_t(15);
-    const uint32_t bytes = (uint32_t)(c1 - c0);
-    if (w1 - w0 < 16 + 2 * 32 || bytes > a.slot_bytes) {
-      if (lane == 0) raise(a.status, NZ_STATUS_BAD_OFFSETS);
-      continue;
+    const bool full_pair = pa.kind == kUnitCoded && pb2.kind == kUnitCoded &&
+                           (uint64_t)(u + 2) * U <= a.n;
+    bool done = false;
+    if (full_pair) {
+      LaneState sa, sb;
+      const bool oka = open_unit(pa, slot_a, lenq, lane, sa);
+      const bool okb = open_unit(pb2, slot_b, lenq, lane, sb);
+      if (oka && okb) {
+        done = true;
+        const uint64_t ea = (uint64_t)u * U + lane * 8, eb = ea + U;
+        const uint8_t *fa = MERGE ? a.frac + ea * (S + 1) / 8 : nullptr;
+        const uint8_t *fb = MERGE ? a.frac + eb * (S + 1) / 8 : nullptr;
+        uint16_t *oa = MERGE ? a.out_bf16 + ea : nullptr, *ob = MERGE ? a.out_bf16 + eb : nullptr;
+        uint8_t *xa = MERGE ? nullptr : a.out_exp + ea, *xb = MERGE ? nullptr : a.out_exp + eb;
+        if (canon)
+          decode_blocks_dual<S, MERGE, true>(sa, sb, lv, a.S / 8, fa, fb, oa, ob, xa, xb, ring);
+        else
+          decode_blocks_dual<S, MERGE, false>(sa, sb, lv, a.S / 8, fa, fb, oa, ob, xa, xb, ring);
+        if (__any_sync(0xFFFFFFFFu, sa.x != kStateLow || sb.x != kStateLow) && lane == 0)
+          raise(a.status, NZ_STATUS_BAD_STATE);
+      }
     }
-    // stage the unit: all lanes are done with the slot's previous contents
+    if (!done) {
+      decode_single<S, MERGE>(a, pa, u, slot_a, lv, canon, payload, lenq, lane);
+      decode_single<S, MERGE>(a, pb2, u + 1, slot_b, lv, canon, payload, lenq, lane);
+    }
+    // every lane is done reading the slots: fetch this warp's next pair
     __syncwarp();
-    if (lane == 0) {
-      mbar_expect_tx(bar, bytes);
-      bulk_g2s(slot, payload + c0, bytes, bar);
-    }
-    bool arrived = false;
-    for (uint32_t it = 0; it < kMaxWaitIters; ++it) {
-      if (mbar_try_wait(bar, parity)) {
-        arrived = true;
-        break;
-      }
-    }
-    parity ^= 1;
-    if (!__all_sync(0xFFFFFFFFu, arrived)) {
-      // Give the copy one more bounded chance to land, then give up on the
-      // whole kernel: the slot cannot be reused while a copy may be in flight.
-      if (!arrived)
-        for (uint32_t it = 0; it < kMaxWaitIters && !mbar_try_wait(bar, parity ^ 1); ++it) {
-        }
-      if (lane == 0) raise(a.status, NZ_STATUS_TIMEOUT);
-      return;
-    }
-    const uint32_t ub = slot + (uint32_t)(b0 - c0);  // shared address of the unit
-    const uint32_t q = lds_u8(ub + lane) * lenq;     // my stream length in words
-    uint32_t incl = q;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-      if (lane >= (uint32_t)o) incl += v;
-    }
-    const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
-    if (__any_sync(0xFFFFFFFFu, q < 2) || 16ull + total != w1 - w0) {
-      if (lane == 0) raise(a.status, NZ_STATUS_BAD_LANES);
-      continue;
-    }
-    LaneState st;
-    const uint32_t sw = ub + 2 * (16 + incl - q);
-    st.x = lds_u16(sw) | (lds_u16(sw + 2) << 16);
-    st.p = sw + 4;
-    st.w = lds_u16(st.p);
-
-    const uint32_t full_blocks = (uint32_t)(count / 256);
-    const uint64_t e_lane = first + lane * 8;
-    const uint8_t *frac_lane = MERGE ? a.frac + e_lane * (S + 1) / 8 : nullptr;
-    uint16_t *out_lane = MERGE ? a.out_bf16 + e_lane : nullptr;
-    uint8_t *exp_lane = MERGE ? nullptr : a.out_exp + e_lane;
-    if (canon)
-      decode_blocks<S, MERGE, true>(st, lut, full_blocks, frac_lane, out_lane, exp_lane);
-    else
-      decode_blocks<S, MERGE, false>(st, lut, full_blocks, frac_lane, out_lane, exp_lane);
-    if (count == U) {
-      if (__any_sync(0xFFFFFFFFu, st.x != kStateLow) && lane == 0)
-        raise(a.status, NZ_STATUS_BAD_STATE);
-    } else if (count & 255) {
-      // the partial block that ends the tensor
-      const uint64_t e0 = e_lane + (uint64_t)full_blocks * 256;
-      for (int t = 0; t < 8; ++t) {
-        const uint32_t ent = decode_step(st, lut);
-        emit_guarded<S, MERGE>(ent & 0xFFu, e0 + t, a);
-      }
-    }
+    pa = plan_unit(a, u + stride, pay_off, max_words, lane);
+    pb2 = plan_unit(a, u + stride + 1, pay_off, max_words, lane);
+    staged = stage_units(a, pa, pb2, pay_off, slot_a, slot_b, bar, lane);
   }
 }
 
 // ------------------------------------------------------------------- host
 struct LaunchGeom {
-  uint32_t warps, slot_bytes, smem_bytes, blocks;
+  uint32_t warps, slot_bytes, smem_bytes, blocks, lut_shift, lut_bytes, ring_offset;
 };
 
+// Grid geometry.  Every warp decodes whole units, two at a time, so the kernel
+// is only as fast as the SM with the most units: one CTA per SM, the same
+// number of warps in every CTA and the same number of unit pairs (within one)
+// for every warp.  The decode table gets what shared memory the slots leave
+// (more copies = fewer bank conflicts), at most 32 copies of 2^10 slots.
 static int decode_geometry(uint64_t n, uint32_t S, uint32_t max_unit_words, LaunchGeom &g) {
   const uint64_t U = 32ull * S;
   uint64_t unit_bytes = max_unit_words ? (uint64_t)max_unit_words * 2 : U;
   if (unit_bytes > U) unit_bytes = U;
   if (unit_bytes < 160) unit_bytes = 160;
-  g.slot_bytes = (uint32_t)((unit_bytes + 32 + 127) & ~uint64_t(127));
+  g.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
   const uint32_t guard = ((S + 8) * 2 + 127) & ~127u;
-  const uint32_t budget = 200 * 1024;
-  uint32_t warps = 16;
-  while (warps > 1 && kLutBytes + 1024 + warps * g.slot_bytes + guard > budget) warps >>= 1;
-  g.warps = warps;
-  g.smem_bytes = kLutBytes + 1024 + warps * g.slot_bytes + guard;
-  if (g.smem_bytes > 227 * 1024) {
-    set_error("decode: a unit of %u symbols does not fit in shared memory", (unsigned)U);
+  const uint32_t sm_smem = 227u * 1024u;
+  const uint32_t kMaxWarps = 20;
+  const uint64_t nu = unit_count(n, S);
+  const uint32_t sms = (uint32_t)sm_count();
+  const uint64_t pairs_per_sm = ((nu + 1) / 2 + sms - 1) / sms;
+  // smallest table first (2^12 slots, one copy = 16 KB) to find how many warps fit
+  auto cap_for = [&](uint32_t lut_bytes) -> uint32_t {
+    const uint32_t fixed = lut_bytes + 1024 + guard;
+    if (fixed + 2 * g.slot_bytes + kRingBytes > sm_smem) return 0;
+    uint32_t c = (sm_smem - fixed) / (2 * g.slot_bytes + kRingBytes);
+    return c > kMaxWarps ? kMaxWarps : c;
+  };
+  uint32_t cap = cap_for(16 * 1024);
+  if (cap == 0) {
+    set_error("decode: two units of %u symbols do not fit in shared memory", (unsigned)U);
     return NZ_E_ARG;
   }
-  const uint64_t nu = unit_count(n, S);
-  uint64_t blocks = (nu + warps - 1) / warps;
-  // resident CTAs per SM by shared memory and by threads (2048 per SM)
-  uint32_t per_sm = (227u * 1024u) / (g.smem_bytes + 1024);
-  const uint32_t by_threads = 2048 / (warps * 32);
-  if (per_sm > by_threads) per_sm = by_threads;
-  if (per_sm < 1) per_sm = 1;
-  const uint64_t cap = (uint64_t)sm_count() * per_sm;
-  if (blocks > cap) blocks = cap;
+  const uint64_t rounds = (pairs_per_sm + cap - 1) / cap;
+  uint32_t warps = (uint32_t)((pairs_per_sm + rounds - 1) / (rounds ? rounds : 1));
+  if (warps < 1) warps = 1;
+  // largest table that still leaves room for these warps
+  g.lut_shift = 2;
+  for (uint32_t sh = 5; sh > 2; --sh) {        // 2^12 slots x 2^(sh-2) copies
+    const uint32_t lut_bytes = 4096u << sh;
+    if (lut_bytes + 1024 + guard + warps * (2 * g.slot_bytes + kRingBytes) <= sm_smem) {
+      g.lut_shift = sh;
+      break;
+    }
+  }
+  g.lut_bytes = 4096u << g.lut_shift;
+  uint64_t blocks = sms;
+  const uint64_t needed = ((nu + 1) / 2 + warps - 1) / warps;     // no CTA without a unit
+  if (blocks > needed) blocks = needed;
   if (blocks == 0) blocks = 1;
+  g.warps = warps;
   g.blocks = (uint32_t)blocks;
+  g.ring_offset = g.lut_bytes + 1024 + guard + warps * 2 * g.slot_bytes;
+  g.smem_bytes = g.ring_offset + warps * kRingBytes;
   return NZ_OK;
 }
 
@@ -440,8 +795,20 @@ static int launch_decode(const DecodeArgs &a, const LaunchGeom &g, cudaStream_t 
   auto kern = decode_kernel<S, MERGE>;
   NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)g.smem_bytes));
-  kern<<<g.blocks, g.warps * 32, g.smem_bytes, st>>>(a);
-  NZ_LAUNCH_CHECK("decode_kernel");
+  // Programmatic stream serialisation: this launch may begin while the previous
+  // kernel of the stream drains; the kernel itself waits (griddepcontrol.wait)
+  // before it reads or writes global memory, so ordering is preserved.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(g.blocks);
+  cfg.blockDim = dim3(g.warps * 32);
+  cfg.dynamicSmemBytes = g.smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  NZ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a));
   return NZ_OK;
 }
 
@@ -466,6 +833,9 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   a.S = S;
   a.n_units = (uint32_t)nu;
   a.slot_bytes = g.slot_bytes;
+  a.lut_shift = g.lut_shift;
+  a.lut_bytes = g.lut_bytes;
+  a.ring_offset = g.ring_offset;
   a.canon = canon;
   a.out_bf16 = (uint16_t *)out_bf16;
   a.out_exp = (uint8_t *)out_exp;

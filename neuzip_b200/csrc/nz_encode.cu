@@ -12,7 +12,7 @@
 //   [0, 1024)            u32 hist[256]
 //   [1024, 1536)         u16 freq[256]
 //   [1536, 2560)         u32 enc_tab[256]   (freq | cum << 16)
-//   [2560, 2576)         u32 misc[4]        (pad symbol, max unit words, raw units, -)
+//   [2560, 2576)         u32 misc[4]        (pad symbol, probability bits, -, -)
 //   [4096, 4096+4*(nu+1))           u32 unit_words[nu]  (bit 31 = raw)
 //   [.., + 64*nu)                   u16 lane_len[nu][32]   (words; 0 = unit raw)
 //   [.., + nu*32*cap*2)             u16 lane_words[nu][32][cap]   cap = lane_cap_words(S)
@@ -86,29 +86,37 @@ histogram_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t *__restri
 }
 
 // ------------------------------------------------------------ normalisation
-// Integer-only, identical to nzo_normalize of the specification.  The counts
-// are 32-bit here (a tensor of 2^32 or more elements is rejected by the host
-// code), the products 64-bit.
+// Integer-only, identical to nzo_choose_prob_bits + nzo_normalize of the
+// specification.  The counts are 32-bit here (a tensor of 2^32 or more
+// elements is rejected by the host code), the products 64-bit.
 __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__restrict__ freq,
                                  uint32_t *__restrict__ enc_tab, uint32_t *__restrict__ misc,
                                  uint16_t *__restrict__ container_freq) {
   __shared__ int32_t f[256];
   __shared__ uint64_t total_sh;
+  __shared__ uint32_t pb_sh;
   const int t = threadIdx.x;  // 256 threads
   if (t == 0) {
     uint64_t total = 0;
-    for (int i = 0; i < 256; ++i) total += hist[i];
+    uint32_t distinct = 0;
+    for (int i = 0; i < 256; ++i) {
+      total += hist[i];
+      distinct += hist[i] != 0;
+    }
     total_sh = total;
+    pb_sh = distinct <= 32 ? 10u : (distinct <= 64 ? 11u : 12u);
   }
   __syncthreads();
   const uint64_t total = total_sh;
+  const uint32_t pb = pb_sh;
+  const uint32_t M = 1u << pb;
   {
     const uint64_t h = hist[t];
     int32_t v = 0;
     if (total == 0) {
-      v = (t == 0) ? (int32_t)kProbScale : 0;
+      v = (t == 0) ? (int32_t)M : 0;
     } else if (h) {
-      const uint64_t q = (h * kProbScale + total / 2) / total;
+      const uint64_t q = (h * M + total / 2) / total;
       v = q ? (int32_t)q : 1;
     }
     f[t] = v;
@@ -117,7 +125,7 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
   if (t == 0) {
     int32_t sum = 0;
     for (int i = 0; i < 256; ++i) sum += f[i];
-    int32_t d = (int32_t)kProbScale - sum;
+    int32_t d = (int32_t)M - sum;
     while (d != 0) {
       int top = 0;
       for (int i = 1; i < 256; ++i)
@@ -133,8 +141,8 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
       }
     }
     for (int i = 0; i < 256; ++i) {
-      if (f[i] == (int32_t)kProbScale) {
-        f[i] = kProbScale - 1;
+      if (f[i] == (int32_t)M) {
+        f[i] = (int32_t)M - 1;
         f[(i + 1) & 255] = 1;
         break;
       }
@@ -146,8 +154,7 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
       cum += f[i];
     }
     misc[0] = pad;
-    misc[1] = 0;  // max coded unit words
-    misc[2] = 0;  // raw units
+    misc[1] = pb;
   }
   __syncthreads();
   freq[t] = (uint16_t)f[t];
@@ -171,6 +178,7 @@ encode_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t 
   for (int i = threadIdx.x; i < 256; i += blockDim.x) tab[i] = enc_tab_g[i];
   __syncthreads();
   const uint32_t pad = misc[0];
+  const uint32_t pb = misc[1];
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t lenq = len_quantum(S);
   const uint32_t cap = lane_cap_words(S);
@@ -202,14 +210,14 @@ encode_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t 
         const uint32_t s = ((t < 4 ? lo : hi) >> (8 * (t & 3))) & 0xFFu;
         const uint32_t ent = tab[s];
         const uint32_t fr = ent & 0xFFFFu, cum = ent >> 16;
-        if (x >= (fr << (32 - kProbBits))) {
+        if (x >= (fr << (32 - pb))) {
           // words beyond the capacity are dropped; the unit is then stored raw
           if (emitted + 2 < cap) mine[cap - 1 - emitted] = (uint16_t)(x & 0xFFFFu);
           else overflow = true;
           ++emitted;
           x >>= 16;
         }
-        x = ((x / fr) << kProbBits) + (x % fr) + cum;
+        x = ((x / fr) << pb) + (x % fr) + cum;
       }
     }
     uint32_t words = emitted + 2;
@@ -273,7 +281,7 @@ scan_kernel(const uint32_t *__restrict__ unit_words, uint32_t n_units, uint64_t 
     h.lane_symbols = S;
     h.len_quantum = len_quantum(S);
     h.n_units = n_units;
-    h.pad_symbol = misc[0];
+    h.prob_bits = misc[1];
     h.payload_offset = pay_off;
     h.payload_words = run;
     h.total_bytes = align16(pay_off + run * 2);

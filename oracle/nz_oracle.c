@@ -28,8 +28,8 @@
  * Container layout ("NZR1"), all little-endian:
  *
  *   [0,64)      header   (struct nzo_header)
- *   [64,576)    freq     u16[256], sum = 4096, every present symbol >= 1,
- *                        no entry above 4095
+ *   [64,576)    freq     u16[256], sum = M = 2^prob_bits, every present symbol
+ *                        >= 1, no entry above M-1
  *   [576, ...)  offsets  u32[n_units+1]; entry u = word offset (16-bit words)
  *                        of unit u inside the payload, bit 31 set when the
  *                        unit is stored raw; last entry = total payload words
@@ -51,20 +51,25 @@
  * (S/2 words is the lane's share of the raw unit) or when the coded form is
  * not smaller than the raw form.
  *
- * rANS: 32-bit state x in [2^16, 2^32), 12-bit probabilities, 16-bit
- * renormalisation.  Decoding one symbol:
- *     slot = x & 4095; s = symbol whose [cum, cum+freq) holds slot;
- *     x = freq[s]*(x >> 12) + slot - cum[s];
+ * rANS: 32-bit state x in [2^16, 2^32), prob_bits-bit probabilities (10, 11 or
+ * 12), 16-bit renormalisation.  Decoding one symbol, with M = 2^prob_bits:
+ *     slot = x & (M-1); s = symbol whose [cum, cum+freq) holds slot;
+ *     x = freq[s]*(x >> prob_bits) + slot - cum[s];
  *     if (x < 2^16) x = (x << 16) | next_word;
  * The encoder runs the lane's symbols backwards from state 2^16.
+ *
+ * prob_bits is chosen from the number of distinct symbols d of the tensor:
+ * 10 for d <= 32, 11 for d <= 64, else 12.  Exponent streams of network
+ * weights have about 30 distinct values, and a 1024-slot decode table can be
+ * replicated across all 32 shared-memory banks of the GPU decoder.
  */
 #include <stdint.h>
 #include <stddef.h>
 #include <stdlib.h>
 #include <string.h>
 
-#define NZO_PROB_BITS 12
-#define NZO_PROB_SCALE (1u << NZO_PROB_BITS)
+#define NZO_MAX_PROB_BITS 12
+#define NZO_MAX_PROB_SCALE (1u << NZO_MAX_PROB_BITS)
 #define NZO_STATE_LOW (1u << 16)
 #define NZO_MAGIC 0x31525A4Eu /* "NZR1" */
 
@@ -75,7 +80,7 @@ typedef struct nzo_header {
   uint32_t lane_symbols;   /* S */
   uint32_t len_quantum;    /* lenq: words per length-byte step */
   uint32_t n_units;
-  uint32_t pad_symbol;     /* symbol used for the tail of the last unit */
+  uint32_t prob_bits;      /* 10, 11 or 12 */
   uint64_t payload_offset; /* byte offset of the payload in the container */
   uint64_t payload_words;  /* payload length in 16-bit words */
   uint64_t total_bytes;    /* container length, multiple of 16 */
@@ -172,34 +177,44 @@ void nzo_histogram(const uint8_t *sym, size_t n, uint64_t *hist) {
   for (size_t i = 0; i < n; ++i) hist[sym[i]]++;
 }
 
-/* Integer-only normalisation of a histogram to 12-bit frequencies.  Pure
- * integer arithmetic so that the CUDA encoder can reproduce it bit for bit.
- *   1. f = round(h * 4096 / T), at least 1 for every present symbol;
- *   2. the difference to 4096 is taken from / given to the currently largest
+/* Probability resolution for a histogram: 10 bits up to 32 distinct symbols,
+ * 11 up to 64, else 12. */
+uint32_t nzo_choose_prob_bits(const uint64_t *hist) {
+  uint32_t d = 0;
+  for (int i = 0; i < 256; ++i) d += hist[i] != 0;
+  return d <= 32 ? 10u : (d <= 64 ? 11u : 12u);
+}
+
+/* Integer-only normalisation of a histogram to prob_bits-bit frequencies
+ * (M = 2^prob_bits).  Pure integer arithmetic so that the CUDA encoder can
+ * reproduce it bit for bit.
+ *   1. f = round(h * M / T), at least 1 for every present symbol;
+ *   2. the difference to M is taken from / given to the currently largest
  *      entry (lowest index on ties), never pushing an entry below 1;
- *   3. an alphabet of one symbol gets 4095 and its successor (mod 256) 1, so
- *      that no frequency needs 13 bits.
- * An empty histogram yields freq[0] = 4095, freq[1] = 1.
- * Returns the most frequent symbol (the pad symbol). */
-uint32_t nzo_normalize(const uint64_t *hist, uint16_t *freq) {
+ *   3. an alphabet of one symbol gets M-1 and its successor (mod 256) 1, so
+ *      that no frequency needs prob_bits+1 bits.
+ * An empty histogram yields freq[0] = M-1, freq[1] = 1.
+ * Returns the most frequent symbol of the histogram. */
+uint32_t nzo_normalize(const uint64_t *hist, uint32_t prob_bits, uint16_t *freq) {
+  const uint32_t M = 1u << prob_bits;
   uint64_t total = 0;
   for (int i = 0; i < 256; ++i) total += hist[i];
   int32_t f[256];
   memset(f, 0, sizeof(f));
   uint32_t best = 0;
   if (total == 0) {
-    f[0] = NZO_PROB_SCALE;
+    f[0] = (int32_t)M;
   } else {
     for (int i = 0; i < 256; ++i) {
       if (hist[i] > hist[best]) best = (uint32_t)i;
       if (hist[i] == 0) continue;
-      uint64_t q = (hist[i] * NZO_PROB_SCALE + total / 2) / total;
+      uint64_t q = (hist[i] * M + total / 2) / total;
       f[i] = q ? (int32_t)q : 1;
     }
   }
   int32_t sum = 0;
   for (int i = 0; i < 256; ++i) sum += f[i];
-  int32_t d = (int32_t)NZO_PROB_SCALE - sum;
+  int32_t d = (int32_t)M - sum;
   while (d != 0) {
     int top = 0;
     for (int i = 1; i < 256; ++i)
@@ -214,8 +229,8 @@ uint32_t nzo_normalize(const uint64_t *hist, uint16_t *freq) {
     }
   }
   for (int i = 0; i < 256; ++i) {
-    if (f[i] == (int32_t)NZO_PROB_SCALE) {
-      f[i] = NZO_PROB_SCALE - 1;
+    if (f[i] == (int32_t)M) {
+      f[i] = (int32_t)M - 1;
       f[(i + 1) & 255] = 1;
       break;
     }
@@ -229,7 +244,7 @@ uint32_t nzo_normalize(const uint64_t *hist, uint16_t *freq) {
 static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
 
 uint32_t nzo_len_quantum(uint32_t lane_symbols) {
-  return (lane_symbols + 511) / 512;
+  return (lane_symbols + 767) / 768;
 }
 
 /* Upper bound of the container size for n symbols. */
@@ -250,7 +265,7 @@ static inline uint64_t unit_element(uint64_t unit, uint32_t S, uint32_t lane,
  * capacity would be exceeded. */
 static uint32_t encode_lane(const uint8_t *sym, uint64_t n, uint64_t unit,
                             uint32_t S, uint32_t lane, uint32_t pad,
-                            const uint16_t *freq, const uint16_t *cum,
+                            uint32_t pb, const uint16_t *freq, const uint16_t *cum,
                             uint16_t *words, uint32_t cap, uint16_t *scratch) {
   uint32_t x = NZO_STATE_LOW;
   uint32_t emitted = 0; /* scratch[0..emitted) in emission order */
@@ -258,12 +273,12 @@ static uint32_t encode_lane(const uint8_t *sym, uint64_t n, uint64_t unit,
     uint64_t e = unit_element(unit, S, lane, (uint32_t)i);
     uint32_t s = (e < n) ? sym[e] : pad;
     uint32_t fr = freq[s];
-    uint32_t x_max = fr << (32 - NZO_PROB_BITS);
+    uint32_t x_max = fr << (32 - pb);
     if (x >= x_max) {
       scratch[emitted++] = (uint16_t)(x & 0xFFFF);
       x >>= 16;
     }
-    x = ((x / fr) << NZO_PROB_BITS) + (x % fr) + cum[s];
+    x = ((x / fr) << pb) + (x % fr) + cum[s];
   }
   uint32_t total = emitted + 2;
   if (total > cap) return 0;
@@ -276,7 +291,7 @@ static uint32_t encode_lane(const uint8_t *sym, uint64_t n, uint64_t unit,
 /* Encode one unit into `dst` (capacity U/2 + 1 words).  Returns the unit's
  * length in words; *raw is set when the unit had to be stored raw. */
 static uint64_t encode_unit(const uint8_t *sym, uint64_t n, uint64_t u,
-                            uint32_t S, uint32_t lenq, uint32_t pad,
+                            uint32_t S, uint32_t lenq, uint32_t pad, uint32_t pb,
                             const uint16_t *freq, const uint16_t *cum,
                             uint16_t *dst, int *raw) {
   const uint64_t U = 32ull * S;
@@ -290,7 +305,7 @@ static uint64_t encode_unit(const uint8_t *sym, uint64_t n, uint64_t u,
   uint64_t p = 16;
   int ok = 1;
   for (uint32_t j = 0; j < 32; ++j) {
-    uint32_t l = encode_lane(sym, n, u, S, j, pad, freq, cum, lane_words,
+    uint32_t l = encode_lane(sym, n, u, S, j, pad, pb, freq, cum, lane_words,
                              lane_cap, scratch);
     if (l == 0) {
       ok = 0;
@@ -320,13 +335,16 @@ static uint64_t encode_unit(const uint8_t *sym, uint64_t n, uint64_t u,
 }
 
 /* Encode n exponent bytes into an NZR1 container.  If `freq_in` is NULL the
- * table is derived from the data (histogram + nzo_normalize).  The pad symbol
+ * table and its resolution are derived from the data (histogram,
+ * nzo_choose_prob_bits, nzo_normalize); otherwise `prob_bits` gives the
+ * resolution of `freq_in` (pass 0 to derive everything).  The pad symbol
  * is the most frequent entry of the table (lowest index on ties).  Returns
  * the container size in bytes, or 0 if `cap` is too small / arguments are
  * invalid.  Units are coded independently (OpenMP over units when built with
  * -fopenmp). */
 uint64_t nzo_encode(const uint8_t *sym, uint64_t n, uint32_t lane_symbols,
-                    const uint16_t *freq_in, uint8_t *out, uint64_t cap) {
+                    const uint16_t *freq_in, uint32_t prob_bits, uint8_t *out,
+                    uint64_t cap) {
   const uint32_t S = lane_symbols;
   if (S == 0 || (S & 7) || S > 8192) return 0;
   const uint32_t lenq = nzo_len_quantum(S);
@@ -335,12 +353,14 @@ uint64_t nzo_encode(const uint8_t *sym, uint64_t n, uint32_t lane_symbols,
   if (cap < nzo_container_bound(n, S)) return 0;
 
   uint16_t freq[256], cum[257];
-  if (freq_in) {
+  uint32_t pb = prob_bits;
+  if (freq_in && pb >= 10 && pb <= NZO_MAX_PROB_BITS) {
     memcpy(freq, freq_in, sizeof(freq));
   } else {
     uint64_t hist[256];
     nzo_histogram(sym, n, hist);
-    nzo_normalize(hist, freq);
+    if (pb < 10 || pb > NZO_MAX_PROB_BITS) pb = nzo_choose_prob_bits(hist);
+    nzo_normalize(hist, pb, freq);
   }
   uint32_t pad = 0;
   for (int i = 1; i < 256; ++i)
@@ -362,7 +382,7 @@ uint64_t nzo_encode(const uint8_t *sym, uint64_t n, uint32_t lane_symbols,
 #pragma omp parallel for schedule(dynamic, 4)
   for (int64_t u = 0; u < (int64_t)n_units; ++u) {
     int raw = 0;
-    ulen[u] = encode_unit(sym, n, (uint64_t)u, S, lenq, pad, freq, cum,
+    ulen[u] = encode_unit(sym, n, (uint64_t)u, S, lenq, pad, pb, freq, cum,
                           tmp + (size_t)u * slot_words, &raw);
     uraw[u] = (uint8_t)raw;
   }
@@ -400,7 +420,7 @@ uint64_t nzo_encode(const uint8_t *sym, uint64_t n, uint32_t lane_symbols,
   h->lane_symbols = S;
   h->len_quantum = lenq;
   h->n_units = (uint32_t)n_units;
-  h->pad_symbol = pad;
+  h->prob_bits = pb;
   h->payload_offset = payload_off;
   h->payload_words = w;
   h->total_bytes = total;
@@ -411,7 +431,7 @@ uint64_t nzo_encode(const uint8_t *sym, uint64_t n, uint32_t lane_symbols,
 
 static int decode_unit(const uint32_t *offsets, const uint16_t *payload,
                        uint64_t pw, uint64_t u, uint64_t n, uint32_t S,
-                       uint32_t lenq, const uint16_t *freq,
+                       uint32_t lenq, uint32_t pb, const uint16_t *freq,
                        const uint16_t *cum, const uint8_t *slot_sym,
                        uint8_t *sym_out) {
   const uint64_t U = 32ull * S;
@@ -436,9 +456,9 @@ static int decode_unit(const uint32_t *offsets, const uint16_t *payload,
     uint64_t q = 2;
     uint32_t x = (uint32_t)ws[0] | ((uint32_t)ws[1] << 16);
     for (uint32_t i = 0; i < S; ++i) {
-      uint32_t slot = x & (NZO_PROB_SCALE - 1);
+      uint32_t slot = x & ((1u << pb) - 1);
       uint32_t s = slot_sym[slot];
-      x = (uint32_t)freq[s] * (x >> NZO_PROB_BITS) + slot - cum[s];
+      x = (uint32_t)freq[s] * (x >> pb) + slot - cum[s];
       if (x < NZO_STATE_LOW) {
         if (q >= lw) return -12;
         x = (x << 16) | ws[q++];
@@ -474,17 +494,20 @@ int nzo_decode(const uint8_t *in, uint64_t in_bytes, uint8_t *sym_out,
   if (h->payload_offset + h->payload_words * 2 > in_bytes) return -7;
   if (h->total_bytes > in_bytes) return -7;
 
+  const uint32_t pb = h->prob_bits;
+  if (pb < 10 || pb > NZO_MAX_PROB_BITS) return -4;
+  const uint32_t M = 1u << pb;
   const uint16_t *freq = (const uint16_t *)(in + 64);
   uint16_t cum[257];
   uint32_t total = 0;
   cum[0] = 0;
   for (int i = 0; i < 256; ++i) {
-    if (freq[i] > NZO_PROB_SCALE - 1) return -8;
+    if (freq[i] > M - 1) return -8;
     total += freq[i];
     cum[i + 1] = (uint16_t)total;
   }
-  if (total != NZO_PROB_SCALE) return -8;
-  uint8_t slot_sym[NZO_PROB_SCALE];
+  if (total != M) return -8;
+  uint8_t slot_sym[NZO_MAX_PROB_SCALE];
   for (int s = 0; s < 256; ++s)
     for (uint32_t k = cum[s]; k < cum[s + 1]; ++k) slot_sym[k] = (uint8_t)s;
 
@@ -496,7 +519,7 @@ int nzo_decode(const uint8_t *in, uint64_t in_bytes, uint8_t *sym_out,
   int err = 0;
 #pragma omp parallel for schedule(dynamic, 4)
   for (int64_t u = 0; u < (int64_t)n_units; ++u) {
-    int rc = decode_unit(offsets, payload, pw, (uint64_t)u, n, S, lenq, freq,
+    int rc = decode_unit(offsets, payload, pw, (uint64_t)u, n, S, lenq, pb, freq,
                          cum, slot_sym, sym_out);
     if (rc) {
 #pragma omp critical
@@ -513,7 +536,7 @@ uint64_t nzo_compress_bf16(const uint16_t *v, uint64_t n, int s,
                            uint32_t lane_symbols, uint8_t *exp_scratch,
                            uint8_t *frac_out, uint8_t *cont_out, uint64_t cap) {
   nzo_split(v, n, s, exp_scratch, frac_out);
-  return nzo_encode(exp_scratch, n, lane_symbols, NULL, cont_out, cap);
+  return nzo_encode(exp_scratch, n, lane_symbols, NULL, 0, cont_out, cap);
 }
 
 /* decompress = decode + merge */

@@ -20,8 +20,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libnz_oracle.so")
 
-PROB_BITS = 12
-PROB_SCALE = 1 << PROB_BITS
+MAX_PROB_BITS = 12
 HEADER_BYTES = 64
 FREQ_OFFSET = 64
 OFFSETS_OFFSET = 576
@@ -53,13 +52,15 @@ def lib() -> ctypes.CDLL:
         L.nzo_merge.restype = None
         L.nzo_histogram.argtypes = [vp, ctypes.c_size_t, vp]
         L.nzo_histogram.restype = None
-        L.nzo_normalize.argtypes = [vp, vp]
+        L.nzo_normalize.argtypes = [vp, u32, vp]
+        L.nzo_choose_prob_bits.argtypes = [vp]
+        L.nzo_choose_prob_bits.restype = u32
         L.nzo_normalize.restype = u32
         L.nzo_len_quantum.argtypes = [u32]
         L.nzo_len_quantum.restype = u32
         L.nzo_container_bound.argtypes = [u64, u32]
         L.nzo_container_bound.restype = u64
-        L.nzo_encode.argtypes = [vp, u64, u32, vp, vp, u64]
+        L.nzo_encode.argtypes = [vp, u64, u32, vp, u32, vp, u64]
         L.nzo_encode.restype = u64
         L.nzo_decode.argtypes = [vp, u64, vp, u64]
         L.nzo_decode.restype = i32
@@ -86,7 +87,7 @@ def default_lane_symbols(s: int) -> int:
     """Symbols per lane stream chosen for each precision: the shorter the lane
     stream the more parallel the decode, the longer the smaller the container;
     lossy modes store fewer bytes in total, so they get the longer streams."""
-    return {7: 256, 3: 384, 1: 512, 0: 512}[s]
+    return {7: 256, 3: 384, 1: 512, 0: 640}[s]
 
 
 def split(bits: np.ndarray, s: int, literal: bool = False) -> Tuple[np.ndarray, np.ndarray]:
@@ -116,10 +117,17 @@ def histogram(sym: np.ndarray) -> np.ndarray:
     return h
 
 
-def normalize(hist: np.ndarray) -> Tuple[np.ndarray, int]:
+def choose_prob_bits(hist: np.ndarray) -> int:
     hist = np.ascontiguousarray(hist, dtype=np.uint64)
+    return int(lib().nzo_choose_prob_bits(_p(hist)))
+
+
+def normalize(hist: np.ndarray, prob_bits: Optional[int] = None) -> Tuple[np.ndarray, int]:
+    hist = np.ascontiguousarray(hist, dtype=np.uint64)
+    if prob_bits is None:
+        prob_bits = choose_prob_bits(hist)
     f = np.zeros(256, np.uint16)
-    best = lib().nzo_normalize(_p(hist), _p(f))
+    best = lib().nzo_normalize(_p(hist), prob_bits, _p(f))
     return f, int(best)
 
 
@@ -127,7 +135,8 @@ def container_bound(n: int, lane_symbols: int) -> int:
     return int(lib().nzo_container_bound(n, lane_symbols))
 
 
-def encode(sym: np.ndarray, lane_symbols: int, freq: Optional[np.ndarray] = None) -> np.ndarray:
+def encode(sym: np.ndarray, lane_symbols: int, freq: Optional[np.ndarray] = None,
+           prob_bits: int = 0) -> np.ndarray:
     sym = np.ascontiguousarray(sym.reshape(-1), dtype=np.uint8)
     cap = container_bound(sym.size, lane_symbols)
     out = np.zeros(cap, np.uint8)
@@ -135,7 +144,7 @@ def encode(sym: np.ndarray, lane_symbols: int, freq: Optional[np.ndarray] = None
     if freq is not None:
         freq = np.ascontiguousarray(freq, dtype=np.uint16)
         fp = _p(freq)
-    got = lib().nzo_encode(_p(sym), sym.size, lane_symbols, fp, _p(out), cap)
+    got = lib().nzo_encode(_p(sym), sym.size, lane_symbols, fp, prob_bits, _p(out), cap)
     if got == 0:
         raise ValueError("oracle encode failed (bad lane_symbols or capacity)")
     return out[:got].copy()
@@ -198,7 +207,7 @@ def parse_header(container: np.ndarray) -> dict:
     h64 = c[:64].view(np.uint64)
     return dict(magic=int(h32[0]), version=int(h32[1]), n_symbols=int(h64[1]),
                 lane_symbols=int(h32[4]), len_quantum=int(h32[5]), n_units=int(h32[6]),
-                pad_symbol=int(h32[7]), payload_offset=int(h64[4]), payload_words=int(h64[5]),
+                prob_bits=int(h32[7]), payload_offset=int(h64[4]), payload_words=int(h64[5]),
                 total_bytes=int(h64[6]), n_raw_units=int(h32[14]),
                 max_coded_unit_words=int(h32[15]))
 
@@ -241,7 +250,7 @@ def decode_python(container: np.ndarray, n: int) -> np.ndarray:
     """Pure-Python decoder of the NZR1 container (small inputs only)."""
     c = np.ascontiguousarray(container, dtype=np.uint8)
     h = parse_header(c)
-    S, lenq = h["lane_symbols"], h["len_quantum"]
+    S, lenq, pb = h["lane_symbols"], h["len_quantum"], h["prob_bits"]
     U = 32 * S
     n_units = h["n_units"]
     freq = c[FREQ_OFFSET:FREQ_OFFSET + 512].view(np.uint16).astype(np.int64)
@@ -264,9 +273,9 @@ def decode_python(container: np.ndarray, n: int) -> np.ndarray:
             x = int(ws[0]) | (int(ws[1]) << 16)
             q = 2
             for i in range(S):
-                slot = x & (PROB_SCALE - 1)
+                slot = x & ((1 << pb) - 1)
                 sy = int(slot_sym[slot])
-                x = int(freq[sy]) * (x >> PROB_BITS) + slot - int(cum[sy])
+                x = int(freq[sy]) * (x >> pb) + slot - int(cum[sy])
                 if x < (1 << 16):
                     x = (x << 16) | int(ws[q])
                     q += 1

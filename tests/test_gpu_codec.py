@@ -85,6 +85,8 @@ def exponent_streams():
     yield "uniform_incompressible", rng.integers(0, 256, size=50000, dtype=np.uint8)
     yield "all_256_skewed", np.concatenate(
         [np.arange(256, dtype=np.uint8), np.full(90000, 17, np.uint8)])
+    yield "fifty_symbols", rng.choice(np.arange(60, 110, dtype=np.uint8), size=70000,
+                                      p=np.r_[np.full(10, 0.08), np.full(40, 0.005)])
     yield "single_element", np.array([200], np.uint8)
     yield "half_raw_half_coded", np.concatenate(
         [rng.integers(0, 256, size=32768, dtype=np.uint8), np.full(32768, 9, np.uint8)])
