@@ -42,8 +42,9 @@ UNIT = "GB/s"
 
 # DRAM traffic of one decode launch on the largest matrix (4096x11008, precision 7),
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture summarised in
-# profiles/decode_kernel_s7_4096x11008.md; scaled to the average launch by elements.
-NCU_TRAFFIC_BYTES_45M = None
+# profiles/kernels_precision7_4096x11008.md; scaled to the average launch by elements.
+NCU_TRAFFIC_BYTES_45M = 60.34e6 + 32.8e6   # read + written by kernel end; the rest of the
+# 90 MB output is still in L2 then and is written back while the next launch runs
 NCU_TRAFFIC_ELEMENTS = 4096 * 11008
 
 
@@ -421,6 +422,7 @@ def run_ours(args):
                            os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
     if rank == 0:
         sampler.start()
+        time.sleep(0.3)
     main = stacks[7]
     ms = timed_passes(torch, dist, lambda: decompress_pass(L, main, outs, status, st),
                       args.steps, args.warmup, world)

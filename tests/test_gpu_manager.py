@@ -1,0 +1,157 @@
+"""GPU tests of the public Python API (Manager, nn, ops, hooks) on the CUDA
+backend: what a user of the reference's package would run."""
+import numpy as np
+import pytest
+import torch
+
+import neuzip
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def bits_of(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16).reshape(-1)
+
+
+def weights(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("precision", (0, 1, 3, 7))
+def test_write_read_matches_oracle(precision):
+    m = neuzip.Manager(precision=precision)
+    w = weights((300, 517), 1)                      # not a multiple of anything
+    h = m.write(w)                                   # CPU tensor is moved to the GPU
+    got = m.read(h)
+    m.check()
+    assert got.is_cuda and got.shape == w.shape and got.dtype == torch.bfloat16
+    assert not got.requires_grad
+    e, f = O.split(bits_of(w), precision)
+    ref = O.merge(e, f, precision, canonical_nan=True)
+    assert np.array_equal(bits_of(got), ref)
+    entry = m._be.entry(h)
+    assert m.size(h) == entry.container.numel() + entry.fractions.numel()
+    assert m.size("nope") == 0
+
+
+def test_rewrite_same_handle_and_many_tensors():
+    m = neuzip.Manager()
+    ws = [weights((64 + 8 * i, 96), 10 + i).cuda() for i in range(5)]
+    hs = [m.write(w) for w in ws]
+    assert hs == [str(i) for i in range(5)]
+    for h, w in zip(hs, ws):
+        assert torch.equal(m.read(h), w)
+    w_new = weights((7, 9), 99).cuda()
+    assert m.write(w_new, hs[2]) == hs[2]
+    assert torch.equal(m.read(hs[2]), w_new)
+    m.check()
+
+
+def test_split_is_full_precision_regardless_of_manager_precision():
+    w = weights((128, 130), 3).cuda()
+    for precision in (7, 1):
+        e, f = neuzip.Manager(precision=precision).split(w)
+        assert e.shape == w.shape and f.shape == w.shape and e.dtype == torch.uint8
+        er, fr = O.split(bits_of(w), 7)
+        assert np.array_equal(e.cpu().numpy().reshape(-1), er)
+        assert np.array_equal(f.cpu().numpy().reshape(-1), fr)
+
+
+def test_errors_follow_the_reference():
+    m = neuzip.Manager()
+    with pytest.raises(RuntimeError, match="Unsupported data type"):
+        m.write(torch.zeros(8, 8, dtype=torch.float32))
+    with pytest.raises(KeyError):
+        m.read("7")
+    with pytest.raises(RuntimeError, match="Data not found"):
+        m._be.read("7")
+
+
+def test_linear_with_and_without_bias():
+    m = neuzip.Manager()
+    w = weights((48, 64), 4).cuda()
+    b = weights((48,), 5).cuda()
+    h = m.write(w)
+    x = weights((3, 5, 64), 6).cuda()
+    y = m.linear(h, x)
+    assert torch.allclose(y.float(), torch.matmul(x, w.t()).float(), atol=1e-3, rtol=1e-2)
+    y2 = m.linear(h, x.reshape(-1, 64), b)
+    ref2 = torch.nn.functional.linear(x.reshape(-1, 64), w, b)
+    assert torch.allclose(y2.float(), ref2.float(), atol=1e-3, rtol=1e-2)
+
+
+def test_dummy_backend_round_trip():
+    m = neuzip.Manager(algorithm=neuzip.Algorithm.dummy)
+    w = weights((16, 32), 7)
+    h = m.write(w)
+    assert torch.equal(m.read(h).cpu(), w)
+    assert m.size(h) == w.numel() * 2
+    x = weights((4, 32), 8).cuda()
+    assert m.linear(h, x).shape == (4, 16)
+
+
+def test_compressed_linear_training_step_matches_dense():
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(64, 32, bias=True).to(torch.bfloat16)
+    dense = torch.nn.Linear(64, 32, bias=True).to(torch.bfloat16)
+    dense.load_state_dict(lin.state_dict())
+    dense = dense.cuda()
+    m = neuzip.Manager()
+    model = m.convert(torch.nn.Sequential(lin)).cuda()
+    x = torch.randn(10, 64, device="cuda", dtype=torch.bfloat16)
+
+    class Sched:
+        def get_last_lr(self):
+            return [0.25]
+
+    sched = Sched()
+    p = model[0]._p
+    p.register_post_accumulate_grad_hook(lambda q: neuzip.compressed_lomo_hook(sched, q))
+    y = model(x)
+    yd = dense(x)
+    assert torch.equal(y, yd)                         # lossless weight, same GEMM
+    y.float().pow(2).mean().backward()
+    yd.float().pow(2).mean().backward()
+    expect = dense.weight.data.clone()
+    expect.add_(dense.weight.grad, alpha=-0.25)
+    assert p._gradient is None                        # consumed by the hook
+    assert torch.equal(p(), expect)                   # read -> update -> write round trip
+    assert torch.allclose(model[0].bias.grad.float(), dense.bias.grad.float(), atol=1e-3)
+    m.check()
+
+
+def test_convert_tiny_llama_logits_and_greedy_tokens():
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=352,
+                                   num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=4, max_position_embeddings=128)
+    torch.manual_seed(0)
+    model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+    ids = torch.randint(0, 512, (1, 16), device="cuda")
+    with torch.no_grad():
+        ref_logits = model(ids).logits
+        ref_tokens = model.generate(ids, max_new_tokens=8, do_sample=False)
+    m = neuzip.Manager()
+    m.convert(model)
+    n_converted = sum(isinstance(mod, neuzip.nn.Linear) for mod in model.modules())
+    assert n_converted == 2 * 7                      # q,k,v,o,gate,up,down per layer; lm_head kept
+    assert isinstance(model.lm_head, torch.nn.Linear)
+    with torch.no_grad():
+        logits = model(ids).logits
+        tokens = model.generate(ids, max_new_tokens=8, do_sample=False)
+    m.check()
+    assert (logits.float() - ref_logits.float()).abs().max().item() <= 1e-2
+    assert torch.equal(tokens, ref_tokens)
+    dense_bytes = sum(int(np.prod(s)) * 2 for s in m.meta_dict.values())
+    assert m.total_size() < 0.75 * dense_bytes
+
+
+def test_lossy_precision_error_bounds():
+    w = weights((256, 256), 11).cuda()
+    bounds = {0: 0.03125, 1: 0.015625, 3: 0.00390625}
+    for precision, bound in bounds.items():
+        m = neuzip.Manager(precision=precision)
+        got = m.read(m.write(w))
+        assert (got.float() - w.float()).abs().max().item() <= bound
