@@ -105,6 +105,35 @@ int nz_encode_exponents(const void *exp_in, uint64_t n, uint32_t lane_symbols,
                         void *container, uint64_t container_cap, void *scratch,
                         uint64_t scratch_bytes, void *stream);
 
+/* Size in bytes of the scratch area built into the library (see below). */
+uint64_t nz_static_scratch_bytes(void);
+
+/* Same result as nz_encode_exponents, byte for byte, but the caller passes no
+ * scratch and the call allocates nothing: no cudaMalloc, no cudaFree, no
+ * allocating library routine.  It exists for hosts that may not allocate device
+ * memory when they compress - a server whose arena already owns the whole GPU
+ * and exposes no allocator to plugins, or a framework that forbids cudaMalloc /
+ * cudaFree on its hot path because both synchronise the device.  The scratch is a
+ * fixed 6 MiB array inside the library image; every GPU that loads the library
+ * carries it until the process exits.
+ *
+ * Limit: nz_encode_scratch_bytes(n, lane_symbols) must not exceed
+ * nz_static_scratch_bytes() (about 5.5 million symbols at lane_symbols 256, fewer
+ * for short lane streams); larger requests return NZ_E_CAPACITY with a message
+ * and leave the container untouched.
+ *
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current; make that first call outside
+ * any stream capture.  All calls on a device share the one array, which keeps the
+ * previous call's contents (the call clears what it needs zeroed itself): two
+ * calls whose work overlaps on the GPU - different streams, or threads - race on
+ * it and corrupt each other's output.  Serialise them, or use nz_encode_exponents.
+ *
+ * This entry point has no counterpart in the reference. */
+int nz_encode_exponents_static_scratch(const void *exp_in, uint64_t n,
+                                       uint32_t lane_symbols, void *container,
+                                       uint64_t container_cap, void *stream);
+
 /* Copies the container header to the host and returns the container length
  * in *total_bytes and the largest coded unit (16-bit words) in
  * *max_unit_words.  Synchronises the stream (the one host sync of a write).

@@ -16,6 +16,8 @@
 //   [4096, 4096+4*(nu+1))           u32 unit_words[nu]  (bit 31 = raw)
 //   [.., + 64*nu)                   u16 lane_len[nu][32]   (words; 0 = unit raw)
 //   [.., + nu*32*cap*2)             u16 lane_words[nu][32][cap]   cap = lane_cap_words(S)
+#include <mutex>
+
 #include "nz_common.cuh"
 
 namespace nz {
@@ -461,6 +463,84 @@ extern "C" int nz_encode_exponents(const void *exp_in, uint64_t n, uint32_t lane
   }
   return nz::encode_exponents(exp_in, n, lane_symbols, container, container_cap, scratch,
                               scratch_bytes, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// Encoding without any device allocation.
+//
+// Some hosts of this library are not allowed to allocate device memory at the
+// point where they need to compress a tensor: a serving process that handed the
+// whole GPU to its own arena at start-up and gives plugins no allocator, or a
+// framework that bans cudaMalloc / cudaFree on its hot path because both
+// synchronise the device and would stall every other stream.  For them the
+// scratch area of the encoder lives in the library image itself: one fixed array
+// in device memory, present on every GPU that loads the library until the
+// process exits.
+//
+// The array below is a *host-side handle* as far as host code is concerned: its
+// name is not a device address and must never be handed to a kernel.  The real
+// address on the current device is looked up once per device with
+// cudaGetSymbolAddress (here, in the same translation unit as the array) and
+// that pointer is what the kernels receive.
+constexpr size_t kStaticScratchBytes = 6u << 20;   // 6 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_mutex;
+static void *g_static_ptr[kMaxDevices];            // resolved address per device ordinal
+
+// Device address of g_static_scratch on the current device.  The first call on
+// a device performs the lookup; later calls return the cached pointer.
+static int static_scratch_ptr(void **out) {
+  int dev = 0;
+  NZ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    nz::set_error("static scratch: device ordinal %d is outside the supported range", dev);
+    return NZ_E_ARG;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    NZ_CUDA_TRY(cudaGetSymbolAddress((void **)&p, g_static_scratch));
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return NZ_OK;
+}
+
+extern "C" uint64_t nz_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int nz_encode_exponents_static_scratch(const void *exp_in, uint64_t n,
+                                                  uint32_t lane_symbols, void *container,
+                                                  uint64_t container_cap, void *stream) {
+  int rc = check_encode_args("nz_encode_exponents_static_scratch", n, lane_symbols);
+  if (rc) return rc;
+  if (!container || (n && !exp_in)) {
+    nz::set_error("nz_encode_exponents_static_scratch: null pointer");
+    return NZ_E_ARG;
+  }
+  if (((uintptr_t)exp_in & 15) || ((uintptr_t)container & 15)) {
+    nz::set_error("nz_encode_exponents_static_scratch: buffers must be 16-byte aligned");
+    return NZ_E_ARG;
+  }
+  const uint64_t need = nz::scratch_layout(n, lane_symbols).total;
+  if (need > kStaticScratchBytes) {
+    nz::set_error("nz_encode_exponents_static_scratch: %llu symbols with lane_symbols %u need %llu "
+                  "bytes of scratch, the built-in area holds %llu; use nz_encode_exponents with "
+                  "caller-provided scratch for tensors this large",
+                  (unsigned long long)n, lane_symbols, (unsigned long long)need,
+                  (unsigned long long)kStaticScratchBytes);
+    return NZ_E_CAPACITY;
+  }
+  void *scratch = nullptr;
+  rc = static_scratch_ptr(&scratch);
+  if (rc) return rc;
+  // The area still holds whatever the previous call left there.  The only part
+  // that must start from zero is the histogram, and the pipeline clears it itself
+  // (a memset on the stream) before counting; every other region is written in
+  // full for the units of this call before it is read.
+  return nz::encode_exponents(exp_in, n, lane_symbols, container, container_cap, scratch,
+                              kStaticScratchBytes, (cudaStream_t)stream);
 }
 
 extern "C" int nz_container_bytes(const void *container, uint64_t *total_bytes,
