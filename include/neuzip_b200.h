@@ -170,6 +170,29 @@ int nz_decompress_bf16(const void *container, uint64_t container_bytes,
                        int canonical_nan, void *out_bf16, void *status,
                        void *stream);
 
+/* One tensor of a batched decompress. */
+typedef struct nz_decompress_item {
+  const void *container;     /* NZR1 container, 16-byte aligned            */
+  uint64_t container_bytes;
+  const void *frac_in;       /* packed fractions, 8-byte aligned           */
+  uint64_t n;                /* elements                                   */
+  uint32_t max_unit_words;   /* from nz_container_bytes, 0 = worst case    */
+  uint32_t reserved;
+  void *out_bf16;            /* bf16[n], 16-byte aligned                   */
+} nz_decompress_item;
+
+/* nz_decompress_bf16 for several tensors of the same precision and
+ * lane_symbols (for instance the seven matrices of one transformer layer) in
+ * as few launches as possible: up to 8 tensors share a launch, each on a share
+ * of the SMs proportional to its size, so small matrices do not leave most of
+ * the GPU idle and the fixed cost of a launch is paid once.  `items` is a host
+ * array; results are the same as `count` single calls.  No host sync.
+ * Reference: Manager::read called once per converted Linear while a layer runs
+ * (neuzip/nn/module.py:23-25 -> neuzip/binding.py:88-92 -> cuda/high_level.cu:223-250). */
+int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_t count,
+                             int precision, uint32_t lane_symbols,
+                             int canonical_nan, void *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,17 @@ SIGNATURES = {
     "nz_decompress_bf16": (_int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _vp, _vp, _vp]),
 }
 
+
+
+class DecompressItem(ctypes.Structure):
+    """struct nz_decompress_item"""
+    _fields_ = [("container", _vp), ("container_bytes", _u64), ("frac_in", _vp), ("n", _u64),
+                ("max_unit_words", _u32), ("reserved", _u32), ("out_bf16", _vp)]
+
+
+SIGNATURES["nz_decompress_bf16_batch"] = (
+    _int, [ctypes.POINTER(DecompressItem), _u32, _int, _u32, _int, _vp, _vp])
+
 _lock = threading.Lock()
 _lib = None
 

@@ -154,6 +154,37 @@ class CodecBackend:
             self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
             _ptr(out), _ptr(self._status), _stream()))
 
+    def read_many(self, names: Sequence[str]) -> List[torch.Tensor]:
+        """Decompress several tensors (for instance all matrices of one layer) with
+        as few launches as possible; same results as ``[self.read(n) for n in names]``.
+        The reference reads one tensor per call (neuzip/binding.py:88-92); batching lets
+        small matrices share the GPU instead of each leaving most SMs idle."""
+        entries = []
+        for name in names:
+            entry = self._cache.get(name)
+            if entry is None:
+                raise RuntimeError("Data not found")
+            entries.append(entry)
+        outs = [torch.empty(e.numel, dtype=torch.bfloat16, device="cuda") for e in entries]
+        # one batched call per lane_symbols value (a manager only ever has one)
+        by_s: Dict[int, List[int]] = {}
+        for i, e in enumerate(entries):
+            by_s.setdefault(e.lane_symbols, []).append(i)
+        for S, idx in by_s.items():
+            items = (_lib.DecompressItem * len(idx))()
+            for k, i in enumerate(idx):
+                e = entries[i]
+                items[k].container = _ptr(e.container)
+                items[k].container_bytes = e.container.numel()
+                items[k].frac_in = _ptr(e.fractions)
+                items[k].n = e.numel
+                items[k].max_unit_words = e.max_unit_words
+                items[k].out_bf16 = _ptr(outs[i])
+            _lib.check(self._lib.nz_decompress_bf16_batch(
+                items, len(idx), self.precision, S, int(self.canonical_nan), _ptr(self._status),
+                _stream()))
+        return outs
+
     def size(self, name: str) -> int:
         """cuda/high_level.cu:208-221: stored bytes, 0 for an unknown name."""
         entry = self._cache.get(name)

@@ -103,6 +103,15 @@ class Manager:
         return exp.reshape(tensor.shape), frac.reshape(tensor.shape)
 
     # extras (not in the reference)
+    def read_many(self, handles) -> list:
+        """Decompress several handles in one batched call (e.g. a whole layer)."""
+        handles = list(handles)
+        if hasattr(self._be, "read_many"):
+            flats = self._be.read_many(handles)
+        else:
+            flats = [self._be.read(h) for h in handles]
+        return [t.requires_grad_(False).reshape(self.meta_dict[h]) for t, h in zip(flats, handles)]
+
     def check(self) -> None:
         """Raise if any decode so far flagged a malformed container."""
         if hasattr(self._be, "check"):

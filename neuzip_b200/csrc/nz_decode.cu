@@ -29,6 +29,8 @@
 // CTA's shared memory (a guard band behind the last slot absorbs run-away
 // pointers), output and fraction addresses never depend on coded data, and
 // the wait on the bulk copy is bounded.
+#include <string.h>
+
 #include "nz_common.cuh"
 
 namespace nz {
@@ -225,6 +227,29 @@ struct DecodeArgs {
   int canon;
   uint16_t *out_bf16;
   uint8_t *out_exp;
+  uint32_t *status;
+};
+
+// One launch decodes up to kMaxBatch tensors; each tensor gets its own range of
+// CTAs (one CTA per SM), sized in proportion to its unit count, so a small
+// tensor does not leave most of the machine idle.
+constexpr uint32_t kMaxBatch = 8;
+struct BatchItem {
+  const uint8_t *container;
+  uint64_t container_bytes;
+  const uint8_t *frac;
+  uint64_t n;
+  uint16_t *out_bf16;
+  uint8_t *out_exp;
+  uint32_t n_units;
+  uint32_t cta_begin;     // first CTA of this tensor
+};
+struct BatchArgs {
+  BatchItem item[kMaxBatch];
+  uint32_t count;
+  uint32_t n_ctas;        // == gridDim.x
+  uint32_t S, slot_bytes, lut_shift, lut_bytes, ring_offset;
+  int canon;
   uint32_t *status;
 };
 
@@ -566,8 +591,31 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
 
 template <int S, bool MERGE>
 __global__ void __launch_bounds__(640, 1)
-decode_kernel(const DecodeArgs a) {
+decode_kernel(const BatchArgs batch) {
   extern __shared__ __align__(128) uint8_t smem[];
+  // which tensor this CTA works on, and its rank among that tensor's CTAs
+  uint32_t ti = 0;
+#pragma unroll
+  for (uint32_t t = 1; t < kMaxBatch; ++t)
+    if (t < batch.count && blockIdx.x >= batch.item[t].cta_begin) ti = t;
+  const uint32_t cta_first = batch.item[ti].cta_begin;
+  const uint32_t cta_end = (ti + 1 < batch.count) ? batch.item[ti + 1].cta_begin : batch.n_ctas;
+  const uint32_t cta_rank = blockIdx.x - cta_first, cta_count = cta_end - cta_first;
+  DecodeArgs a;
+  a.container = batch.item[ti].container;
+  a.container_bytes = batch.item[ti].container_bytes;
+  a.frac = batch.item[ti].frac;
+  a.n = batch.item[ti].n;
+  a.S = batch.S;
+  a.n_units = batch.item[ti].n_units;
+  a.slot_bytes = batch.slot_bytes;
+  a.lut_shift = batch.lut_shift;
+  a.lut_bytes = batch.lut_bytes;
+  a.ring_offset = batch.ring_offset;
+  a.canon = batch.canon;
+  a.out_bf16 = batch.item[ti].out_bf16;
+  a.out_exp = batch.item[ti].out_exp;
+  a.status = batch.status;
   const uint32_t n_warps = blockDim.x >> 5;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t lut_bytes = 4096u << a.lut_shift;           // 2^pb slots would need 4 << shift each
@@ -602,8 +650,8 @@ decode_kernel(const DecodeArgs a) {
   const Header *h = reinterpret_cast<const Header *>(a.container);
   const uint64_t pay_off = payload_offset(a.n_units);
   const uint64_t max_words = (a.container_bytes - pay_off) / 2;   // host checked bytes >= pay_off
-  const uint32_t stride = 2 * gridDim.x * n_warps;
-  uint32_t u = 2 * (blockIdx.x * n_warps + warp);
+  const uint32_t stride = 2 * cta_count * n_warps;
+  uint32_t u = 2 * (cta_rank * n_warps + warp);
   uint32_t parity = 0;
   UnitPlan pa = plan_unit(a, u, pay_off, max_words, lane);
   UnitPlan pb2 = plan_unit(a, u + 1, pay_off, max_words, lane);
@@ -652,7 +700,7 @@ decode_kernel(const DecodeArgs a) {
   if (bad) {
     // copies may be in flight into this warp's slots: let them land before leaving
     if (staged) wait_staged(bar, parity);
-    if (threadIdx.x == 0 && blockIdx.x == 0) raise(a.status, bad);
+    if (threadIdx.x == 0 && cta_rank == 0) raise(a.status, bad);
     return;
   }
   // Decode table: warps take symbols in turn; a symbol's slot range is a run of
@@ -733,120 +781,203 @@ decode_kernel(const DecodeArgs a) {
 }
 
 // ------------------------------------------------------------------- host
-struct LaunchGeom {
-  uint32_t warps, slot_bytes, smem_bytes, blocks, lut_shift, lut_bytes, ring_offset;
+struct HostItem {
+  const void *container;
+  uint64_t container_bytes;
+  const void *frac;
+  uint64_t n;
+  uint32_t max_unit_words;
+  void *out_bf16;
+  void *out_exp;
 };
 
-// Grid geometry.  Every warp decodes whole units, two at a time, so the kernel
-// is only as fast as the SM with the most units: one CTA per SM, the same
-// number of warps in every CTA and the same number of unit pairs (within one)
-// for every warp.  The decode table gets what shared memory the slots leave
-// (more copies = fewer bank conflicts), at most 32 copies of 2^10 slots.
-static int decode_geometry(uint64_t n, uint32_t S, uint32_t max_unit_words, LaunchGeom &g) {
+// Grid geometry of one launch over `count` tensors.  One CTA per SM.  Every
+// warp decodes whole units, two at a time, so a tensor is only as fast as its
+// busiest CTA: each tensor gets CTAs in proportion to its units, every CTA the
+// same number of warps, every warp the same number of unit pairs (within one).
+// The decode table gets what shared memory the slots and rings leave (more
+// copies = fewer bank conflicts), at most 128 KB.
+static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, BatchArgs &b,
+                           uint32_t &warps, uint32_t &smem_bytes) {
   const uint64_t U = 32ull * S;
-  uint64_t unit_bytes = max_unit_words ? (uint64_t)max_unit_words * 2 : U;
-  if (unit_bytes > U) unit_bytes = U;
+  uint64_t unit_bytes = 0, total_units = 0;
+  for (uint32_t t = 0; t < count; ++t) {
+    uint64_t ub = items[t].max_unit_words ? (uint64_t)items[t].max_unit_words * 2 : U;
+    if (ub > U) ub = U;
+    if (ub > unit_bytes) unit_bytes = ub;
+    total_units += unit_count(items[t].n, S);
+  }
   if (unit_bytes < 160) unit_bytes = 160;
-  g.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
+  b.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
   const uint32_t guard = ((S + 8) * 2 + 127) & ~127u;
   const uint32_t sm_smem = 227u * 1024u;
   const uint32_t kMaxWarps = 20;
-  const uint64_t nu = unit_count(n, S);
-  const uint32_t sms = (uint32_t)sm_count();
-  const uint64_t pairs_per_sm = ((nu + 1) / 2 + sms - 1) / sms;
-  // smallest table first (2^12 slots, one copy = 16 KB) to find how many warps fit
-  auto cap_for = [&](uint32_t lut_bytes) -> uint32_t {
-    const uint32_t fixed = lut_bytes + 1024 + guard;
-    if (fixed + 2 * g.slot_bytes + kRingBytes > sm_smem) return 0;
-    uint32_t c = (sm_smem - fixed) / (2 * g.slot_bytes + kRingBytes);
-    return c > kMaxWarps ? kMaxWarps : c;
-  };
-  uint32_t cap = cap_for(16 * 1024);
-  if (cap == 0) {
+  const uint32_t per_warp = 2 * b.slot_bytes + kRingBytes;
+  const uint32_t min_fixed = 16 * 1024 + 1024 + guard;
+  if (min_fixed + per_warp > sm_smem) {
     set_error("decode: two units of %u symbols do not fit in shared memory", (unsigned)U);
     return NZ_E_ARG;
   }
-  const uint64_t rounds = (pairs_per_sm + cap - 1) / cap;
-  uint32_t warps = (uint32_t)((pairs_per_sm + rounds - 1) / (rounds ? rounds : 1));
+  uint32_t cap = (sm_smem - min_fixed) / per_warp;
+  if (cap > kMaxWarps) cap = kMaxWarps;
+
+  // CTAs per tensor: proportional to units, at least one, summing to the SM count
+  // (or fewer when there is not enough work to give every SM a pair of units)
+  const uint32_t sms = (uint32_t)sm_count();
+  uint64_t total_pairs = 0;
+  for (uint32_t t = 0; t < count; ++t) total_pairs += (unit_count(items[t].n, S) + 1) / 2;
+  uint32_t n_ctas = sms;
+  if (total_pairs < n_ctas) n_ctas = (uint32_t)total_pairs;
+  if (n_ctas < count) n_ctas = count;
+  uint32_t ctas[kMaxBatch], used = 0;
+  for (uint32_t t = 0; t < count; ++t) {
+    const uint64_t nu = unit_count(items[t].n, S);
+    uint64_t c = total_units ? (nu * n_ctas + total_units / 2) / total_units : 1;
+    const uint64_t pairs = (nu + 1) / 2;
+    if (c > pairs) c = pairs;
+    if (c < 1) c = 1;
+    ctas[t] = (uint32_t)c;
+    used += ctas[t];
+  }
+  // fix the rounding: take from / give to the tensor with the most / fewest pairs per CTA
+  auto load = [&](uint32_t t, uint32_t c) {
+    return (double)((unit_count(items[t].n, S) + 1) / 2) / (double)c;
+  };
+  while (used > n_ctas) {
+    uint32_t best = kMaxBatch;
+    for (uint32_t t = 0; t < count; ++t)
+      if (ctas[t] > 1 && (best == kMaxBatch || load(t, ctas[t] - 1) < load(best, ctas[best] - 1)))
+        best = t;
+    if (best == kMaxBatch) break;
+    --ctas[best];
+    --used;
+  }
+  while (used < n_ctas) {
+    uint32_t best = kMaxBatch;
+    for (uint32_t t = 0; t < count; ++t) {
+      const uint64_t pairs = (unit_count(items[t].n, S) + 1) / 2;
+      if (ctas[t] < pairs && (best == kMaxBatch || load(t, ctas[t]) > load(best, ctas[best])))
+        best = t;
+    }
+    if (best == kMaxBatch) break;
+    ++ctas[best];
+    ++used;
+  }
+  // warps per CTA: enough for the busiest CTA's pairs, spread over whole rounds
+  uint32_t max_pairs = 1;
+  for (uint32_t t = 0; t < count; ++t) {
+    const uint64_t pairs = (unit_count(items[t].n, S) + 1) / 2;
+    const uint32_t per_cta = (uint32_t)((pairs + ctas[t] - 1) / ctas[t]);
+    if (per_cta > max_pairs) max_pairs = per_cta;
+  }
+  const uint32_t rounds = (max_pairs + cap - 1) / cap;
+  warps = (max_pairs + rounds - 1) / rounds;
   if (warps < 1) warps = 1;
   // largest table that still leaves room for these warps
-  g.lut_shift = 2;
+  b.lut_shift = 2;
   for (uint32_t sh = 5; sh > 2; --sh) {        // 2^12 slots x 2^(sh-2) copies
-    const uint32_t lut_bytes = 4096u << sh;
-    if (lut_bytes + 1024 + guard + warps * (2 * g.slot_bytes + kRingBytes) <= sm_smem) {
-      g.lut_shift = sh;
+    if ((4096u << sh) + 1024 + guard + warps * per_warp <= sm_smem) {
+      b.lut_shift = sh;
       break;
     }
   }
-  g.lut_bytes = 4096u << g.lut_shift;
-  uint64_t blocks = sms;
-  const uint64_t needed = ((nu + 1) / 2 + warps - 1) / warps;     // no CTA without a unit
-  if (blocks > needed) blocks = needed;
-  if (blocks == 0) blocks = 1;
-  g.warps = warps;
-  g.blocks = (uint32_t)blocks;
-  g.ring_offset = g.lut_bytes + 1024 + guard + warps * 2 * g.slot_bytes;
-  g.smem_bytes = g.ring_offset + warps * kRingBytes;
+  b.lut_bytes = 4096u << b.lut_shift;
+  b.ring_offset = b.lut_bytes + 1024 + guard + warps * 2 * b.slot_bytes;
+  smem_bytes = b.ring_offset + warps * kRingBytes;
+  uint32_t begin = 0;
+  for (uint32_t t = 0; t < count; ++t) {
+    b.item[t].cta_begin = begin;
+    begin += ctas[t];
+  }
+  b.n_ctas = begin;
   return NZ_OK;
 }
 
 template <int S, bool MERGE>
-static int launch_decode(const DecodeArgs &a, const LaunchGeom &g, cudaStream_t st) {
+static int launch_decode(const BatchArgs &b, uint32_t warps, uint32_t smem_bytes, cudaStream_t st) {
   auto kern = decode_kernel<S, MERGE>;
   NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)g.smem_bytes));
+                                   (int)smem_bytes));
   // Programmatic stream serialisation: this launch may begin while the previous
   // kernel of the stream drains; the kernel itself waits (griddepcontrol.wait)
   // before it reads or writes global memory, so ordering is preserved.
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(g.blocks);
-  cfg.blockDim = dim3(g.warps * 32);
-  cfg.dynamicSmemBytes = g.smem_bytes;
+  cfg.gridDim = dim3(b.n_ctas);
+  cfg.blockDim = dim3(warps * 32);
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  NZ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a));
+  NZ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, b));
   return NZ_OK;
+}
+
+// Decode `count` tensors (same precision and lane_symbols), kMaxBatch per launch.
+int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S, int canon,
+                bool merge, void *status, cudaStream_t st) {
+  HostItem live[kMaxBatch];
+  uint32_t n_live = 0;
+  auto flush = [&]() -> int {
+    if (n_live == 0) return NZ_OK;
+    BatchArgs b;
+    memset(&b, 0, sizeof(b));
+    uint32_t warps = 0, smem_bytes = 0;
+    int rc = decode_geometry(live, n_live, S, b, warps, smem_bytes);
+    if (rc) return rc;
+    b.count = n_live;
+    b.S = S;
+    b.canon = canon;
+    b.status = (uint32_t *)status;
+    for (uint32_t t = 0; t < n_live; ++t) {
+      b.item[t].container = (const uint8_t *)live[t].container;
+      b.item[t].container_bytes = live[t].container_bytes;
+      b.item[t].frac = (const uint8_t *)live[t].frac;
+      b.item[t].n = live[t].n;
+      b.item[t].out_bf16 = (uint16_t *)live[t].out_bf16;
+      b.item[t].out_exp = (uint8_t *)live[t].out_exp;
+      b.item[t].n_units = (uint32_t)unit_count(live[t].n, S);
+    }
+    n_live = 0;
+    if (!merge) return launch_decode<7, false>(b, warps, smem_bytes, st);
+    switch (precision) {
+      case 0: return launch_decode<0, true>(b, warps, smem_bytes, st);
+      case 1: return launch_decode<1, true>(b, warps, smem_bytes, st);
+      case 3: return launch_decode<3, true>(b, warps, smem_bytes, st);
+      default: return launch_decode<7, true>(b, warps, smem_bytes, st);
+    }
+  };
+  for (uint32_t i = 0; i < count; ++i) {
+    if (items[i].n == 0) continue;
+    const uint64_t nu = unit_count(items[i].n, S);
+    if (items[i].container_bytes < payload_offset(nu)) {
+      set_error("decode: container %u of %llu bytes is too short for %llu units", i,
+                (unsigned long long)items[i].container_bytes, (unsigned long long)nu);
+      return NZ_E_FORMAT;
+    }
+    live[n_live++] = items[i];
+    if (n_live == kMaxBatch) {
+      int rc = flush();
+      if (rc) return rc;
+    }
+  }
+  return flush();
 }
 
 int decode_common(const void *container, uint64_t container_bytes, const void *frac, uint64_t n,
                   int precision, uint32_t S, uint32_t max_unit_words, int canon, void *out_bf16,
                   void *out_exp, void *status, cudaStream_t st) {
-  if (n == 0) return NZ_OK;
-  const uint64_t nu = unit_count(n, S);
-  if (container_bytes < payload_offset(nu)) {
-    set_error("decode: container of %llu bytes is too short for %llu units",
-              (unsigned long long)container_bytes, (unsigned long long)nu);
-    return NZ_E_FORMAT;
-  }
-  LaunchGeom g;
-  int rc = decode_geometry(n, S, max_unit_words, g);
-  if (rc) return rc;
-  DecodeArgs a;
-  a.container = (const uint8_t *)container;
-  a.container_bytes = container_bytes;
-  a.frac = (const uint8_t *)frac;
-  a.n = n;
-  a.S = S;
-  a.n_units = (uint32_t)nu;
-  a.slot_bytes = g.slot_bytes;
-  a.lut_shift = g.lut_shift;
-  a.lut_bytes = g.lut_bytes;
-  a.ring_offset = g.ring_offset;
-  a.canon = canon;
-  a.out_bf16 = (uint16_t *)out_bf16;
-  a.out_exp = (uint8_t *)out_exp;
-  a.status = (uint32_t *)status;
-  if (!out_bf16) return launch_decode<7, false>(a, g, st);
-  switch (precision) {
-    case 0: return launch_decode<0, true>(a, g, st);
-    case 1: return launch_decode<1, true>(a, g, st);
-    case 3: return launch_decode<3, true>(a, g, st);
-    default: return launch_decode<7, true>(a, g, st);
-  }
+  HostItem it;
+  it.container = container;
+  it.container_bytes = container_bytes;
+  it.frac = frac;
+  it.n = n;
+  it.max_unit_words = max_unit_words;
+  it.out_bf16 = out_bf16;
+  it.out_exp = out_exp;
+  return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
 }  // namespace nz
@@ -898,4 +1029,45 @@ extern "C" int nz_decompress_bf16(const void *container, uint64_t container_byte
   return nz::decode_common(container, container_bytes, frac_in, n, precision, lane_symbols,
                            max_unit_words, canonical_nan, out_bf16, nullptr, status,
                            (cudaStream_t)stream);
+}
+
+extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_t count,
+                                        int precision, uint32_t lane_symbols, int canonical_nan,
+                                        void *status, void *stream) {
+  if (!nz::valid_precision(precision)) {
+    nz::set_error("nz_decompress_bf16_batch: precision must be 0, 1, 3 or 7 (got %d)", precision);
+    return NZ_E_ARG;
+  }
+  if (count == 0) return NZ_OK;
+  if (!items) {
+    nz::set_error("nz_decompress_bf16_batch: null item array");
+    return NZ_E_ARG;
+  }
+  constexpr uint32_t kChunk = 64;
+  nz::HostItem host[kChunk];
+  for (uint32_t base = 0; base < count; base += kChunk) {
+    const uint32_t m = count - base < kChunk ? count - base : kChunk;
+    for (uint32_t i = 0; i < m; ++i) {
+      const nz_decompress_item &it = items[base + i];
+      int rc = check_decode_args("nz_decompress_bf16_batch", it.container, it.n, lane_symbols);
+      if (rc) return rc;
+      if (it.n && (!it.out_bf16 || !it.frac_in || ((uintptr_t)it.out_bf16 & 15) ||
+                   ((uintptr_t)it.frac_in & 7))) {
+        nz::set_error("nz_decompress_bf16_batch: item %u: output must be 16-byte, fractions "
+                      "8-byte aligned", base + i);
+        return NZ_E_ARG;
+      }
+      host[i].container = it.container;
+      host[i].container_bytes = it.container_bytes;
+      host[i].frac = it.frac_in;
+      host[i].n = it.n;
+      host[i].max_unit_words = it.max_unit_words;
+      host[i].out_bf16 = it.out_bf16;
+      host[i].out_exp = nullptr;
+    }
+    int rc = nz::decode_many(host, m, precision, lane_symbols, canonical_nan, true, status,
+                             (cudaStream_t)stream);
+    if (rc) return rc;
+  }
+  return NZ_OK;
 }

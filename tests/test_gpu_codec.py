@@ -230,3 +230,49 @@ def test_argument_errors():
     assert L.nz_split_bf16(x.data_ptr() + 2, 8, 7, e.data_ptr(), e.data_ptr(), 0) == _lib.NZ_E_ARG
     assert L.nz_decode_exponents(e.data_ptr(), 64, 64, 12, 0, e.data_ptr(), 0, 0) == _lib.NZ_E_ARG
     assert L.nz_encode_exponents(e.data_ptr(), 64, 256, e.data_ptr(), 64, e.data_ptr(), 64, 0) == _lib.NZ_E_CAPACITY
+
+
+# ------------------------------------------------------------- batched decode
+@pytest.mark.parametrize("s", PRECISIONS)
+def test_batched_decompress_equals_single_calls(s):
+    from neuzip_b200 import _lib
+    L = A.lib()
+    S = O.default_lane_symbols(s)
+    sizes = [1 << 20, 300, 0, 70000, 8192 * 3, 4096 * 640, 9, 1 << 16, 123457, 2 << 20, 77]
+    tensors, comps, singles = [], [], []
+    for i, n in enumerate(sizes):
+        x = weights(max(n, 1), 900 + i)[:n].cuda().contiguous() if n else torch.empty(
+            0, dtype=torch.bfloat16, device="cuda")
+        tensors.append(x)
+        if n:
+            c, f, mw = A.compress(x, s, S)
+            out, status = A.decompress(c, f, n, s, S, mw, canon=True)
+            assert status == 0
+        else:
+            c = torch.zeros(16, dtype=torch.uint8, device="cuda")
+            f = torch.zeros(16, dtype=torch.uint8, device="cuda")
+            mw, out = 0, x
+        comps.append((c, f, mw))
+        singles.append(out)
+    items = (_lib.DecompressItem * len(sizes))()
+    raws, outs = [], []
+    for i, n in enumerate(sizes):
+        raw, out = A.guarded(2 * n, torch.bfloat16)
+        raws.append(raw)
+        outs.append(out)
+        c, f, mw = comps[i]
+        items[i].container = c.data_ptr()
+        items[i].container_bytes = c.numel()
+        items[i].frac_in = f.data_ptr()
+        items[i].n = n
+        items[i].max_unit_words = mw if i % 2 else 0
+        items[i].out_bf16 = out.data_ptr() if n else 0
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.nz_decompress_bf16_batch(items, len(sizes), s, S, 1, status.data_ptr(), A.stream()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for i, n in enumerate(sizes):
+        assert A.guards_intact(raws[i], 2 * n)
+        assert torch.equal(outs[i].view(torch.int16), singles[i].view(torch.int16)), (s, i, n)
+        if s == 7 and n:
+            assert torch.equal(outs[i].view(torch.int16), tensors[i].view(torch.int16))

@@ -155,3 +155,15 @@ def test_lossy_precision_error_bounds():
         m = neuzip.Manager(precision=precision)
         got = m.read(m.write(w))
         assert (got.float() - w.float()).abs().max().item() <= bound
+
+
+def test_read_many_matches_read():
+    m = neuzip.Manager(precision=3)
+    ws = [weights(shape, 40 + i) for i, shape in enumerate([(256, 256), (704, 256), (256, 704),
+                                                            (3, 5), (1024, 512)])]
+    hs = [m.write(w) for w in ws]
+    many = m.read_many(hs)
+    for h, t in zip(hs, many):
+        assert t.shape == m.meta_dict[h]
+        assert torch.equal(t, m.read(h))
+    m.check()
