@@ -378,6 +378,65 @@ __device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb,
   constexpr uint32_t kFracStride = 32u * (S + 1);
   constexpr bool kAsync = MERGE && (S == 7 || S == 3);
   constexpr int kAhead = 4;
+  if (MERGE && (S == 0 || S == 1) && (n_blocks & 3) == 0) {
+    // Narrow fractions: four blocks of a unit are 128 (s=0) or 256 (s=1) contiguous
+    // bytes, copied by the whole warp (4 or 8 bytes per lane) into a double-buffered
+    // ring one group of four blocks ahead; lanes then read their own 1 or 2 bytes.
+    constexpr uint32_t kLaneBytes = 4u * (S + 1);          // per lane and group
+    constexpr uint32_t kGroupBytes = 32u * kLaneBytes;     // per unit and group
+    const uint32_t lane_id = threadIdx.x & 31;
+    const uint32_t ring0 = ring - lane_id * 4;             // `ring` carries lane*4 for s<7
+    const uint32_t n_groups = n_blocks >> 2;
+    const uint8_t *ga = frac_a - (uint64_t)lane_id * (S + 1);   // unit base of the fractions
+    const uint8_t *gb = frac_b - (uint64_t)lane_id * (S + 1);
+    auto issue = [&](uint32_t g) {
+      const uint32_t dst = ring0 + (g & 1) * 1024 + lane_id * kLaneBytes;
+      const uint8_t *sa_ = ga + (uint64_t)g * kGroupBytes + lane_id * kLaneBytes;
+      const uint8_t *sb_ = gb + (uint64_t)g * kGroupBytes + lane_id * kLaneBytes;
+      if (S == 1) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(sa_) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 512), "l"(sb_) : "memory");
+      } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(sa_) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 512), "l"(sb_) : "memory");
+      }
+      frac_commit();
+    };
+    issue(0);
+    for (uint32_t g = 0; g < n_groups; ++g) {
+      __syncwarp();                       // everyone is done with the buffer about to be refilled
+      if (g + 1 < n_groups) {
+        issue(g + 1);
+        frac_wait<1>();
+      } else {
+        frac_wait<0>();
+      }
+      __syncwarp();                       // all lanes' copies of group g have landed
+      const uint32_t src = ring0 + (g & 1) * 1024 + lane_id * (S + 1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint64_t bits_a, bits_b;
+        if (S == 1) {
+          bits_a = lds_u16(src + k * 64);
+          bits_b = lds_u16(src + 512 + k * 64);
+        } else {
+          bits_a = lds_u8(src + k * 32);
+          bits_b = lds_u8(src + 512 + k * 32);
+        }
+        uint32_t ea[8], eb[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          ea[t] = decode_step(sa, lut);
+          eb[t] = decode_step(sb, lut);
+        }
+        store_block<S, CANON>(ea, bits_a, out_a + k * 256);
+        store_block<S, CANON>(eb, bits_b, out_b + k * 256);
+      }
+      out_a += 4 * 256;
+      out_b += 4 * 256;
+    }
+    return;
+  }
   uint64_t fa[kAhead] = {0, 0, 0, 0}, fb[kAhead] = {0, 0, 0, 0};
   if (kAsync) {
 #pragma unroll

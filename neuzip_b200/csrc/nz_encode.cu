@@ -95,72 +95,125 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
                                  uint32_t *__restrict__ enc_tab, uint32_t *__restrict__ misc,
                                  uint16_t *__restrict__ container_freq) {
   __shared__ int32_t f[256];
-  __shared__ uint64_t total_sh;
-  __shared__ uint32_t pb_sh;
+  __shared__ uint64_t red64[8];
+  __shared__ uint32_t red32[8];
+  __shared__ int32_t top_sh[8];
   const int t = threadIdx.x;  // 256 threads
-  if (t == 0) {
-    uint64_t total = 0;
-    uint32_t distinct = 0;
-    for (int i = 0; i < 256; ++i) {
-      total += hist[i];
-      distinct += hist[i] != 0;
-    }
-    total_sh = total;
-    pb_sh = distinct <= 32 ? 10u : (distinct <= 64 ? 11u : 12u);
+  const int lane = t & 31, wid = t >> 5;
+  const uint64_t h = hist[t];
+  // total count and number of distinct symbols
+  uint64_t tot = h;
+  uint32_t dis = h != 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    tot += __shfl_xor_sync(0xFFFFFFFFu, tot, o);
+    dis += __shfl_xor_sync(0xFFFFFFFFu, dis, o);
+  }
+  if (lane == 0) {
+    red64[wid] = tot;
+    red32[wid] = dis;
   }
   __syncthreads();
-  const uint64_t total = total_sh;
-  const uint32_t pb = pb_sh;
+  uint64_t total = 0;
+  uint32_t distinct = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    total += red64[w];
+    distinct += red32[w];
+  }
+  const uint32_t pb = distinct <= 32 ? 10u : (distinct <= 64 ? 11u : 12u);
   const uint32_t M = 1u << pb;
-  {
-    const uint64_t h = hist[t];
-    int32_t v = 0;
-    if (total == 0) {
-      v = (t == 0) ? (int32_t)M : 0;
-    } else if (h) {
-      const uint64_t q = (h * M + total / 2) / total;
-      v = q ? (int32_t)q : 1;
+  int32_t v = 0;
+  if (total == 0) {
+    v = (t == 0) ? (int32_t)M : 0;
+  } else if (h) {
+    const uint64_t q = (h * M + total / 2) / total;
+    v = q ? (int32_t)q : 1;
+  }
+  f[t] = v;
+  __syncthreads();
+  // block-wide helpers over f[]: sum, and arg-max with the lowest index on ties
+  auto block_sum = [&]() {
+    int32_t x = f[t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xFFFFFFFFu, x, o);
+    __syncthreads();
+    if (lane == 0) top_sh[wid] = x;
+    __syncthreads();
+    int32_t sum = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sum += top_sh[w];
+    return sum;
+  };
+  auto block_argmax = [&]() {
+    int32_t bv = f[t], bi = t;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const int32_t ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+      const int32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
     }
-    f[t] = v;
+    __syncthreads();
+    if (lane == 0) top_sh[wid] = bi;
+    __syncthreads();
+    int32_t best = top_sh[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+      const int32_t c = top_sh[w];
+      if (f[c] > f[best]) best = c;   // ascending w keeps the lowest index on ties
+    }
+    return best;
+  };
+  int32_t d = (int32_t)M - block_sum();
+  while (d != 0) {            // same verdict in every thread: all values come from shared memory
+    const int32_t top = block_argmax();
+    __syncthreads();
+    if (d > 0) {
+      if (t == 0) f[top] += d;
+      d = 0;
+    } else {
+      const int32_t room = f[top] - 1;
+      const int32_t take = (-d < room) ? -d : room;
+      __syncthreads();
+      if (t == 0) f[top] -= take;
+      d += take;
+    }
+    __syncthreads();
+  }
+  // an alphabet of one symbol: M-1 for it, 1 for its successor
+  const bool full = f[t] == (int32_t)M;
+  __syncthreads();
+  if (full) {
+    f[t] = (int32_t)M - 1;
+    f[(t + 1) & 255] = 1;
   }
   __syncthreads();
+  // cumulative starts by a two-level warp scan
+  const int32_t mine = f[t];
+  int32_t incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int32_t u = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += u;
+  }
+  if (lane == 31) top_sh[wid] = incl;
+  __syncthreads();
+  int32_t base = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w)
+    if (w < wid) base += top_sh[w];
+  const uint32_t cum = (uint32_t)(base + incl - mine);
+  enc_tab[t] = (uint32_t)mine | (cum << 16);
+  freq[t] = (uint16_t)mine;
+  container_freq[t] = (uint16_t)mine;
+  const int32_t pad = block_argmax();
   if (t == 0) {
-    int32_t sum = 0;
-    for (int i = 0; i < 256; ++i) sum += f[i];
-    int32_t d = (int32_t)M - sum;
-    while (d != 0) {
-      int top = 0;
-      for (int i = 1; i < 256; ++i)
-        if (f[i] > f[top]) top = i;
-      if (d > 0) {
-        f[top] += d;
-        d = 0;
-      } else {
-        const int32_t room = f[top] - 1;
-        const int32_t take = (-d < room) ? -d : room;
-        f[top] -= take;
-        d += take;
-      }
-    }
-    for (int i = 0; i < 256; ++i) {
-      if (f[i] == (int32_t)M) {
-        f[i] = (int32_t)M - 1;
-        f[(i + 1) & 255] = 1;
-        break;
-      }
-    }
-    uint32_t cum = 0, pad = 0;
-    for (int i = 0; i < 256; ++i) {
-      if (f[i] > f[pad]) pad = i;
-      enc_tab[i] = (uint32_t)f[i] | (cum << 16);
-      cum += f[i];
-    }
-    misc[0] = pad;
+    misc[0] = (uint32_t)pad;
     misc[1] = pb;
   }
-  __syncthreads();
-  freq[t] = (uint16_t)f[t];
-  container_freq[t] = (uint16_t)f[t];
 }
 
 // ------------------------------------------------------------------ encoder
@@ -177,7 +230,13 @@ encode_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t 
               uint32_t *__restrict__ unit_words, uint16_t *__restrict__ lane_len,
               uint16_t *__restrict__ lane_words) {
   __shared__ uint32_t tab[256];
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) tab[i] = enc_tab_g[i];
+  __shared__ uint32_t rcp[256];   // floor(2^32 / freq): quotient estimate, at most 1 too small
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    const uint32_t e = enc_tab_g[i];
+    tab[i] = e;
+    const uint32_t fr = e & 0xFFFFu;
+    rcp[i] = fr > 1 ? (uint32_t)((1ull << 32) / fr) : 0xFFFFFFFFu;
+  }
   __syncthreads();
   const uint32_t pad = misc[0];
   const uint32_t pb = misc[1];
@@ -219,7 +278,14 @@ encode_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t 
           ++emitted;
           x >>= 16;
         }
-        x = ((x / fr) << pb) + (x % fr) + cum;
+        // x / fr and x % fr without a division: the estimate is exact or one short
+        uint32_t q = __umulhi(x, rcp[s]);
+        uint32_t rem = x - q * fr;
+        if (rem >= fr) {
+          ++q;
+          rem -= fr;
+        }
+        x = (q << pb) + rem + cum;
       }
     }
     uint32_t words = emitted + 2;
@@ -261,20 +327,48 @@ scan_kernel(const uint32_t *__restrict__ unit_words, uint32_t n_units, uint64_t 
     s += w & ~kRawFlag;
     if (w & kRawFlag) ++r; else if (w > m) m = w;
   }
-  part[t] = s;
-  raw_cnt[t] = r;
-  max_w[t] = m;
+  // block-wide exclusive scan of s (and totals of r, max of m): warp scans, then
+  // one warp scans the 32 warp totals
+  const uint32_t lane = t & 31, wid = t >> 5;
+  uint64_t incl = s;
+  uint32_t rsum = r, mmax = m;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint64_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= (uint32_t)o) incl += v;
+    rsum += __shfl_xor_sync(0xFFFFFFFFu, rsum, o);
+    const uint32_t mo = __shfl_xor_sync(0xFFFFFFFFu, mmax, o);
+    if (mo > mmax) mmax = mo;
+  }
+  if (lane == 31) part[wid] = incl;
+  if (lane == 0) {
+    raw_cnt[wid] = rsum;
+    max_w[wid] = mmax;
+  }
   __syncthreads();
-  if (t == 0) {
-    uint64_t run = 0;
-    uint32_t rr = 0, mm = 0;
-    for (int i = 0; i < 1024; ++i) {
-      const uint64_t v = part[i];
-      part[i] = run;
-      run += v;
-      rr += raw_cnt[i];
-      if (max_w[i] > mm) mm = max_w[i];
+  if (wid == 0) {
+    uint64_t wt = part[lane], winc = wt;
+    uint32_t rr = raw_cnt[lane], mm = max_w[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint64_t v = __shfl_up_sync(0xFFFFFFFFu, winc, o);
+      if (lane >= (uint32_t)o) winc += v;
+      rr += __shfl_xor_sync(0xFFFFFFFFu, rr, o);
+      const uint32_t mo = __shfl_xor_sync(0xFFFFFFFFu, mm, o);
+      if (mo > mm) mm = mo;
     }
+    part[lane] = winc - wt;                // exclusive warp offsets
+    if (lane == 31) part[32] = winc;       // grand total
+    if (lane == 0) {
+      raw_cnt[0] = rr;
+      max_w[0] = mm;
+    }
+  }
+  __syncthreads();
+  const uint64_t my_start = part[wid] + incl - s;
+  if (t == 0) {
+    const uint64_t run = part[32];
+    const uint32_t rr = raw_cnt[0], mm = max_w[0];
     const uint64_t pay_off = payload_offset(n_units);
     Header h;
     h.magic = kMagic;
@@ -296,8 +390,7 @@ scan_kernel(const uint32_t *__restrict__ unit_words, uint32_t n_units, uint64_t 
     for (uint64_t b = kOffsetsOffset + 4ull * (n_units + 1); b < pay_off; ++b) container[b] = 0;
     for (uint64_t b = pay_off + run * 2; b < h.total_bytes; ++b) container[b] = 0;
   }
-  __syncthreads();
-  uint64_t run = part[t];
+  uint64_t run = my_start;
   uint32_t *offsets = reinterpret_cast<uint32_t *>(container + kOffsetsOffset);
   for (uint32_t u = lo; u < hi; ++u) {
     const uint32_t w = unit_words[u];
