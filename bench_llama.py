@@ -1,0 +1,115 @@
+#!/usr/bin/env python
+"""Model-level check of the codec: a random-init Llama-architecture model,
+dense vs. converted with neuzip.Manager (BASELINE configs 3 and 4 shapes).
+
+    python bench_llama.py --config 7b --prompt 128 --new 256 [--precision 7]
+
+Builds the model with linear weights N(0, 0.02) (transformers' initialiser;
+synthetic stand-in for the Llama checkpoints), times greedy decoding dense,
+converts it in place, times it again per-Linear and with layer-wise batched
+decode, and reports tokens/s, logits difference, token agreement and stored
+bytes as one JSON line.
+"""
+import argparse
+import json
+import time
+
+import torch
+
+CONFIGS = {
+    "tiny": dict(hidden_size=256, intermediate_size=704, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=4),
+    "1.3b": dict(hidden_size=2048, intermediate_size=5504, num_hidden_layers=24,
+                 num_attention_heads=16, num_key_value_heads=16),
+    "7b": dict(hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+               num_attention_heads=32, num_key_value_heads=32),
+}
+
+
+def timed_generate(model, ids, new_tokens):
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    with torch.no_grad():
+        out = model.generate(ids, max_new_tokens=new_tokens, min_new_tokens=new_tokens,
+                             do_sample=False, pad_token_id=0)
+    e1.record()
+    torch.cuda.synchronize()
+    return out, e0.elapsed_time(e1) * 1e-3, time.perf_counter() - t0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="7b", choices=sorted(CONFIGS))
+    ap.add_argument("--prompt", type=int, default=128)
+    ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--precision", type=int, default=7)
+    args = ap.parse_args()
+
+    import transformers
+    import neuzip
+    from neuzip_b200 import layerwise
+
+    cfg = transformers.LlamaConfig(vocab_size=32000, max_position_embeddings=4096,
+                                   rms_norm_eps=1e-5, **CONFIGS[args.config])
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16)
+    model.eval()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 32000, (args.batch, args.prompt), generator=g).cuda()
+
+    res = {"config": args.config, "precision": args.precision, "batch": args.batch,
+           "prompt": args.prompt, "new_tokens": args.new, "data": "synthetic"}
+    dense_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+    res["dense_param_bytes"] = dense_bytes
+
+    timed_generate(model, ids, 8)                                   # warm-up
+    with torch.no_grad():
+        ref_logits = model(ids).logits.float()
+    ref_out, t_first, _ = timed_generate(model, ids, args.new)
+    ref_out, t_gpu, _ = timed_generate(model, ids, args.new)      # second run: allocator and
+    res["dense_tok_s_first_run"] = args.batch * args.new / t_first  # library heuristics are warm
+    res["dense_tok_s"] = args.batch * args.new / t_gpu
+    torch.cuda.reset_peak_memory_stats()
+
+    manager = neuzip.Manager(precision=args.precision)
+    t0 = time.perf_counter()
+    manager.convert(model)
+    torch.cuda.synchronize()
+    res["convert_s"] = time.perf_counter() - t0
+    manager._be.release_scratch()
+    torch.cuda.empty_cache()
+    stored = manager.total_size()
+    converted_dense = sum(int(torch.Size(s).numel()) * 2 for s in manager.meta_dict.values())
+    res["converted_tensors"] = len(manager.meta_dict)
+    res["ratio_converted_weights"] = stored / converted_dense
+    res["model_bytes_after"] = dense_bytes - converted_dense + stored
+
+    timed_generate(model, ids, 8)
+    with torch.no_grad():
+        logits = model(ids).logits.float()
+    out, t_gpu, _ = timed_generate(model, ids, args.new)
+    out, t_gpu, _ = timed_generate(model, ids, args.new)
+    manager.check()
+    res["neuzip_tok_s"] = args.batch * args.new / t_gpu
+    res["max_abs_logit_diff"] = (logits - ref_logits).abs().max().item()
+    res["tokens_identical"] = bool(torch.equal(out, ref_out))
+
+    hooks = layerwise.attach(model, manager)
+    timed_generate(model, ids, 8)
+    out2, t_gpu, _ = timed_generate(model, ids, args.new)
+    out2, t_gpu, _ = timed_generate(model, ids, args.new)
+    manager.check()
+    res["neuzip_layerwise_tok_s"] = args.batch * args.new / t_gpu
+    res["layerwise_tokens_identical"] = bool(torch.equal(out2, ref_out))
+    res["layerwise_blocks"] = len(hooks) // 2
+    res["peak_memory_bytes_compressed_run"] = torch.cuda.max_memory_allocated()
+    res["ratio_vs_dense_tok_s"] = res["neuzip_layerwise_tok_s"] / res["dense_tok_s"]
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

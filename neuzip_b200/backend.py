@@ -185,6 +185,37 @@ class CodecBackend:
                 _stream()))
         return outs
 
+    def make_batch(self, names: Sequence[str], outs: Sequence[torch.Tensor]):
+        """Pre-build the argument block of a batched decode of `names` into the given
+        flat bf16 output tensors; returns an object for `run_batch`.  Lets a caller that
+        decodes the same tensors again and again (every forward of a layer) skip all
+        per-call Python work."""
+        entries = [self._cache[n] for n in names]
+        S = {e.lane_symbols for e in entries}
+        if len(S) != 1:
+            raise ValueError("a batch must share one lane_symbols value")
+        items = (_lib.DecompressItem * len(entries))()
+        for k, (e, out) in enumerate(zip(entries, outs)):
+            if out.numel() < e.numel or out.dtype != torch.bfloat16 or not out.is_cuda:
+                raise ValueError("output buffers must be CUDA bf16 tensors of at least numel elements")
+            items[k].container = _ptr(e.container)
+            items[k].container_bytes = e.container.numel()
+            items[k].frac_in = _ptr(e.fractions)
+            items[k].n = e.numel
+            items[k].max_unit_words = e.max_unit_words
+            items[k].out_bf16 = _ptr(out)
+        # keep the tensors alive as long as the batch exists
+        return (items, len(entries), S.pop(), [e.container for e in entries],
+                [e.fractions for e in entries], list(outs))
+
+    def run_batch(self, batch) -> None:
+        items, count, S = batch[0], batch[1], batch[2]
+        rc = self._lib.nz_decompress_bf16_batch(items, count, self.precision, S,
+                                                int(self.canonical_nan), _ptr(self._status),
+                                                _stream())
+        if rc:
+            _lib.check(rc)
+
     def size(self, name: str) -> int:
         """cuda/high_level.cu:208-221: stored bytes, 0 for an unknown name."""
         entry = self._cache.get(name)

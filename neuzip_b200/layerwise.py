@@ -1,0 +1,74 @@
+"""Layer-wise decode: one batched decompress per transformer block.
+
+The reference decompresses each weight inside its own Linear forward
+(neuzip/nn/linear.py:30-31 -> neuzip/nn/module.py:27-28), i.e. seven separate
+decodes per Llama block.  `attach` registers a forward pre-hook on every module
+that directly owns compressed Linears below it (a decoder block) which decodes
+all of them with one batched call - one kernel launch in which each matrix gets
+a share of the SMs - into a set of decode buffers shared by all blocks, and
+hands views of those buffers to the Linears; a forward hook takes them away
+again, so that backward (which runs the blocks in the opposite order) falls back
+to its own decode.  Only one block is ever held decoded.  Results are identical
+to the per-Linear path.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+
+from .nn import Linear
+
+
+def _compressed_linears(module: torch.nn.Module) -> List[Linear]:
+    return [m for m in module.modules() if isinstance(m, Linear)]
+
+
+def default_block_filter(module: torch.nn.Module) -> bool:
+    """A block = a module whose class name ends in 'DecoderLayer' / 'Block' /
+    'EncoderLayer' and that contains compressed Linears."""
+    name = type(module).__name__
+    return name.endswith(("DecoderLayer", "Block", "EncoderLayer")) and bool(_compressed_linears(module))
+
+
+def attach(model: torch.nn.Module, manager,
+           is_block: Optional[Callable[[torch.nn.Module], bool]] = None) -> List:
+    """Install the hooks; returns the hook handles (call .remove() on each to undo)."""
+    is_block = is_block or default_block_filter
+    backend = manager._be
+    blocks = [m for m in model.modules() if is_block(m)]
+    # shared decode buffers: slot k is as large as the k-th Linear of the largest block
+    sizes: List[int] = []
+    for block in blocks:
+        for k, lin in enumerate(_compressed_linears(block)):
+            n = int(torch.Size(lin._p._shape).numel())
+            if k == len(sizes):
+                sizes.append(n)
+            else:
+                sizes[k] = max(sizes[k], n)
+    buffers = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for n in sizes]
+    handles = []
+    for block in blocks:
+        params = [lin._p for lin in _compressed_linears(block)]
+        names = [p._handle for p in params]
+        if hasattr(backend, "make_batch"):
+            batch = backend.make_batch(names, buffers[:len(names)])
+            views = [buffers[k][:int(torch.Size(p._shape).numel())].view(p._shape)
+                     for k, p in enumerate(params)]
+
+            def pre(mod, args, _params=params, _views=views, _batch=batch):
+                backend.run_batch(_batch)
+                for p, v in zip(_params, _views):
+                    p._staged = v
+        else:   # a backend without batched decode (the pass-through one)
+            def pre(mod, args, _params=params, _names=names):
+                for p, w in zip(_params, manager.read_many(_names)):
+                    p._staged = w
+
+        def post(mod, args, output, _params=params):
+            for p in _params:
+                p._staged = None
+
+        handles.append(block.register_forward_pre_hook(pre))
+        handles.append(block.register_forward_hook(post))
+    return handles

@@ -21,6 +21,11 @@ class Linear(torch.nn.Module):
         return self._p
 
     def forward(self, x):
+        if not (torch.is_grad_enabled() and (x.requires_grad or self._p.requires_grad)):
+            # inference: same arithmetic without the autograd.Function round trip
+            if torch.is_autocast_enabled():
+                x = x.to(torch.get_autocast_gpu_dtype())
+            return self._p.linear(x, self.bias)
         return CompressedLinear.apply(x, self._p, self.bias)
 
     def extra_repr(self) -> str:

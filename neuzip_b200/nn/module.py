@@ -19,8 +19,15 @@ class Parameter(torch.nn.Parameter):
 
     @torch.no_grad()
     def __call__(self) -> torch.Tensor:
+        staged = getattr(self, "_staged", None)
+        if staged is not None:
+            return staged
         w = self._manager.read(self._handle).reshape(self._shape)
         return w.to(self.device).requires_grad_(False)
 
     def linear(self, inputs, bias=None):
+        staged = getattr(self, "_staged", None)
+        if staged is not None:
+            # a layer-wise prefetch (neuzip_b200.layerwise) already decoded this weight
+            return torch.nn.functional.linear(inputs, staged, bias)
         return self._manager.linear(self._handle, inputs, bias).to(self.device)

@@ -167,3 +167,37 @@ def test_read_many_matches_read():
         assert t.shape == m.meta_dict[h]
         assert torch.equal(t, m.read(h))
     m.check()
+
+
+def test_layerwise_prefetch_gives_identical_outputs_and_gradients():
+    transformers = pytest.importorskip("transformers")
+    from neuzip_b200 import layerwise
+    cfg = transformers.LlamaConfig(vocab_size=256, hidden_size=128, intermediate_size=352,
+                                   num_hidden_layers=3, num_attention_heads=4,
+                                   num_key_value_heads=4, max_position_embeddings=64)
+    torch.manual_seed(1)
+    model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16).cuda()
+    m = neuzip.Manager()
+    m.convert(model)
+    ids = torch.randint(0, 256, (2, 12), device="cuda")
+    with torch.no_grad():
+        ref = model(ids).logits
+    loss = model(ids, labels=ids).loss
+    loss.backward()
+    ref_grads = [p._gradient.clone() for p in model.parameters() if hasattr(p, "_gradient")]
+    for p in model.parameters():
+        if hasattr(p, "_gradient"):
+            p._gradient = None
+    hooks = layerwise.attach(model, m)
+    assert len(hooks) == 6
+    with torch.no_grad():
+        got = model(ids).logits
+    assert torch.equal(got, ref)
+    model(ids, labels=ids).loss.backward()           # backward decodes on its own
+    grads = [p._gradient for p in model.parameters() if hasattr(p, "_gradient")]
+    assert len(grads) == len(ref_grads) == 21
+    for a, b in zip(grads, ref_grads):
+        assert torch.equal(a, b)
+    for h in hooks:
+        h.remove()
+    m.check()
