@@ -39,14 +39,116 @@ def timed_generate(model, ids, new_tokens):
     return out, e0.elapsed_time(e1) * 1e-3, time.perf_counter() - t0
 
 
+def train_mode(args):
+    """BASELINE config 4 shape: AdamW training with lossless compressed weights,
+    per-layer decode in forward and backward, data-parallel over the ranks."""
+    import os
+    import torch.distributed as dist
+    import transformers
+    import neuzip
+    from neuzip_b200.optim import CompressedAdamW
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = transformers.LlamaConfig(vocab_size=32000, max_position_embeddings=4096,
+                                   rms_norm_eps=1e-5, **CONFIGS[args.config])
+
+    def build():
+        torch.manual_seed(0)
+        with torch.device("cuda"):
+            return transformers.LlamaForCausalLM(cfg).to(torch.bfloat16)
+
+    g = torch.Generator().manual_seed(100 + rank)
+    ids = torch.randint(0, 32000, (args.batch, args.seq), generator=g).cuda()
+
+    def run(model, opt, steps, warmup):
+        times = []
+        for it in range(warmup + steps):
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            loss = model(ids, labels=ids).loss
+            loss.backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(e0.elapsed_time(e1) * 1e-3)
+        t = sum(times) / len(times)
+        if world > 1:
+            tt = torch.tensor([t], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
+        return t, float(loss.item())
+
+    res = {"mode": "train", "config": args.config, "batch_per_gpu": args.batch, "seq": args.seq,
+           "n_gpus": world, "steps": args.steps, "data": "synthetic", "precision": args.precision}
+    tokens = world * args.batch * args.seq
+
+    if not args.skip_dense:
+        dense = build()
+        if world > 1:
+            dense_ddp = torch.nn.parallel.DistributedDataParallel(dense, device_ids=[local])
+        else:
+            dense_ddp = dense
+        opt = torch.optim.AdamW(dense.parameters(), lr=1e-4)
+        t, loss = run(dense_ddp, opt, args.steps, 2)
+        res["dense_tok_s"] = tokens / t
+        res["dense_loss"] = loss
+        res["dense_peak_bytes"] = torch.cuda.max_memory_allocated()
+        del dense, dense_ddp, opt
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+
+    model = build()
+    manager = neuzip.Manager(precision=args.precision)
+    manager.convert(model)
+    torch.cuda.empty_cache()
+    # moments in bf16, as torch.optim.AdamW keeps them for bf16 parameters
+    opt = CompressedAdamW(model.parameters(), lr=1e-4, state_dtype=torch.bfloat16)
+    t, loss = run(model, opt, args.steps, 2)
+    manager.check()
+    res["neuzip_tok_s"] = tokens / t
+    res["neuzip_loss"] = loss
+    res["neuzip_peak_bytes"] = torch.cuda.max_memory_allocated()
+    if "dense_tok_s" in res:
+        res["ratio_vs_dense_tok_s"] = res["neuzip_tok_s"] / res["dense_tok_s"]
+    if world > 1:
+        # replicas must hold bit-identical compressed weights after the updates
+        h = list(manager.meta_dict)[len(manager.meta_dict) // 2]
+        w = manager.read(h).view(torch.int16).to(torch.int64).sum().reshape(1)
+        lo, hi = w.clone(), w.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        res["replicas_identical"] = bool((lo == hi).item())
+    if rank == 0:
+        print(json.dumps(res))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--train", action="store_true")
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--skip-dense", action="store_true")
     ap.add_argument("--config", default="7b", choices=sorted(CONFIGS))
     ap.add_argument("--prompt", type=int, default=128)
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--precision", type=int, default=7)
     args = ap.parse_args()
+    if args.train:
+        return train_mode(args)
 
     import transformers
     import neuzip

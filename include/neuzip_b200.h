@@ -170,6 +170,18 @@ int nz_decompress_bf16(const void *container, uint64_t container_bytes,
                        int canonical_nan, void *out_bf16, void *status,
                        void *stream);
 
+/* Fused AdamW step on a decoded bf16 weight (in place): m and v are fp32 or
+ * bf16 arrays of n elements (state_is_bf16), `step` counts from 1, the gradient
+ * is multiplied by grad_scale first (1/world_size after a sum all-reduce).
+ * w <- w*(1 - lr*wd) - lr/(1-b1^t) * m / (sqrt(v/(1-b2^t)) + eps), all in fp32,
+ * rounded to bf16 once.  It is the update between the read and the write of
+ * the reference's in-backward step, which uses plain SGD there.
+ * Reference: compressed_lomo_hook, neuzip/__init__.py:25-35. */
+int nz_adamw_bf16(void *weight_bf16, const void *grad_bf16, void *exp_avg,
+                  void *exp_avg_sq, uint64_t n, int state_is_bf16, float lr,
+                  float beta1, float beta2, float eps, float weight_decay,
+                  uint32_t step, float grad_scale, void *stream);
+
 /* One tensor of a batched decompress. */
 typedef struct nz_decompress_item {
   const void *container;     /* NZR1 container, 16-byte aligned            */

@@ -56,6 +56,9 @@ class DecompressItem(ctypes.Structure):
                 ("max_unit_words", _u32), ("reserved", _u32), ("out_bf16", _vp)]
 
 
+_f32 = ctypes.c_float
+SIGNATURES["nz_adamw_bf16"] = (_int, [_vp, _vp, _vp, _vp, _u64, _int, _f32, _f32, _f32, _f32, _f32,
+                                       _u32, _f32, _vp])
 SIGNATURES["nz_decompress_bf16_batch"] = (
     _int, [ctypes.POINTER(DecompressItem), _u32, _int, _u32, _int, _vp, _vp])
 

@@ -1,0 +1,104 @@
+"""AdamW for models whose Linear weights are compressed.
+
+The reference only ships an in-backward SGD step for compressed parameters
+(`compressed_lomo_hook`, neuzip/__init__.py:25-35: decompress, add -lr * grad,
+recompress).  This optimiser keeps that read -> update -> write shape and adds
+what BASELINE's training configuration asks for: AdamW moments (fp32, kept
+uncompressed) and, under torch.distributed, an all-reduce of each compressed
+weight's gradient.  The reference accumulates that gradient in the side
+attribute `_gradient` (neuzip/ops/linear.py:37-40), which DDP never sees, so its
+data-parallel replicas drift apart; here the all-reduce is started from a
+post-accumulate-grad hook as soon as a layer's backward has produced the
+gradient, and `step()` waits for it.  Replicas stay bit-identical because the
+codec is deterministic.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .nn import Parameter
+
+
+class CompressedAdamW:
+    def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-4,
+                 betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 process_group=None, overlap_allreduce: bool = True,
+                 state_dtype: torch.dtype = torch.float32) -> None:
+        params = list(params)
+        self.compressed: List[Parameter] = [p for p in params if isinstance(p, Parameter)]
+        plain = [p for p in params if not isinstance(p, Parameter) and p.requires_grad]
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.group = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.plain = torch.optim.AdamW(plain, lr=lr, betas=betas, eps=eps,
+                                       weight_decay=weight_decay) if plain else None
+        self.state: Dict[int, dict] = {}
+        self.steps = 0
+        self.state_dtype = state_dtype
+        from . import _lib
+        self._lib_mod = _lib
+        self._lib = _lib.load()
+        self._pending: Dict[int, object] = {}
+        self._hooks = []
+        if self.world > 1 and overlap_allreduce:
+            for p in self.compressed:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._start_allreduce))
+
+    # gradient of a compressed weight is ready: start summing it over the ranks
+    def _start_allreduce(self, p: Parameter) -> None:
+        if p._gradient is not None and id(p) not in self._pending:
+            self._pending[id(p)] = dist.all_reduce(p._gradient, group=self.group, async_op=True)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for p in self.compressed:
+            p._gradient = None
+            p.grad = None
+        if self.plain is not None:
+            self.plain.zero_grad(set_to_none=set_to_none)
+
+    @torch.no_grad()
+    def step(self) -> None:
+        self.steps += 1
+        b1, b2 = self.betas
+        if self.world > 1 and self.plain is not None:
+            for group in self.plain.param_groups:
+                for q in group["params"]:
+                    if q.grad is not None:
+                        dist.all_reduce(q.grad, group=self.group)
+                        q.grad.div_(self.world)
+        stream = torch.cuda.current_stream().cuda_stream
+        for p in self.compressed:
+            g = p._gradient
+            if g is None:
+                continue
+            if self.world > 1:
+                work = self._pending.pop(id(p), None)
+                if work is None:
+                    dist.all_reduce(g, group=self.group)
+                else:
+                    work.wait()
+            g = g.contiguous()
+            if g.dtype != torch.bfloat16:
+                g = g.to(torch.bfloat16)
+            st = self.state.get(id(p))
+            if st is None:
+                st = {"m": torch.zeros(g.shape, dtype=self.state_dtype, device=g.device),
+                      "v": torch.zeros(g.shape, dtype=self.state_dtype, device=g.device)}
+                self.state[id(p)] = st
+            w = p()                                                    # decode (bf16, contiguous)
+            self._lib_mod.check(self._lib.nz_adamw_bf16(
+                w.data_ptr(), g.data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(), w.numel(),
+                int(self.state_dtype == torch.bfloat16), self.lr, b1, b2, self.eps,
+                self.weight_decay, self.steps, 1.0 / self.world, stream))
+            p._manager.write(w, p._handle)                             # recompress in place
+            p._gradient = None
+            p.grad = None
+        if self.plain is not None:
+            self.plain.step()
+
+    def state_bytes(self) -> int:
+        return sum(2 * s["m"].numel() * s["m"].element_size() for s in self.state.values())

@@ -201,3 +201,33 @@ def test_layerwise_prefetch_gives_identical_outputs_and_gradients():
     for h in hooks:
         h.remove()
     m.check()
+
+
+def test_compressed_adamw_matches_a_dense_restatement():
+    from neuzip_b200.optim import CompressedAdamW
+    torch.manual_seed(2)
+    lin = torch.nn.Linear(48, 32, bias=True).to(torch.bfloat16)
+    w = lin.weight.data.clone().cuda()
+    m = neuzip.Manager()
+    model = m.convert(torch.nn.Sequential(lin)).cuda()
+    opt = CompressedAdamW(model.parameters(), lr=1e-2, weight_decay=0.1)
+    mom = torch.zeros(32, 48, device="cuda")
+    var = torch.zeros(32, 48, device="cuda")
+    for step in range(1, 4):
+        x = torch.randn(6, 48, device="cuda", dtype=torch.bfloat16)
+        y = model(x)
+        gy = torch.randn_like(y)
+        y.backward(gy)
+        g = torch.mm(gy.t(), x).float()
+        opt.step()
+        opt.zero_grad()
+        mom.mul_(0.9).add_(g, alpha=0.1)
+        var.mul_(0.999).addcmul_(g, g, value=0.001)
+        wf = w.float() * (1 - 1e-2 * 0.1)
+        wf.addcdiv_(mom, (var / (1 - 0.999 ** step)).sqrt() + 1e-8, value=-1e-2 / (1 - 0.9 ** step))
+        w = wf.to(torch.bfloat16)
+        # fused kernel vs. this restatement: same formula, fp32 throughout; allow one bf16 ulp
+        got = model[0]._p()
+        assert (got.float() - w.float()).abs().max().item() <= 2.0 ** -8 * w.float().abs().max().item()
+        w = got.clone()
+    m.check()
