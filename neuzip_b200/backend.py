@@ -247,6 +247,30 @@ class CodecBackend:
         _lib.check(self._lib.nz_split_bf16(_ptr(flat), n, 7, _ptr(exp), _ptr(frac), _stream()))
         return [exp, frac]
 
+    # -- serialisation ----------------------------------------------------
+    def export_entry(self, name: str) -> dict:
+        """The stored form of one tensor as CPU tensors plus the numbers needed to
+        decode it; what `nn.Linear.get_extra_state` puts into a state_dict."""
+        e = self._cache[name]
+        return {"format": "NZR1", "precision": self.precision, "numel": e.numel,
+                "lane_symbols": e.lane_symbols, "max_unit_words": e.max_unit_words,
+                "container": e.container.cpu(), "fractions": e.fractions.cpu()}
+
+    def import_entry(self, name: str, blob: dict) -> None:
+        """Inverse of `export_entry`: the compressed bytes go straight to the GPU,
+        no bf16 copy of the tensor is ever materialised."""
+        if blob.get("format") != "NZR1" or int(blob["precision"]) != self.precision:
+            raise ValueError("checkpoint entry does not match this manager "
+                             f"(format {blob.get('format')!r}, precision {blob.get('precision')})")
+        self._ensure_device()
+        container = blob["container"].to(device="cuda", dtype=torch.uint8).contiguous()
+        fractions = blob["fractions"].to(device="cuda", dtype=torch.uint8).contiguous()
+        n = int(blob["numel"])
+        if fractions.numel() != int(self._lib.nz_frac_bytes(n, self.precision)):
+            raise ValueError("checkpoint entry: fraction stream has the wrong length")
+        self._cache[name] = _Entry(n, torch.bfloat16, int(blob["lane_symbols"]),
+                                   int(blob["max_unit_words"]), container, fractions)
+
     # -- extras -----------------------------------------------------------
     def erase(self, name: str) -> None:
         self._cache.pop(name, None)

@@ -112,6 +112,20 @@ class Manager:
             flats = [self._be.read(h) for h in handles]
         return [t.requires_grad_(False).reshape(self.meta_dict[h]) for t, h in zip(flats, handles)]
 
+    def export_entry(self, handle: str) -> dict:
+        """Stored bytes + metadata of a handle (for checkpoints)."""
+        blob = self._be.export_entry(handle)
+        blob["shape"] = tuple(self.meta_dict[handle])
+        return blob
+
+    def import_entry(self, blob: dict, handle: Optional[str] = None) -> str:
+        """Register compressed bytes produced by `export_entry` under a handle."""
+        if handle is None:
+            handle = str(len(self.meta_dict))
+        self.meta_dict[handle] = torch.Size(blob["shape"])
+        self._be.import_entry(handle, blob)
+        return handle
+
     def check(self) -> None:
         """Raise if any decode so far flagged a malformed container."""
         if hasattr(self._be, "check"):

@@ -28,6 +28,19 @@ class Linear(torch.nn.Module):
             return self._p.linear(x, self.bias)
         return CompressedLinear.apply(x, self._p, self.bias)
 
+    # The reference's state_dict of a converted model only holds the zero-size
+    # placeholder (neuzip/nn/module.py:13), so saving it loses the weights.  Here the
+    # compressed bytes travel as the module's extra state: a checkpoint of a converted
+    # model holds containers + fractions and loads without a bf16 staging copy.
+    def get_extra_state(self):
+        return self._p._manager.export_entry(self._p._handle)
+
+    def set_extra_state(self, state):
+        if state is None:
+            return
+        self._p._manager.import_entry(state, self._p._handle)
+        self._p._shape = torch.Size(state["shape"])
+
     def extra_repr(self) -> str:
         return (f"! in_features={self.in_features}, out_features={self.out_features}, "
                 f"bias={self.bias is not None}")

@@ -38,6 +38,17 @@ class OracleBackend:
     def linear_without_bias(self, handle, inputs, shape):
         return torch.matmul(inputs, self.read(handle).view(*shape).t())
 
+    def export_entry(self, handle):
+        n, cont, frac = self.store[handle]
+        return {"format": "NZR1", "precision": self.precision, "numel": n,
+                "lane_symbols": O.default_lane_symbols(self.precision), "max_unit_words": 0,
+                "container": torch.from_numpy(cont.copy()), "fractions": torch.from_numpy(frac.copy())}
+
+    def import_entry(self, handle, blob):
+        assert blob["format"] == "NZR1" and blob["precision"] == self.precision
+        self.store[handle] = (int(blob["numel"]), blob["container"].numpy().copy(),
+                              blob["fractions"].numpy().copy())
+
     def split(self, tensor):
         bits = tensor.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16).reshape(-1)
         e, f = O.split(bits, 7)

@@ -231,3 +231,28 @@ def test_compressed_adamw_matches_a_dense_restatement():
         assert (got.float() - w.float()).abs().max().item() <= 2.0 ** -8 * w.float().abs().max().item()
         w = got.clone()
     m.check()
+
+
+def test_checkpoint_of_converted_model_round_trips_on_gpu(tmp_path):
+    torch.manual_seed(5)
+    def make():
+        return torch.nn.Sequential(torch.nn.Linear(96, 64, bias=True), torch.nn.ReLU(),
+                                   torch.nn.Linear(64, 32, bias=False)).to(torch.bfloat16)
+    src = make()
+    m1 = neuzip.Manager(precision=3)
+    m1.convert(src)
+    src.cuda()
+    x = torch.randn(4, 96, device="cuda", dtype=torch.bfloat16)
+    expect = src(x)
+    torch.save(src.state_dict(), tmp_path / "c.pt")
+    dst = make()
+    m2 = neuzip.Manager(precision=3)
+    m2.convert(dst)
+    dst.cuda()
+    dst.load_state_dict(torch.load(tmp_path / "c.pt", weights_only=False))
+    assert torch.equal(dst(x), expect)
+    m2.check()
+    wrong = neuzip.Manager(precision=7)
+    other = wrong.convert(make()).cuda()
+    with pytest.raises(Exception):
+        other.load_state_dict(torch.load(tmp_path / "c.pt", weights_only=False))

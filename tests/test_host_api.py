@@ -204,3 +204,25 @@ def test_dummy_backend_api():
     be = neuzip.binding.DummyBackend()
     for meth in ("write", "read", "size", "linear", "linear_without_bias"):
         assert callable(getattr(be, meth))
+
+
+def test_state_dict_round_trip_keeps_the_compressed_weights(tmp_path):
+    torch.manual_seed(3)
+    src = Tiny().to(torch.bfloat16)
+    ids = torch.randint(0, 20, (2, 5))
+    expect = src(ids)
+    m1 = cpu_manager()
+    m1.convert(src)
+    sd = src.state_dict()
+    assert "block.0._extra_state" in sd and sd["block.0._p"].numel() == 0
+    assert sd["block.0._extra_state"]["container"].dtype == torch.uint8
+    path = tmp_path / "ckpt.pt"
+    torch.save(sd, path)
+    # a fresh model with different weights, converted, then loaded from the checkpoint
+    torch.manual_seed(4)
+    dst = Tiny().to(torch.bfloat16)
+    m2 = cpu_manager()
+    m2.convert(dst)
+    assert not torch.equal(dst(ids), expect)
+    dst.load_state_dict(torch.load(path, weights_only=False))
+    assert torch.equal(dst(ids), expect)
