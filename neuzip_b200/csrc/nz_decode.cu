@@ -455,41 +455,42 @@ __device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb,
         fb[k] = load_frac<S>(frac_b + k * kFracStride);
       }
   }
-  for (uint32_t b = 0; b < n_blocks; b += kAhead) {
-#pragma unroll
-    for (int k = 0; k < kAhead; ++k) {
-      if (b + k < n_blocks) {
-        uint64_t bits_a = fa[k], bits_b = fb[k];
-        if (kAsync) {
-          // block b+k+3 goes into the ring slot that block b+k-1 has left
-          if (b + k + 3 < n_blocks) {
-            frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes, frac_a + (k + 3) * kFracStride);
-            frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes + 256,
-                          frac_b + (k + 3) * kFracStride);
-          }
-          frac_commit();
-          frac_wait<3>();
-          bits_a = frac_from_ring<S>(ring + k * kRingSlotBytes);
-          bits_b = frac_from_ring<S>(ring + k * kRingSlotBytes + 256);
-        } else if (MERGE && b + kAhead + k < n_blocks) {
-          fa[k] = load_frac<S>(frac_a + (kAhead + k) * kFracStride);
-          fb[k] = load_frac<S>(frac_b + (kAhead + k) * kFracStride);
-        }
-        uint32_t ea[8], eb[8];
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          ea[t] = decode_step(sa, lut);
-          eb[t] = decode_step(sb, lut);
-        }
-        if (MERGE) {
-          store_block<S, CANON>(ea, bits_a, out_a + k * 256);
-          store_block<S, CANON>(eb, bits_b, out_b + k * 256);
-        } else {
-          store_exp_block(ea, exp_a + k * 256);
-          store_exp_block(eb, exp_b + k * 256);
-        }
+  // One block of both units: fetch the fractions of block b+k (and start the copy
+  // for block b+k+3), decode 8 symbols of each chain, merge, store.  `kGuard`
+  // is false when the block count is a multiple of four and nothing needs testing
+  // except the end of the prefetch.
+  auto one_block = [&](uint32_t b, int k, bool guard) {
+    if (guard && !(b + k < n_blocks)) return;
+    uint64_t bits_a = fa[k], bits_b = fb[k];
+    if (kAsync) {
+      // block b+k+3 goes into the ring slot that block b+k-1 has left
+      if (b + k + 3 < n_blocks) {
+        frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes, frac_a + (k + 3) * kFracStride);
+        frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes + 256, frac_b + (k + 3) * kFracStride);
       }
+      frac_commit();
+      frac_wait<3>();
+      bits_a = frac_from_ring<S>(ring + k * kRingSlotBytes);
+      bits_b = frac_from_ring<S>(ring + k * kRingSlotBytes + 256);
+    } else if (MERGE && b + kAhead + k < n_blocks) {
+      fa[k] = load_frac<S>(frac_a + (kAhead + k) * kFracStride);
+      fb[k] = load_frac<S>(frac_b + (kAhead + k) * kFracStride);
     }
+    uint32_t ea[8], eb[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      ea[t] = decode_step(sa, lut);
+      eb[t] = decode_step(sb, lut);
+    }
+    if (MERGE) {
+      store_block<S, CANON>(ea, bits_a, out_a + k * 256);
+      store_block<S, CANON>(eb, bits_b, out_b + k * 256);
+    } else {
+      store_exp_block(ea, exp_a + k * 256);
+      store_exp_block(eb, exp_b + k * 256);
+    }
+  };
+  auto advance = [&]() {
     if (MERGE) {
       frac_a += kAhead * kFracStride;
       frac_b += kAhead * kFracStride;
@@ -498,6 +499,19 @@ __device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb,
     } else {
       exp_a += kAhead * 256;
       exp_b += kAhead * 256;
+    }
+  };
+  if ((n_blocks & 3) == 0) {
+    for (uint32_t b = 0; b < n_blocks; b += kAhead) {
+#pragma unroll
+      for (int k = 0; k < kAhead; ++k) one_block(b, k, false);
+      advance();
+    }
+  } else {
+    for (uint32_t b = 0; b < n_blocks; b += kAhead) {
+#pragma unroll
+      for (int k = 0; k < kAhead; ++k) one_block(b, k, true);
+      advance();
     }
   }
   if (kAsync) frac_wait<0>();
