@@ -98,6 +98,7 @@ struct LutView {
   uint32_t stride;  // bytes between slots (4 x copies)
   uint32_t pb;      // probability bits
   uint32_t one, two, k64k;  // 1, 2 and 65536 in registers the compiler cannot fold
+  uint32_t neg4096;         // -4096 likewise
 };
 
 // One symbol.  Returns the table entry (symbol | bias << 8 | freq << 20); the
@@ -116,10 +117,10 @@ __device__ __forceinline__ uint32_t decode_step(LaneState &st, const LutView &lv
       "mad.lo.u32 a, a, %6, %4;\n\t"         // slot * stride + lane's table base
       "ld.shared.u32 %0, [a];\n\t"
       "shr.u32 q, %1, %7;\n\t"
+      "mad.lo.u32 q, q, %8, %11;\n\t"        // q - 4096 (see below), on the FMA pipe
       "shr.u32 f, %0, 20;\n\t"
-      "shr.u32 b, %0, 8;\n\t"
-      "and.b32 b, b, 4095;\n\t"
-      "mad.lo.u32 %1, f, q, b;\n\t"
+      "shr.u32 b, %0, 8;\n\t"                // freq << 12 | bias
+      "mad.lo.u32 %1, f, q, b;\n\t"          // f*(q-4096) + (f*4096 + bias) = f*q + bias (mod 2^32)
       "setp.lt.u32 r, %1, 65536;\n\t"
       "@r mad.lo.u32 %1, %1, %9, %3;\n\t"    // x = x * 65536 + w
       "@r mad.lo.u32 %2, %8, %10, %2;\n\t"   // p += 2
@@ -127,7 +128,7 @@ __device__ __forceinline__ uint32_t decode_step(LaneState &st, const LutView &lv
       "}"
       : "=&r"(ent), "+r"(st.x), "+r"(st.p), "+r"(st.w)
       : "r"(lv.base), "r"(lv.mask), "r"(lv.stride), "r"(lv.pb), "r"(lv.one), "r"(lv.k64k),
-        "r"(lv.two));
+        "r"(lv.two), "r"(lv.neg4096));
   return ent;
 }
 
@@ -790,6 +791,7 @@ decode_kernel(const BatchArgs batch) {
   lv.one = a.S ? 1u : 0u;
   lv.two = lv.one << 1;
   lv.k64k = lv.one << 16;
+  lv.neg4096 = 0u - (lv.one << 12);
   uint32_t *lut_w = reinterpret_cast<uint32_t *>(smem);
   const uint32_t wsh = row_shift - 2;                     // log2 of the words per slot row
   for (uint32_t sym = warp; sym < 256; sym += n_warps) {
