@@ -224,34 +224,77 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
 // decoder order.
 constexpr int kEncWarps = 4;
 
+// One symbol of one lane, in PTX to keep it short: the symbol is byte `sel & 3`
+// of `src`; its 16-byte table entry holds {threshold, reciprocal, -freq, cum}.
+//   if (x >= threshold) { slice[max(idx, 1)] = low16(x); --idx; x >>= 16; }
+//   q = umulhi(x, rcp); rem = x - q*freq; if (rem >= freq) { ++q; rem -= freq; }
+//   x = q*M + rem + cum
+// idx is signed and simply keeps counting down: once it is below 2 the lane has
+// used the two places kept for its final state, the writes pile up harmlessly on
+// place 1 and the count of emitted words (cap - 1 - idx) stays exact, which is how
+// the caller sees the overflow.  The quotient estimate is exact or one short
+// because rcp = floor(2^32 / freq).
+__device__ __forceinline__ void encode_step(uint32_t &x, int32_t &idx, uint32_t src, uint32_t sel,
+                                            uint32_t tab_addr, uint16_t *slice, uint32_t pow_m) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 s, a, xm, rc, nf, cm, q, r0, r1, j;\n\t"
+      ".reg .b64 ad;\n\t"
+      ".reg .pred p, g;\n\t"
+      "prmt.b32 s, %2, 0, %3;\n\t"
+      "mad.lo.u32 a, s, 16, %4;\n\t"
+      "ld.shared.v4.u32 {xm, rc, nf, cm}, [a];\n\t"
+      "setp.ge.u32 p, %0, xm;\n\t"
+      "max.s32 j, %1, 1;\n\t"
+      "@p mad.wide.u32 ad, j, 2, %5;\n\t"
+      "@p st.global.u16 [ad], %0;\n\t"
+      "@p shr.u32 %0, %0, 16;\n\t"
+      "@p sub.s32 %1, %1, 1;\n\t"
+      "mul.hi.u32 q, %0, rc;\n\t"
+      "mad.lo.u32 r0, q, nf, %0;\n\t"         // x - q*freq
+      "add.u32 r1, r0, nf;\n\t"               // ... - freq
+      "setp.ge.s32 g, r1, 0;\n\t"             // estimate one short?
+      "@g add.u32 q, q, 1;\n\t"
+      "@g mov.b32 r0, r1;\n\t"
+      "add.u32 r0, r0, cm;\n\t"
+      "mad.lo.u32 %0, q, %6, r0;\n\t"
+      "}"
+      : "+r"(x), "+r"(idx)
+      : "r"(src), "r"(sel), "r"(tab_addr), "l"(slice), "r"(pow_m));
+}
+
 __global__ void __launch_bounds__(kEncWarps * 32)
 encode_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t n_units,
               const uint32_t *__restrict__ enc_tab_g, const uint32_t *__restrict__ misc,
               uint32_t *__restrict__ unit_words, uint16_t *__restrict__ lane_len,
               uint16_t *__restrict__ lane_words) {
-  __shared__ uint32_t tab[256];
-  __shared__ uint32_t rcp[256];   // floor(2^32 / freq): quotient estimate, at most 1 too small
+  // per symbol: renormalisation threshold, reciprocal, minus frequency, cumulative start
+  __shared__ uint4 tab[256];
+  const uint32_t pb = misc[1];
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {
     const uint32_t e = enc_tab_g[i];
-    tab[i] = e;
     const uint32_t fr = e & 0xFFFFu;
-    rcp[i] = fr > 1 ? (uint32_t)((1ull << 32) / fr) : 0xFFFFFFFFu;
+    // floor(2^32 / freq): the quotient estimate it gives is exact or one short
+    const uint32_t rc = fr > 1 ? (uint32_t)((1ull << 32) / fr) : 0xFFFFFFFFu;
+    tab[i] = make_uint4(fr << (32 - pb), rc, 0u - fr, e >> 16);
   }
   __syncthreads();
   const uint32_t pad = misc[0];
-  const uint32_t pb = misc[1];
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t lenq = len_quantum(S);
   const uint32_t cap = lane_cap_words(S);
   const uint64_t U = 32ull * S;
+  const uint32_t tab_addr = (uint32_t)__cvta_generic_to_shared(tab);
+  const uint32_t pow_m = 1u << pb;
   for (uint32_t u = blockIdx.x * kEncWarps + (threadIdx.x >> 5); u < n_units;
        u += gridDim.x * kEncWarps) {
     const uint64_t first = (uint64_t)u * U;
     const uint64_t count = (n - first < U) ? (n - first) : U;
     uint16_t *mine = lane_words + ((uint64_t)u * 32 + lane) * cap;
+    // Words are written downwards from the end of the slice; the two lowest places
+    // are for the final state.
+    int32_t idx = (int32_t)cap - 1;   // next write position in the slice, counts down
     uint32_t x = kStateLow;
-    uint32_t emitted = 0;
-    bool overflow = false;
     for (int32_t blk = (int32_t)(S / 8) - 1; blk >= 0; --blk) {
       const uint64_t e0 = first + (uint64_t)blk * 256 + lane * 8;
       uint32_t lo, hi;
@@ -267,29 +310,12 @@ encode_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t 
         }
       }
 #pragma unroll
-      for (int t = 7; t >= 0; --t) {
-        const uint32_t s = ((t < 4 ? lo : hi) >> (8 * (t & 3))) & 0xFFu;
-        const uint32_t ent = tab[s];
-        const uint32_t fr = ent & 0xFFFFu, cum = ent >> 16;
-        if (x >= (fr << (32 - pb))) {
-          // words beyond the capacity are dropped; the unit is then stored raw
-          if (emitted + 2 < cap) mine[cap - 1 - emitted] = (uint16_t)(x & 0xFFFFu);
-          else overflow = true;
-          ++emitted;
-          x >>= 16;
-        }
-        // x / fr and x % fr without a division: the estimate is exact or one short
-        uint32_t q = __umulhi(x, rcp[s]);
-        uint32_t rem = x - q * fr;
-        if (rem >= fr) {
-          ++q;
-          rem -= fr;
-        }
-        x = (q << pb) + rem + cum;
-      }
+      for (int t = 7; t >= 0; --t)
+        encode_step(x, idx, t < 4 ? lo : hi, 0x4440u | (uint32_t)(t & 3), tab_addr, mine, pow_m);
     }
-    uint32_t words = emitted + 2;
-    if (words > cap) overflow = true;
+    const uint32_t emitted = (uint32_t)((int32_t)cap - 1 - idx);
+    const bool overflow = emitted + 2 > cap;
+    const uint32_t words = emitted + 2;
     const uint32_t q = (words + lenq - 1) / lenq;
     if (!overflow) {
       // state in front of the emitted words
@@ -399,43 +425,81 @@ scan_kernel(const uint32_t *__restrict__ unit_words, uint32_t n_units, uint64_t 
   }
 }
 
-// Copy each unit to its place in the payload: one warp per unit.
-__global__ void __launch_bounds__(256)
+// Copy each unit to its place in the payload: one warp per unit.  The unit's
+// 32 scratch slices (one fixed-size slice per lane, the stream at its end) are
+// brought into shared memory with 16-byte loads that are all in flight together,
+// squeezed there into the unit's final layout, and written out with consecutive
+// lanes on consecutive words.
+constexpr int kCompactWarps = 4;
+
+__global__ void __launch_bounds__(kCompactWarps * 32)
 compact_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t S, uint32_t n_units,
                const uint16_t *__restrict__ lane_len, const uint16_t *__restrict__ lane_words,
                uint8_t *__restrict__ container) {
-  const uint32_t lane = threadIdx.x & 31;
+  extern __shared__ __align__(16) uint8_t cmp_smem[];
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t lenq = len_quantum(S);
   const uint32_t cap = lane_cap_words(S);
   const uint64_t U = 32ull * S;
   const uint32_t *offsets = reinterpret_cast<const uint32_t *>(container + kOffsetsOffset);
   uint16_t *payload = reinterpret_cast<uint16_t *>(container + payload_offset(n_units));
-  for (uint32_t u = blockIdx.x * 8 + (threadIdx.x >> 5); u < n_units; u += gridDim.x * 8) {
+  // per warp: 16 words for the length bytes, then the 32 slices
+  const uint32_t cell_words = 16 + 32 * cap;
+  uint16_t *cell = reinterpret_cast<uint16_t *>(cmp_smem) + (uint64_t)warp * ((cell_words + 7) & ~7u);
+  for (uint32_t u = blockIdx.x * kCompactWarps + warp; u < n_units;
+       u += gridDim.x * kCompactWarps) {
     const uint32_t off = offsets[u];
-    uint16_t *dst = payload + (off & ~kRawFlag);
-    const uint64_t first = (uint64_t)u * U;
-    const uint64_t count = (n - first < U) ? (n - first) : U;
+    const uint32_t w0 = off & ~kRawFlag;
+    uint16_t *dst = payload + w0;
     if (off & kRawFlag) {
+      const uint64_t first = (uint64_t)u * U;
+      const uint64_t count = (n - first < U) ? (n - first) : U;
       uint8_t *d8 = reinterpret_cast<uint8_t *>(dst);
       for (uint64_t i = lane; i < count; i += 32) d8[i] = sym[first + i];
       if ((count & 1) && lane == 0) d8[count] = 0;
       continue;
     }
+    const uint32_t words_total = (offsets[u + 1] & ~kRawFlag) - w0;
+    // 1. slices -> shared memory: the 32 slices of a unit are one run of 64*cap bytes
+    //    that starts on a 64-byte boundary, whatever cap is
+    {
+      const uint4 *s4 = reinterpret_cast<const uint4 *>(lane_words + (uint64_t)u * 32 * cap);
+      uint4 *c4 = reinterpret_cast<uint4 *>(cell + 16);
+      for (uint32_t k = lane; k < 4 * cap; k += 32) c4[k] = s4[k];
+    }
     const uint32_t my_words = lane_len[(uint64_t)u * 32 + lane];
     const uint32_t my_q = (my_words + lenq - 1) / lenq;
-    reinterpret_cast<uint8_t *>(dst)[lane] = (uint8_t)my_q;
+    __syncwarp();
+    reinterpret_cast<uint8_t *>(cell)[lane] = (uint8_t)my_q;
+    // 2. squeeze: lane streams move down, in lane order, to sit back to back.  A
+    //    stream never moves up, and it ends before the next lane's slice begins, so
+    //    going lane by lane and chunk by chunk (read, sync, write) is safe in place.
     uint32_t p = 16;
     for (uint32_t j = 0; j < 32; ++j) {
       const uint32_t words = __shfl_sync(0xFFFFFFFFu, my_words, j);
       const uint32_t padded = __shfl_sync(0xFFFFFFFFu, my_q, j) * lenq;
-      // the lane's words sit at the end of its scratch slice, in decoder order
-      const uint16_t *src = lane_words + ((uint64_t)u * 32 + j + 1) * cap - words;
-      for (uint32_t k = lane; k < padded; k += 32) dst[p + k] = (k < words) ? src[k] : (uint16_t)0;
+      const uint32_t from = 16 + (j + 1) * cap - words;
+      for (uint32_t k0 = 0; k0 < padded; k0 += 32) {
+        const uint32_t k = k0 + lane;
+        const uint16_t v = (k < words) ? cell[from + k] : (uint16_t)0;
+        __syncwarp();
+        if (k < padded) cell[p + k] = v;
+        __syncwarp();
+      }
       p += padded;
     }
+    // 3. out: p == words_total
+    if ((w0 & 1) == 0) {
+      const uint32_t *c32 = reinterpret_cast<const uint32_t *>(cell);
+      uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+      for (uint32_t k = lane; k < words_total / 2; k += 32) d32[k] = c32[k];
+      if ((words_total & 1) && lane == 0) dst[words_total - 1] = cell[words_total - 1];
+    } else {
+      for (uint32_t k = lane; k < words_total; k += 32) dst[k] = cell[k];
+    }
+    __syncwarp();
   }
 }
-
 
 // ------------------------------------------------------------------- host
 int histogram_u8(const void *sym, uint64_t n, void *hist, cudaStream_t st) {
@@ -493,10 +557,14 @@ int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container
                                   (const uint32_t *)(sc + kScratchMisc), cont);
   NZ_LAUNCH_CHECK("scan_kernel");
   if (nu) {
-    uint32_t blocks = (nu + 7) / 8;
-    const uint32_t capb = (uint32_t)sm_count() * 8;
+    const uint32_t cell_bytes = ((16 + 32 * lane_cap_words(S) + 7) & ~7u) * 2;
+    const uint32_t cmp_smem_bytes = kCompactWarps * cell_bytes;
+    NZ_CUDA_TRY(cudaFuncSetAttribute(compact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)cmp_smem_bytes));
+    uint32_t blocks = (nu + kCompactWarps - 1) / kCompactWarps;
+    const uint32_t capb = (uint32_t)sm_count() * 16;
     if (blocks > capb) blocks = capb;
-    compact_kernel<<<blocks, 256, 0, st>>>((const uint8_t *)exp_in, n, S, nu,
+    compact_kernel<<<blocks, kCompactWarps * 32, cmp_smem_bytes, st>>>((const uint8_t *)exp_in, n, S, nu,
                                            (const uint16_t *)(sc + L.lane_len),
                                            (const uint16_t *)(sc + L.lane_words), cont);
     NZ_LAUNCH_CHECK("compact_kernel");
