@@ -90,6 +90,26 @@ int nz_merge_bf16(const void *exp_in, const void *frac_in, uint64_t n,
                   int precision, int canonical_nan, void *out_bf16,
                   void *stream);
 
+/* ---- block normaliser (normalizer_size > 0) ------------------------------ */
+
+/* Bytes of the normaliser stream: ceil(n / group), one byte per group of
+ * `group` consecutive elements (a power of two up to 1024).
+ * Reference: cuda/high_level.cu:89-93. */
+uint64_t nz_normalizer_bytes(uint64_t n, uint32_t group);
+
+/* Scale every group by 1.<mantissa of its absmax> before the split:
+ * out = bf16(float(in) / scale), normalizers[g] = top 8 mantissa bits.
+ * Reference: normalized=true path of kernel_aligned_split,
+ * cuda/kernels.cuh:94-118 (intended semantics, see nz_normalize.cu). */
+int nz_normalize_bf16(const void *in_bf16, uint64_t n, uint32_t group,
+                      void *out_bf16, void *normalizers, void *stream);
+
+/* Undo the scaling after the merge, in place: v = bf16(scale8 * float(v)) with
+ * the scale rebuilt from the stored byte.
+ * Reference: cuda/kernels.cuh:188-191, :208-216. */
+int nz_denormalize_bf16(void *inout_bf16, uint64_t n, uint32_t group,
+                        const void *normalizers, void *stream);
+
 /* ---- entropy stage ------------------------------------------------------ */
 
 /* 256-bin histogram of n bytes into hist_u32[256] (device; cleared first). */

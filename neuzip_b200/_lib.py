@@ -38,6 +38,9 @@ SIGNATURES = {
     "nz_compress_scratch_bytes": (_u64, [_u64, _u32]),
     "nz_split_bf16": (_int, [_vp, _u64, _int, _vp, _vp, _vp]),
     "nz_merge_bf16": (_int, [_vp, _vp, _u64, _int, _int, _vp, _vp]),
+    "nz_normalizer_bytes": (_u64, [_u64, _u32]),
+    "nz_normalize_bf16": (_int, [_vp, _u64, _u32, _vp, _vp, _vp]),
+    "nz_denormalize_bf16": (_int, [_vp, _u64, _u32, _vp, _vp]),
     "nz_histogram_u8": (_int, [_vp, _u64, _vp, _vp]),
     "nz_encode_exponents": (_int, [_vp, _u64, _u32, _vp, _u64, _vp, _u64, _vp]),
     "nz_static_scratch_bytes": (_u64, []),

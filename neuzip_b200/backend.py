@@ -7,8 +7,8 @@ Where the reference keeps its compressed tensors in a C++ map inside the
 extension (cuda/high_level.cu:35-43), this backend keeps torch tensors in a
 Python dict and calls the stateless C-ABI kernels of ``libneuzip_b200.so`` on
 the caller's current CUDA stream.  Only the rANS ("ans") algorithm, bf16
-tensors and ``normalizer_size == 0`` are implemented; the other combinations
-raise ``NotImplementedError`` when constructed.
+tensors are implemented (every precision and normaliser size); the other
+algorithms raise ``NotImplementedError`` when constructed.
 """
 from __future__ import annotations
 
@@ -41,6 +41,7 @@ class _Entry:
     max_unit_words: int
     container: torch.Tensor   # uint8, right-sized NZR1 container
     fractions: torch.Tensor   # uint8, packed sign+mantissa stream
+    normalizers: Optional[torch.Tensor] = None   # uint8, one byte per group (normalizer_size > 0)
 
 
 def _ptr(t: Optional[torch.Tensor]) -> int:
@@ -81,8 +82,6 @@ class CodecBackend:
         if algorithm is not Algorithm.ans:
             raise NotImplementedError(
                 f"algorithm {algorithm.name!r}: only the rANS coder ('ans') is implemented")
-        if self.normalizer_size != 0:
-            raise NotImplementedError("the block normaliser (normalizer_size > 0) is not implemented")
         self._lib = _lib.load()
         self.chunk_size = int(chunk_size)   # kept for API parity; the unit size follows precision
         self.lane_symbols = int(self._lib.nz_default_lane_symbols(self.precision))
@@ -124,19 +123,29 @@ class CodecBackend:
         n = flat.numel()
         L, S = self._lib, self.lane_symbols
         self._cache.pop(name, None)
+        st = _stream()
+        normalizers = None
+        if self.normalizer_size:
+            # per-group scaling first (cuda/kernels.cuh:94-118); the scaled copy is what gets split
+            normalizers = torch.empty(int(L.nz_normalizer_bytes(n, self.normalizer_size)),
+                                      dtype=torch.uint8, device="cuda")
+            scaled = torch.empty_like(flat)
+            _lib.check(L.nz_normalize_bf16(_ptr(flat), n, self.normalizer_size, _ptr(scaled),
+                                           _ptr(normalizers), st))
+            flat = scaled
         frac = torch.empty(int(L.nz_frac_bytes(n, self.precision)), dtype=torch.uint8, device="cuda")
         cap = int(L.nz_container_bound(n, S))
         staging = torch.empty(cap, dtype=torch.uint8, device="cuda")
         scratch_bytes = int(L.nz_compress_scratch_bytes(n, S))
         scratch = self._scratch_for(scratch_bytes)
-        st = _stream()
         _lib.check(L.nz_compress_bf16(_ptr(flat), n, self.precision, S, _ptr(frac), _ptr(staging),
                                       cap, _ptr(scratch), scratch.numel(), st))
         total = _lib._u64(0)
         max_words = _lib._u32(0)
         _lib.check(L.nz_container_bytes(_ptr(staging), total, max_words, st))
         container = staging[: total.value].clone()
-        self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac)
+        self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac,
+                                   normalizers)
 
     def read(self, name: str) -> torch.Tensor:
         """cuda/high_level.cu:223-250 (+ _decompress_and_merge :164-206); no host sync."""
@@ -153,6 +162,12 @@ class CodecBackend:
             _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
             self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
             _ptr(out), _ptr(self._status), _stream()))
+        self._denormalize(entry, out)
+
+    def _denormalize(self, entry: _Entry, out: torch.Tensor) -> None:
+        if entry.normalizers is not None:
+            _lib.check(self._lib.nz_denormalize_bf16(_ptr(out), entry.numel, self.normalizer_size,
+                                                     _ptr(entry.normalizers), _stream()))
 
     def read_many(self, names: Sequence[str]) -> List[torch.Tensor]:
         """Decompress several tensors (for instance all matrices of one layer) with
@@ -183,6 +198,8 @@ class CodecBackend:
             _lib.check(self._lib.nz_decompress_bf16_batch(
                 items, len(idx), self.precision, S, int(self.canonical_nan), _ptr(self._status),
                 _stream()))
+        for e, out in zip(entries, outs):
+            self._denormalize(e, out)
         return outs
 
     def make_batch(self, names: Sequence[str], outs: Sequence[torch.Tensor]):
@@ -206,7 +223,7 @@ class CodecBackend:
             items[k].out_bf16 = _ptr(out)
         # keep the tensors alive as long as the batch exists
         return (items, len(entries), S.pop(), [e.container for e in entries],
-                [e.fractions for e in entries], list(outs))
+                [e.fractions for e in entries], list(outs), entries)
 
     def run_batch(self, batch) -> None:
         items, count, S = batch[0], batch[1], batch[2]
@@ -215,13 +232,17 @@ class CodecBackend:
                                                 _stream())
         if rc:
             _lib.check(rc)
+        if self.normalizer_size:
+            for e, out in zip(batch[6], batch[5]):
+                self._denormalize(e, out)
 
     def size(self, name: str) -> int:
         """cuda/high_level.cu:208-221: stored bytes, 0 for an unknown name."""
         entry = self._cache.get(name)
         if entry is None:
             return 0
-        return entry.container.numel() + entry.fractions.numel()
+        extra = 0 if entry.normalizers is None else entry.normalizers.numel()
+        return entry.container.numel() + entry.fractions.numel() + extra
 
     def linear(self, name: str, input: torch.Tensor, shape: Sequence[int],
                bias: torch.Tensor) -> torch.Tensor:
@@ -254,12 +275,15 @@ class CodecBackend:
         e = self._cache[name]
         return {"format": "NZR1", "precision": self.precision, "numel": e.numel,
                 "lane_symbols": e.lane_symbols, "max_unit_words": e.max_unit_words,
-                "container": e.container.cpu(), "fractions": e.fractions.cpu()}
+                "container": e.container.cpu(), "fractions": e.fractions.cpu(),
+                "normalizer_size": self.normalizer_size,
+                "normalizers": None if e.normalizers is None else e.normalizers.cpu()}
 
     def import_entry(self, name: str, blob: dict) -> None:
         """Inverse of `export_entry`: the compressed bytes go straight to the GPU,
         no bf16 copy of the tensor is ever materialised."""
-        if blob.get("format") != "NZR1" or int(blob["precision"]) != self.precision:
+        if (blob.get("format") != "NZR1" or int(blob["precision"]) != self.precision
+                or int(blob.get("normalizer_size", 0)) != self.normalizer_size):
             raise ValueError("checkpoint entry does not match this manager "
                              f"(format {blob.get('format')!r}, precision {blob.get('precision')})")
         self._ensure_device()
@@ -268,8 +292,11 @@ class CodecBackend:
         n = int(blob["numel"])
         if fractions.numel() != int(self._lib.nz_frac_bytes(n, self.precision)):
             raise ValueError("checkpoint entry: fraction stream has the wrong length")
+        normalizers = blob.get("normalizers")
+        if normalizers is not None:
+            normalizers = normalizers.to(device="cuda", dtype=torch.uint8).contiguous()
         self._cache[name] = _Entry(n, torch.bfloat16, int(blob["lane_symbols"]),
-                                   int(blob["max_unit_words"]), container, fractions)
+                                   int(blob["max_unit_words"]), container, fractions, normalizers)
 
     # -- extras -----------------------------------------------------------
     def erase(self, name: str) -> None:

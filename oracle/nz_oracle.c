@@ -566,3 +566,63 @@ uint32_t nzo_crc32(const uint8_t *p, uint64_t n) {
   for (uint64_t i = 0; i < n; ++i) c = table[(c ^ p[i]) & 0xFF] ^ (c >> 8);
   return c ^ 0xFFFFFFFFu;
 }
+
+/* ------------------------------------------------------- block normaliser */
+
+/* float -> bf16 bits, round to nearest even, NaN -> 0x7FFF: the conversion the
+ * reference's stores perform (c10::BFloat16 from float on sm_80+). */
+static uint16_t f32_to_bf16_rne(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7F800000u) == 0x7F800000u && (u & 0x007FFFFFu)) return 0x7FFF;
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+static float bf16_to_f32(uint16_t b) {
+  uint32_t u = (uint32_t)b << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+/* Per-group scaling before the split, the *intended* semantics of the
+ * normalized=true path of kernel_aligned_split (cuda/kernels.cuh:94-118; the
+ * reference's own BlockReduce misbehaves for groups of 64..512 threads, so its
+ * bits are not reproducible there): for every run of `group` consecutive
+ * elements, absmax of |float(v)| (missing tail elements count as 0), scale =
+ * 1.<23 mantissa bits of absmax> in [1, 2), v' = bf16(float(v) / scale); the
+ * stored normaliser byte is the top 8 mantissa bits (:103-116). */
+void nzo_normalize_groups(const uint16_t *v, uint64_t n, uint32_t group, uint16_t *out,
+                          uint8_t *normalizers) {
+  const uint64_t n_groups = (n + group - 1) / group;
+#pragma omp parallel for schedule(static)
+  for (int64_t g = 0; g < (int64_t)n_groups; ++g) {
+    uint64_t lo = (uint64_t)g * group, hi = lo + group < n ? lo + group : n;
+    float amax = 0.0f;
+    for (uint64_t i = lo; i < hi; ++i) {
+      float a = bf16_to_f32((uint16_t)(v[i] & 0x7FFF));
+      if (a > amax) amax = a; /* NaN never wins, like fmaxf-free cub::Max on floats */
+    }
+    uint32_t bits;
+    memcpy(&bits, &amax, 4);
+    uint32_t frac = bits & 0x007FFFFFu;
+    uint32_t sbits = 0x3F800000u | frac;
+    float scale;
+    memcpy(&scale, &sbits, 4);
+    normalizers[g] = (uint8_t)(frac >> 15);
+    for (uint64_t i = lo; i < hi; ++i) out[i] = f32_to_bf16_rne(bf16_to_f32(v[i]) / scale);
+  }
+}
+
+/* Inverse scaling after the merge (cuda/kernels.cuh:208-216): the scale is
+ * rebuilt from the stored byte only, out = bf16(scale8 * float(v)). */
+void nzo_denormalize_groups(uint16_t *v, uint64_t n, uint32_t group, const uint8_t *normalizers) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i64 = 0; i64 < (int64_t)n; ++i64) {
+    uint64_t i = (uint64_t)i64;
+    uint32_t sbits = 0x3F800000u | ((uint32_t)normalizers[i / group] << 15);
+    float scale;
+    memcpy(&scale, &sbits, 4);
+    v[i] = f32_to_bf16_rne(scale * bf16_to_f32(v[i]));
+  }
+}

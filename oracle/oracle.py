@@ -68,6 +68,10 @@ def lib() -> ctypes.CDLL:
         L.nzo_compress_bf16.restype = u64
         L.nzo_decompress_bf16.argtypes = [vp, u64, vp, u64, i32, i32, vp, vp]
         L.nzo_decompress_bf16.restype = i32
+        L.nzo_normalize_groups.argtypes = [vp, u64, u32, vp, vp]
+        L.nzo_normalize_groups.restype = None
+        L.nzo_denormalize_groups.argtypes = [vp, u64, u32, vp]
+        L.nzo_denormalize_groups.restype = None
         L.nzo_crc32.argtypes = [vp, u64]
         L.nzo_crc32.restype = u32
         _lib = L
@@ -193,6 +197,22 @@ def decompress_bf16(cont: np.ndarray, frac: np.ndarray, n: int, s: int,
                                    _p(scratch), _p(out))
     if rc != 0:
         raise ValueError(f"oracle decompress failed with code {rc}")
+    return out
+
+
+def normalize_groups(bits: np.ndarray, group: int) -> Tuple[np.ndarray, np.ndarray]:
+    """Block normaliser before the split: returns (scaled bf16 bits, normaliser bytes)."""
+    bits = np.ascontiguousarray(bits.reshape(-1), dtype=np.uint16)
+    out = np.empty_like(bits)
+    norm = np.empty((bits.size + group - 1) // group, np.uint8)
+    lib().nzo_normalize_groups(_p(bits), bits.size, group, _p(out), _p(norm))
+    return out, norm
+
+
+def denormalize_groups(bits: np.ndarray, group: int, normalizers: np.ndarray) -> np.ndarray:
+    out = np.ascontiguousarray(bits.reshape(-1), dtype=np.uint16).copy()
+    normalizers = np.ascontiguousarray(normalizers, dtype=np.uint8)
+    lib().nzo_denormalize_groups(_p(out), out.size, group, _p(normalizers))
     return out
 
 

@@ -276,3 +276,39 @@ def test_batched_decompress_equals_single_calls(s):
         assert torch.equal(outs[i].view(torch.int16), singles[i].view(torch.int16)), (s, i, n)
         if s == 7 and n:
             assert torch.equal(outs[i].view(torch.int16), tensors[i].view(torch.int16))
+
+
+# ------------------------------------------------------------ block normaliser
+@pytest.mark.parametrize("group", (1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024))
+def test_normalize_and_denormalize_match_oracle(group):
+    from neuzip_b200 import _lib
+    L = A.lib()
+    for n, seed in ((1, 1), (7, 2), (1024, 3), (1025, 4), (5000, 5), (70001, 6)):
+        x = (weights(n, 700 + seed, std=0.05)).cuda()
+        bits = A.to_bits(x)
+        nb = int(L.nz_normalizer_bytes(n, group))
+        raw_o, out = A.guarded(2 * n, torch.bfloat16)
+        raw_n, norm = A.guarded(nb)
+        _lib.check(L.nz_normalize_bf16(x.data_ptr(), n, group, out.data_ptr(), norm.data_ptr(), A.stream()))
+        torch.cuda.synchronize()
+        assert A.guards_intact(raw_o, 2 * n) and A.guards_intact(raw_n, nb)
+        ref, ref_norm = O.normalize_groups(bits, group)
+        assert np.array_equal(A.to_bits(out), ref), (group, n)
+        assert np.array_equal(norm.cpu().numpy(), ref_norm), (group, n)
+        _lib.check(L.nz_denormalize_bf16(out.data_ptr(), n, group, norm.data_ptr(), A.stream()))
+        torch.cuda.synchronize()
+        assert np.array_equal(A.to_bits(out), O.denormalize_groups(ref, group, ref_norm)), (group, n)
+        assert A.guards_intact(raw_o, 2 * n)
+
+
+def test_normalizer_on_special_values():
+    from neuzip_b200 import _lib
+    L = A.lib()
+    bits = np.tile(all_patterns(), 2)
+    x = A.from_bits(bits)
+    n = bits.size
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    norm = torch.empty(int(L.nz_normalizer_bytes(n, 64)), dtype=torch.uint8, device="cuda")
+    _lib.check(L.nz_normalize_bf16(x.data_ptr(), n, 64, out.data_ptr(), norm.data_ptr(), A.stream()))
+    ref, ref_norm = O.normalize_groups(bits, 64)
+    assert np.array_equal(A.to_bits(out), ref) and np.array_equal(norm.cpu().numpy(), ref_norm)

@@ -256,3 +256,25 @@ def test_checkpoint_of_converted_model_round_trips_on_gpu(tmp_path):
     other = wrong.convert(make()).cuda()
     with pytest.raises(Exception):
         other.load_state_dict(torch.load(tmp_path / "c.pt", weights_only=False))
+
+
+@pytest.mark.parametrize("precision,group", ((3, 512), (1, 64), (0, 1024), (7, 8), (3, 1)))
+def test_manager_with_block_normaliser_matches_oracle(precision, group):
+    m = neuzip.Manager(precision=precision, normalizer_size=group)
+    w = weights((257, 300), 60 + group)
+    h = m.write(w)
+    got = m.read(h)
+    m.check()
+    scaled, norm = O.normalize_groups(bits_of(w), group)
+    e, f = O.split(scaled, precision)
+    ref = O.denormalize_groups(O.merge(e, f, precision, canonical_nan=True), group, norm)
+    assert np.array_equal(bits_of(got), ref)
+    entry = m._be.entry(h)
+    assert m.size(h) == entry.container.numel() + entry.fractions.numel() + norm.size
+    assert torch.equal(m.read_many([h])[0], got)
+    # the normaliser tightens the lossy error
+    if precision == 3:
+        plain = neuzip.Manager(precision=3)
+        err_plain = (plain.read(plain.write(w)).float() - w.cuda().float()).abs().mean().item()
+        err_norm = (got.float() - w.cuda().float()).abs().mean().item()
+        assert err_norm <= err_plain * 1.05

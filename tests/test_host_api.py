@@ -50,8 +50,7 @@ def test_unsupported_combinations_raise_clearly():
         neuzip.Manager(normalizer_size=3)
     with pytest.raises(NotImplementedError):
         neuzip.Manager(algorithm=neuzip.Algorithm.zstd)
-    with pytest.raises(NotImplementedError):
-        neuzip.Manager(normalizer_size=512)
+    assert neuzip.Manager(precision=3, normalizer_size=512)._be.normalizer_size == 512
     m = neuzip.Manager()                       # constructing the real backend needs no GPU
     assert m._be.precision == 7 and m._be.lane_symbols == 256
     assert m.size("nope") == 0
