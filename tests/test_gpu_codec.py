@@ -312,3 +312,69 @@ def test_normalizer_on_special_values():
     _lib.check(L.nz_normalize_bf16(x.data_ptr(), n, 64, out.data_ptr(), norm.data_ptr(), A.stream()))
     ref, ref_norm = O.normalize_groups(bits, 64)
     assert np.array_equal(A.to_bits(out), ref) and np.array_equal(norm.cpu().numpy(), ref_norm)
+
+
+# ------------------------------------------------- full-size and stress cases
+def test_largest_baseline_tensor_round_trips_on_device():
+    """28672 x 8192 (the largest matrix of the 70B configuration, 235 M elements):
+    checked through size-independent properties on the device - lossless equality,
+    lossy idempotence (compressing the decoded tensor again changes nothing) and
+    the stored size against the entropy bound."""
+    n = 28672 * 8192
+    g = torch.Generator(device="cuda").manual_seed(70)
+    x = (torch.randn(n, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    for s in (7, 3):
+        S = O.default_lane_symbols(s)
+        cont, frac, mw = A.compress(x, s, S)
+        out, status = A.decompress(cont, frac, n, s, S, mw, canon=True)
+        assert status == 0
+        if s == 7:
+            assert torch.equal(out.view(torch.int16), x.view(torch.int16))
+        else:
+            cont2, frac2, mw2 = A.compress(out, s, S)
+            out2, status2 = A.decompress(cont2, frac2, n, s, S, mw2, canon=True)
+            assert status2 == 0 and torch.equal(out2.view(torch.int16), out.view(torch.int16))
+            assert torch.equal(frac2, frac)
+        exp = ((out.view(torch.int16).to(torch.int32) >> 7) & 0xFF)
+        hist = torch.bincount(exp.flatten(), minlength=256).double()
+        p = hist[hist > 0] / n
+        ideal = float(-(p * p.log2()).sum()) * n / 8 + frac.numel() + (n + 1023) // 1024
+        assert cont.numel() + frac.numel() <= 1.02 * ideal
+        del cont, frac, out
+
+
+def test_concurrent_streams_do_not_interfere():
+    from neuzip_b200 import _lib
+    L = A.lib()
+    xs = [weights(1 << 20, 800 + i).cuda() for i in range(4)]
+    comps = [A.compress(x, 7, 256) for x in xs]
+    outs = [torch.empty_like(x) for x in xs]
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    streams = [torch.cuda.Stream() for _ in range(4)]
+    torch.cuda.synchronize()
+    for rep in range(5):
+        for i, st in enumerate(streams):
+            c, f, mw = comps[i]
+            _lib.check(L.nz_decompress_bf16(c.data_ptr(), c.numel(), f.data_ptr(), xs[i].numel(), 7,
+                                            256, mw, 1, outs[i].data_ptr(),
+                                            status[i:].data_ptr(), st.cuda_stream))
+    torch.cuda.synchronize()
+    assert int(status.abs().sum().item()) == 0
+    for x, o in zip(xs, outs):
+        assert torch.equal(o.view(torch.int16), x.view(torch.int16))
+
+
+def test_random_shapes_and_lane_lengths_property():
+    rng = np.random.default_rng(123)
+    for trial in range(25):
+        n = int(rng.integers(1, 200000))
+        s = int(rng.choice(PRECISIONS))
+        S = int(rng.choice([8, 16, 64, 128, 256, 384, 512, 640, 1024]))
+        std = float(rng.choice([1e-4, 0.02, 1.0, 300.0]))
+        x = weights(n, 10_000 + trial, std=std).cuda()
+        cont, frac, mw = A.compress(x, s, S)
+        c_ref, f_ref = O.compress_bf16(A.to_bits(x), s, S)
+        assert np.array_equal(cont.cpu().numpy(), c_ref), (trial, n, s, S)
+        out, status = A.decompress(cont, frac, n, s, S, mw if trial % 2 else 0, canon=True)
+        assert status == 0
+        assert np.array_equal(A.to_bits(out), O.decompress_bf16(c_ref, f_ref, n, s, canonical_nan=True))
