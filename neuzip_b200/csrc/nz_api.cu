@@ -39,7 +39,7 @@ int split_bf16(const void *in, uint64_t n, int precision, void *exp_out, void *f
                cudaStream_t st);
 int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container,
                      uint64_t container_cap, void *scratch, uint64_t scratch_bytes,
-                     cudaStream_t st);
+                     cudaStream_t st, uint32_t low_prob_bits);
 
 }  // namespace nz
 
@@ -123,5 +123,10 @@ extern "C" int nz_compress_bf16(const void *in_bf16, uint64_t n, int precision,
     int rc = nz::split_bf16(in_bf16, n, precision, exp_buf, frac_out, st);
     if (rc) return rc;
   }
-  return nz::encode_exponents(exp_buf, n, lane_symbols, container, container_cap, scratch, enc, st);
+  // Lossless tensors keep 8 fraction bits per element, so the exponent stream is
+  // a quarter of what is stored: 9-bit probabilities cost 0.2 % of the stored
+  // size there and let the decoder keep one table copy per shared-memory bank.
+  const uint32_t low_pb = precision == 7 ? nz::kMinProbBits : nz::kDefaultLowProbBits;
+  return nz::encode_exponents(exp_buf, n, lane_symbols, container, container_cap, scratch, enc, st,
+                              low_pb);
 }

@@ -13,7 +13,8 @@
 
 namespace nz {
 
-constexpr uint32_t kMinProbBits = 10;
+constexpr uint32_t kMinProbBits = 9;          // lowest resolution a container may carry
+constexpr uint32_t kDefaultLowProbBits = 10;  // resolution for up to 32 distinct symbols
 constexpr uint32_t kMaxProbBits = 12;
 constexpr uint32_t kStateLow = 1u << 16;
 constexpr uint32_t kMagic = 0x31525A4Eu;  // "NZR1"

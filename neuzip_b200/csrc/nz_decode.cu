@@ -33,6 +33,16 @@
 
 #include "nz_common.cuh"
 
+#ifndef NZ_DECODE_CHAINS
+#define NZ_DECODE_CHAINS 2
+#endif
+#ifndef NZ_DECODE_ROLLED
+#define NZ_DECODE_ROLLED 4
+#endif
+#ifndef NZ_DECODE_MAX_WARPS
+#define NZ_DECODE_MAX_WARPS (NZ_DECODE_CHAINS == 2 ? 20 : 16)
+#endif
+
 namespace nz {
 
 constexpr uint32_t kMaxWaitIters = 1u << 20;
@@ -214,6 +224,18 @@ __device__ __forceinline__ void store_block(const uint32_t (&ent)[8], uint64_t f
   __stcs(reinterpret_cast<uint4 *>(dst), make_uint4(w[0], w[1], w[2], w[3]));
 }
 
+// One output word (two elements) from two table entries and the lane's packed
+// fractions of the block; `pair` is 0..3.
+template <int S, bool CANON>
+__device__ __forceinline__ uint32_t merge_word(uint32_t ea, uint32_t eb, uint64_t fbits, int pair) {
+  if (S == 7 && !CANON) {
+    const uint32_t half = (pair < 2) ? (uint32_t)fbits : (uint32_t)(fbits >> 32);
+    return merge_pair_s7(ea, eb, half, (pair & 1) ? 0x3322 : 0x1100);
+  }
+  return merge_pair_generic<S>(ea, eb, field_of<S>(fbits, 2 * pair), field_of<S>(fbits, 2 * pair + 1),
+                               CANON);
+}
+
 struct DecodeArgs {
   const uint8_t *container;
   uint64_t container_bytes;
@@ -360,22 +382,25 @@ __device__ __forceinline__ uint64_t frac_from_ring(uint32_t addr) {
   return lds_u32(addr);
 }
 
-constexpr uint32_t kRingSlots = 4;        // blocks of fractions in flight per unit + 1
-constexpr uint32_t kRingSlotBytes = 512;  // 2 units x 32 lanes x 8 bytes
+constexpr int kChains = NZ_DECODE_CHAINS;        // units a warp decodes side by side
+constexpr int kRolled = NZ_DECODE_ROLLED;        // blocks per trip of the rolled decode loop
+constexpr uint32_t kRingSlots = 4;               // blocks of fractions in flight per unit + 1
+constexpr uint32_t kRingUnitBytes = 256;         // 32 lanes x 8 bytes
+constexpr uint32_t kRingSlotBytes = kChains * kRingUnitBytes;
 constexpr uint32_t kRingBytes = kRingSlots * kRingSlotBytes;
 
-// Two units interleaved in one lane: the two rANS chains are independent, so
-// one hides the shared-memory and multiply latency of the other.  For
+// kChains units interleaved in one lane: the rANS chains are independent, so
+// each hides the shared-memory and multiply latency of the others.  For
 // precisions 3 and 7 the packed fractions travel through a small ring in shared
 // memory, fetched three blocks ahead with per-lane asynchronous copies; the
 // narrower fractions of precisions 0 and 1 (1 and 2 bytes per lane and block)
-// are loaded into registers.
+// are fetched four blocks at a time by the whole warp.
 template <int S, bool MERGE, bool CANON>
-__device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb, const LutView &lut,
-                                                   uint32_t n_blocks, const uint8_t *frac_a,
-                                                   const uint8_t *frac_b, uint16_t *out_a,
-                                                   uint16_t *out_b, uint8_t *exp_a, uint8_t *exp_b,
-                                                   uint32_t ring) {
+__device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], const LutView &lut,
+                                                    uint32_t n_blocks,
+                                                    const uint8_t *(&frac)[kChains],
+                                                    uint16_t *(&out)[kChains],
+                                                    uint8_t *(&exp)[kChains], uint32_t ring) {
   constexpr uint32_t kFracStride = 32u * (S + 1);
   constexpr bool kAsync = MERGE && (S == 7 || S == 3);
   constexpr int kAhead = 4;
@@ -385,21 +410,26 @@ __device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb,
     // ring one group of four blocks ahead; lanes then read their own 1 or 2 bytes.
     constexpr uint32_t kLaneBytes = 4u * (S + 1);          // per lane and group
     constexpr uint32_t kGroupBytes = 32u * kLaneBytes;     // per unit and group
+    constexpr uint32_t kBufBytes = kChains * kRingUnitBytes;
     const uint32_t lane_id = threadIdx.x & 31;
     const uint32_t ring0 = ring - lane_id * 4;             // `ring` carries lane*4 for s<7
     const uint32_t n_groups = n_blocks >> 2;
-    const uint8_t *ga = frac_a - (uint64_t)lane_id * (S + 1);   // unit base of the fractions
-    const uint8_t *gb = frac_b - (uint64_t)lane_id * (S + 1);
+    const uint8_t *gbase[kChains];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) gbase[c] = frac[c] - (uint64_t)lane_id * (S + 1);
     auto issue = [&](uint32_t g) {
-      const uint32_t dst = ring0 + (g & 1) * 1024 + lane_id * kLaneBytes;
-      const uint8_t *sa_ = ga + (uint64_t)g * kGroupBytes + lane_id * kLaneBytes;
-      const uint8_t *sb_ = gb + (uint64_t)g * kGroupBytes + lane_id * kLaneBytes;
-      if (S == 1) {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(sa_) : "memory");
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 512), "l"(sb_) : "memory");
-      } else {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(sa_) : "memory");
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 512), "l"(sb_) : "memory");
+      const uint32_t dst = ring0 + (g & 1) * kBufBytes + lane_id * kLaneBytes;
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) {
+        const uint8_t *src = gbase[c] + (uint64_t)g * kGroupBytes + lane_id * kLaneBytes;
+        if (S == 1)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + c * kRingUnitBytes),
+                       "l"(src)
+                       : "memory");
+        else
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + c * kRingUnitBytes),
+                       "l"(src)
+                       : "memory");
       }
       frac_commit();
     };
@@ -413,38 +443,101 @@ __device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb,
         frac_wait<0>();
       }
       __syncwarp();                       // all lanes' copies of group g have landed
-      const uint32_t src = ring0 + (g & 1) * 1024 + lane_id * (S + 1);
+      const uint32_t src = ring0 + (g & 1) * kBufBytes + lane_id * (S + 1);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        uint64_t bits_a, bits_b;
-        if (S == 1) {
-          bits_a = lds_u16(src + k * 64);
-          bits_b = lds_u16(src + 512 + k * 64);
-        } else {
-          bits_a = lds_u8(src + k * 32);
-          bits_b = lds_u8(src + 512 + k * 32);
-        }
-        uint32_t ea[8], eb[8];
+        uint64_t bits[kChains];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          ea[t] = decode_step(sa, lut);
-          eb[t] = decode_step(sb, lut);
+        for (int c = 0; c < kChains; ++c)
+          bits[c] = (S == 1) ? lds_u16(src + c * kRingUnitBytes + k * 64)
+                             : lds_u8(src + c * kRingUnitBytes + k * 32);
+        uint32_t w[kChains][4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          uint32_t e0[kChains], e1[kChains];
+#pragma unroll
+          for (int c = 0; c < kChains; ++c) e0[c] = decode_step(st[c], lut);
+#pragma unroll
+          for (int c = 0; c < kChains; ++c) e1[c] = decode_step(st[c], lut);
+#pragma unroll
+          for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
         }
-        store_block<S, CANON>(ea, bits_a, out_a + k * 256);
-        store_block<S, CANON>(eb, bits_b, out_b + k * 256);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c)
+          __stcs(reinterpret_cast<uint4 *>(out[c] + k * 256),
+                 make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]));
       }
-      out_a += 4 * 256;
-      out_b += 4 * 256;
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) out[c] += 4 * 256;
     }
     return;
   }
-  uint64_t fa[kAhead] = {0, 0, 0, 0}, fb[kAhead] = {0, 0, 0, 0};
+  if (kAsync && (n_blocks % kRolled) == 0) {
+    // Rolled form: the loop body covers kRolled blocks, so that the instruction
+    // working set of a CTA's warps stays small.
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      if ((uint32_t)k < n_blocks) {
+#pragma unroll
+        for (int c = 0; c < kChains; ++c)
+          frac_async<S>(ring + k * kRingSlotBytes + c * kRingUnitBytes, frac[c] + k * kFracStride);
+      }
+      frac_commit();
+    }
+#pragma unroll 1
+    for (uint32_t b = 0; b < n_blocks; b += kRolled) {
+#pragma unroll
+      for (int k = 0; k < kRolled; ++k) {
+        const uint32_t bk = b + k;
+        if (bk + 3 < n_blocks) {
+#pragma unroll
+          for (int c = 0; c < kChains; ++c)
+            frac_async<S>(ring + ((bk + 3) & 3) * kRingSlotBytes + c * kRingUnitBytes,
+                          frac[c] + (k + 3) * kFracStride);
+        }
+        frac_commit();
+        frac_wait<3>();
+        uint64_t bits[kChains];
+#pragma unroll
+        for (int c = 0; c < kChains; ++c)
+          bits[c] = frac_from_ring<S>(ring + (bk & 3) * kRingSlotBytes + c * kRingUnitBytes);
+        uint32_t w[kChains][4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          uint32_t e0[kChains], e1[kChains];
+#pragma unroll
+          for (int c = 0; c < kChains; ++c) e0[c] = decode_step(st[c], lut);
+#pragma unroll
+          for (int c = 0; c < kChains; ++c) e1[c] = decode_step(st[c], lut);
+#pragma unroll
+          for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
+        }
+#pragma unroll
+        for (int c = 0; c < kChains; ++c)
+          __stcs(reinterpret_cast<uint4 *>(out[c] + k * 256),
+                 make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]));
+      }
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) {
+        frac[c] += kRolled * kFracStride;
+        out[c] += kRolled * 256;
+      }
+    }
+    frac_wait<0>();
+    return;
+  }
+  uint64_t fr[kChains][kAhead];
+#pragma unroll
+  for (int c = 0; c < kChains; ++c)
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) fr[c][k] = 0;
   if (kAsync) {
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
       if ((uint32_t)k < n_blocks) {
-        frac_async<S>(ring + k * kRingSlotBytes, frac_a + k * kFracStride);
-        frac_async<S>(ring + k * kRingSlotBytes + 256, frac_b + k * kFracStride);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c)
+          frac_async<S>(ring + k * kRingSlotBytes + c * kRingUnitBytes, frac[c] + k * kFracStride);
       }
       frac_commit();
     }
@@ -452,54 +545,73 @@ __device__ __forceinline__ void decode_blocks_dual(LaneState &sa, LaneState &sb,
 #pragma unroll
     for (int k = 0; k < kAhead; ++k)
       if ((uint32_t)k < n_blocks) {
-        fa[k] = load_frac<S>(frac_a + k * kFracStride);
-        fb[k] = load_frac<S>(frac_b + k * kFracStride);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) fr[c][k] = load_frac<S>(frac[c] + k * kFracStride);
       }
   }
-  // One block of both units: fetch the fractions of block b+k (and start the copy
-  // for block b+k+3), decode 8 symbols of each chain, merge, store.  `kGuard`
+  // One block of every unit: fetch the fractions of block b+k (and start the copy
+  // for block b+k+3), decode 8 symbols of each chain, merge, store.  `guard`
   // is false when the block count is a multiple of four and nothing needs testing
   // except the end of the prefetch.
   auto one_block = [&](uint32_t b, int k, bool guard) {
     if (guard && !(b + k < n_blocks)) return;
-    uint64_t bits_a = fa[k], bits_b = fb[k];
+    uint64_t bits[kChains];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) bits[c] = fr[c][k];
     if (kAsync) {
       // block b+k+3 goes into the ring slot that block b+k-1 has left
       if (b + k + 3 < n_blocks) {
-        frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes, frac_a + (k + 3) * kFracStride);
-        frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes + 256, frac_b + (k + 3) * kFracStride);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c)
+          frac_async<S>(ring + ((k + 3) & 3) * kRingSlotBytes + c * kRingUnitBytes,
+                        frac[c] + (k + 3) * kFracStride);
       }
       frac_commit();
       frac_wait<3>();
-      bits_a = frac_from_ring<S>(ring + k * kRingSlotBytes);
-      bits_b = frac_from_ring<S>(ring + k * kRingSlotBytes + 256);
-    } else if (MERGE && b + kAhead + k < n_blocks) {
-      fa[k] = load_frac<S>(frac_a + (kAhead + k) * kFracStride);
-      fb[k] = load_frac<S>(frac_b + (kAhead + k) * kFracStride);
-    }
-    uint32_t ea[8], eb[8];
 #pragma unroll
-    for (int t = 0; t < 8; ++t) {
-      ea[t] = decode_step(sa, lut);
-      eb[t] = decode_step(sb, lut);
+      for (int c = 0; c < kChains; ++c)
+        bits[c] = frac_from_ring<S>(ring + k * kRingSlotBytes + c * kRingUnitBytes);
+    } else if (MERGE && b + kAhead + k < n_blocks) {
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) fr[c][k] = load_frac<S>(frac[c] + (kAhead + k) * kFracStride);
     }
     if (MERGE) {
-      store_block<S, CANON>(ea, bits_a, out_a + k * 256);
-      store_block<S, CANON>(eb, bits_b, out_b + k * 256);
+      // two symbols of each chain, then their output words: the table entries do
+      // not have to stay live for the whole block
+      uint32_t w[kChains][4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        uint32_t e0[kChains], e1[kChains];
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) e0[c] = decode_step(st[c], lut);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) e1[c] = decode_step(st[c], lut);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
+      }
+#pragma unroll
+      for (int c = 0; c < kChains; ++c)
+        __stcs(reinterpret_cast<uint4 *>(out[c] + k * 256),
+               make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]));
     } else {
-      store_exp_block(ea, exp_a + k * 256);
-      store_exp_block(eb, exp_b + k * 256);
+      uint32_t e[kChains][8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t)
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) e[c][t] = decode_step(st[c], lut);
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) store_exp_block(e[c], exp[c] + k * 256);
     }
   };
   auto advance = [&]() {
-    if (MERGE) {
-      frac_a += kAhead * kFracStride;
-      frac_b += kAhead * kFracStride;
-      out_a += kAhead * 256;
-      out_b += kAhead * 256;
-    } else {
-      exp_a += kAhead * 256;
-      exp_b += kAhead * 256;
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) {
+      if (MERGE) {
+        frac[c] += kAhead * kFracStride;
+        out[c] += kAhead * 256;
+      } else {
+        exp[c] += kAhead * 256;
+      }
     }
   };
   if ((n_blocks & 3) == 0) {
@@ -575,19 +687,22 @@ __device__ __forceinline__ UnitPlan plan_unit(const DecodeArgs &a, uint32_t u, u
   return pl;
 }
 
-// Lane 0 arms the warp's mbarrier with the bytes of both copies and starts them.
+// Lane 0 arms the warp's mbarrier with the bytes of all copies and starts them.
 // Returns true when at least one copy was issued.
-__device__ __forceinline__ bool stage_units(const DecodeArgs &a, const UnitPlan &pa,
-                                            const UnitPlan &pb, uint64_t pay_off, uint32_t slot_a,
-                                            uint32_t slot_b, uint32_t bar, uint32_t lane) {
-  const uint32_t bytes = pa.copy_bytes + pb.copy_bytes;
+__device__ __forceinline__ bool stage_units(const DecodeArgs &a, const UnitPlan (&pl)[kChains],
+                                            uint64_t pay_off, uint32_t slot0, uint32_t bar,
+                                            uint32_t lane) {
+  uint32_t bytes = 0;
+#pragma unroll
+  for (int c = 0; c < kChains; ++c) bytes += pl[c].copy_bytes;
   if (bytes == 0) return false;
   if (lane == 0) {
     mbar_expect_tx(bar, bytes);
-    if (pa.copy_bytes)
-      bulk_g2s(slot_a, a.container + pay_off + (pa.byte0 & ~uint64_t(15)), pa.copy_bytes, bar);
-    if (pb.copy_bytes)
-      bulk_g2s(slot_b, a.container + pay_off + (pb.byte0 & ~uint64_t(15)), pb.copy_bytes, bar);
+#pragma unroll
+    for (int c = 0; c < kChains; ++c)
+      if (pl[c].copy_bytes)
+        bulk_g2s(slot0 + c * a.slot_bytes, a.container + pay_off + (pl[c].byte0 & ~uint64_t(15)),
+                 pl[c].copy_bytes, bar);
   }
   return true;
 }
@@ -664,7 +779,7 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
 }
 
 template <int S, bool MERGE>
-__global__ void __launch_bounds__(640, 1)
+__global__ void __launch_bounds__(NZ_DECODE_MAX_WARPS * 32, 1)
 decode_kernel(const BatchArgs batch) {
   extern __shared__ __align__(128) uint8_t smem[];
   // which tensor this CTA works on, and its rank among that tensor's CTAs
@@ -700,8 +815,7 @@ decode_kernel(const BatchArgs batch) {
   uint8_t *slots = smem + a.lut_bytes + 1024;
   (void)lut_bytes;
   const uint32_t bar = smem_u32(&bars[warp]);
-  const uint32_t slot_a = smem_u32(slots + (uint64_t)(2 * warp) * a.slot_bytes);
-  const uint32_t slot_b = slot_a + a.slot_bytes;
+  const uint32_t slot0 = smem_u32(slots + (uint64_t)(kChains * warp) * a.slot_bytes);
   // per-warp ring for the packed fractions, behind all slots and their guard band
   const uint32_t ring = smem_u32(smem) + a.ring_offset + warp * kRingBytes + lane * (S == 7 ? 8 : 4);
 
@@ -720,16 +834,17 @@ decode_kernel(const BatchArgs batch) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // ---- start fetching the first pair of units, build the decode table meanwhile
+  // ---- start fetching the first group of units, build the decode table meanwhile
   const Header *h = reinterpret_cast<const Header *>(a.container);
   const uint64_t pay_off = payload_offset(a.n_units);
   const uint64_t max_words = (a.container_bytes - pay_off) / 2;   // host checked bytes >= pay_off
-  const uint32_t stride = 2 * cta_count * n_warps;
-  uint32_t u = 2 * (cta_rank * n_warps + warp);
+  const uint32_t stride = kChains * cta_count * n_warps;
+  uint32_t u = kChains * (cta_rank * n_warps + warp);
   uint32_t parity = 0;
-  UnitPlan pa = plan_unit(a, u, pay_off, max_words, lane);
-  UnitPlan pb2 = plan_unit(a, u + 1, pay_off, max_words, lane);
-  bool staged = stage_units(a, pa, pb2, pay_off, slot_a, slot_b, bar, lane);
+  UnitPlan pl[kChains];
+#pragma unroll
+  for (int c = 0; c < kChains; ++c) pl[c] = plan_unit(a, u + c, pay_off, max_words, lane);
+  bool staged = stage_units(a, pl, pay_off, slot0, bar, lane);
 
   const uint16_t *freq_g = reinterpret_cast<const uint16_t *>(a.container + kFreqOffset);
   if (warp == 0) {
@@ -804,7 +919,7 @@ decode_kernel(const BatchArgs batch) {
   const bool canon = MERGE && a.canon && (cum_sh[256] != cum_sh[255]);
   __syncthreads();
 
-  // ---- units, two at a time
+  // ---- units, kChains at a time
   const uint8_t *payload = a.container + pay_off;
   const uint32_t lenq = len_quantum(a.S);
   const uint64_t U = 32ull * a.S;
@@ -821,37 +936,50 @@ decode_kernel(const BatchArgs batch) {
         return;
       }
     }
-    const bool full_pair = pa.kind == kUnitCoded && pb2.kind == kUnitCoded &&
-                           (uint64_t)(u + 2) * U <= a.n;
+    bool full_group = (uint64_t)(u + kChains) * U <= a.n;
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) full_group = full_group && pl[c].kind == kUnitCoded;
     bool done = false;
-    if (full_pair) {
-      LaneState sa, sb;
-      const bool oka = open_unit(pa, slot_a, lenq, lane, sa);
-      const bool okb = open_unit(pb2, slot_b, lenq, lane, sb);
-      if (oka && okb) {
+    if (full_group) {
+      LaneState st[kChains];
+      bool ok = true;
+#pragma unroll
+      for (int c = 0; c < kChains; ++c)
+        ok = open_unit(pl[c], slot0 + c * a.slot_bytes, lenq, lane, st[c]) && ok;
+      if (ok) {
         done = true;
-        const uint64_t ea = (uint64_t)u * U + lane * 8, eb = ea + U;
-        const uint8_t *fa = MERGE ? a.frac + ea * (S + 1) / 8 : nullptr;
-        const uint8_t *fb = MERGE ? a.frac + eb * (S + 1) / 8 : nullptr;
-        uint16_t *oa = MERGE ? a.out_bf16 + ea : nullptr, *ob = MERGE ? a.out_bf16 + eb : nullptr;
-        uint8_t *xa = MERGE ? nullptr : a.out_exp + ea, *xb = MERGE ? nullptr : a.out_exp + eb;
+        const uint8_t *fr[kChains];
+        uint16_t *ob[kChains];
+        uint8_t *xb[kChains];
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) {
+          const uint64_t e = (uint64_t)(u + c) * U + lane * 8;
+          fr[c] = MERGE ? a.frac + e * (S + 1) / 8 : nullptr;
+          ob[c] = MERGE ? a.out_bf16 + e : nullptr;
+          xb[c] = MERGE ? nullptr : a.out_exp + e;
+        }
         if (canon)
-          decode_blocks_dual<S, MERGE, true>(sa, sb, lv, a.S / 8, fa, fb, oa, ob, xa, xb, ring);
+          decode_blocks_multi<S, MERGE, true>(st, lv, a.S / 8, fr, ob, xb, ring);
         else
-          decode_blocks_dual<S, MERGE, false>(sa, sb, lv, a.S / 8, fa, fb, oa, ob, xa, xb, ring);
-        if (__any_sync(0xFFFFFFFFu, sa.x != kStateLow || sb.x != kStateLow) && lane == 0)
-          raise(a.status, NZ_STATUS_BAD_STATE);
+          decode_blocks_multi<S, MERGE, false>(st, lv, a.S / 8, fr, ob, xb, ring);
+        bool low = true;
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) low = low && st[c].x == kStateLow;
+        if (__any_sync(0xFFFFFFFFu, !low) && lane == 0) raise(a.status, NZ_STATUS_BAD_STATE);
       }
     }
     if (!done) {
-      decode_single<S, MERGE>(a, pa, u, slot_a, lv, canon, payload, lenq, lane);
-      decode_single<S, MERGE>(a, pb2, u + 1, slot_b, lv, canon, payload, lenq, lane);
+#pragma unroll
+      for (int c = 0; c < kChains; ++c)
+        decode_single<S, MERGE>(a, pl[c], u + c, slot0 + c * a.slot_bytes, lv, canon, payload, lenq,
+                                lane);
     }
-    // every lane is done reading the slots: fetch this warp's next pair
+    // every lane is done reading the slots: fetch this warp's next group
     __syncwarp();
-    pa = plan_unit(a, u + stride, pay_off, max_words, lane);
-    pb2 = plan_unit(a, u + stride + 1, pay_off, max_words, lane);
-    staged = stage_units(a, pa, pb2, pay_off, slot_a, slot_b, bar, lane);
+#pragma unroll
+    for (int c = 0; c < kChains; ++c)
+      pl[c] = plan_unit(a, u + stride + c, pay_off, max_words, lane);
+    staged = stage_units(a, pl, pay_off, slot0, bar, lane);
   }
 }
 
@@ -867,9 +995,9 @@ struct HostItem {
 };
 
 // Grid geometry of one launch over `count` tensors.  One CTA per SM.  Every
-// warp decodes whole units, two at a time, so a tensor is only as fast as its
+// warp decodes whole units, kChains at a time, so a tensor is only as fast as its
 // busiest CTA: each tensor gets CTAs in proportion to its units, every CTA the
-// same number of warps, every warp the same number of unit pairs (within one).
+// same number of warps, every warp the same number of unit groups (within one).
 // The decode table gets what shared memory the slots and rings leave (more
 // copies = fewer bank conflicts), at most 128 KB.
 static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, BatchArgs &b,
@@ -886,11 +1014,11 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   b.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
   const uint32_t guard = ((S + 8) * 2 + 127) & ~127u;
   const uint32_t sm_smem = 227u * 1024u;
-  const uint32_t kMaxWarps = 20;
-  const uint32_t per_warp = 2 * b.slot_bytes + kRingBytes;
+  const uint32_t kMaxWarps = NZ_DECODE_MAX_WARPS;
+  const uint32_t per_warp = kChains * b.slot_bytes + kRingBytes;
   const uint32_t min_fixed = 16 * 1024 + 1024 + guard;
   if (min_fixed + per_warp > sm_smem) {
-    set_error("decode: two units of %u symbols do not fit in shared memory", (unsigned)U);
+    set_error("decode: a warp's units of %u symbols do not fit in shared memory", (unsigned)U);
     return NZ_E_ARG;
   }
   uint32_t cap = (sm_smem - min_fixed) / per_warp;
@@ -900,7 +1028,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   // (or fewer when there is not enough work to give every SM a pair of units)
   const uint32_t sms = (uint32_t)sm_count();
   uint64_t total_pairs = 0;
-  for (uint32_t t = 0; t < count; ++t) total_pairs += (unit_count(items[t].n, S) + 1) / 2;
+  for (uint32_t t = 0; t < count; ++t) total_pairs += (unit_count(items[t].n, S) + kChains - 1) / kChains;
   uint32_t n_ctas = sms;
   if (total_pairs < n_ctas) n_ctas = (uint32_t)total_pairs;
   if (n_ctas < count) n_ctas = count;
@@ -908,7 +1036,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   for (uint32_t t = 0; t < count; ++t) {
     const uint64_t nu = unit_count(items[t].n, S);
     uint64_t c = total_units ? (nu * n_ctas + total_units / 2) / total_units : 1;
-    const uint64_t pairs = (nu + 1) / 2;
+    const uint64_t pairs = (nu + kChains - 1) / kChains;
     if (c > pairs) c = pairs;
     if (c < 1) c = 1;
     ctas[t] = (uint32_t)c;
@@ -916,7 +1044,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   }
   // fix the rounding: take from / give to the tensor with the most / fewest pairs per CTA
   auto load = [&](uint32_t t, uint32_t c) {
-    return (double)((unit_count(items[t].n, S) + 1) / 2) / (double)c;
+    return (double)((unit_count(items[t].n, S) + kChains - 1) / kChains) / (double)c;
   };
   while (used > n_ctas) {
     uint32_t best = kMaxBatch;
@@ -930,7 +1058,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   while (used < n_ctas) {
     uint32_t best = kMaxBatch;
     for (uint32_t t = 0; t < count; ++t) {
-      const uint64_t pairs = (unit_count(items[t].n, S) + 1) / 2;
+      const uint64_t pairs = (unit_count(items[t].n, S) + kChains - 1) / kChains;
       if (ctas[t] < pairs && (best == kMaxBatch || load(t, ctas[t]) > load(best, ctas[best])))
         best = t;
     }
@@ -941,7 +1069,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   // warps per CTA: enough for the busiest CTA's pairs, spread over whole rounds
   uint32_t max_pairs = 1;
   for (uint32_t t = 0; t < count; ++t) {
-    const uint64_t pairs = (unit_count(items[t].n, S) + 1) / 2;
+    const uint64_t pairs = (unit_count(items[t].n, S) + kChains - 1) / kChains;
     const uint32_t per_cta = (uint32_t)((pairs + ctas[t] - 1) / ctas[t]);
     if (per_cta > max_pairs) max_pairs = per_cta;
   }
@@ -957,7 +1085,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
     }
   }
   b.lut_bytes = 4096u << b.lut_shift;
-  b.ring_offset = b.lut_bytes + 1024 + guard + warps * 2 * b.slot_bytes;
+  b.ring_offset = b.lut_bytes + 1024 + guard + warps * kChains * b.slot_bytes;
   smem_bytes = b.ring_offset + warps * kRingBytes;
   uint32_t begin = 0;
   for (uint32_t t = 0; t < count; ++t) {

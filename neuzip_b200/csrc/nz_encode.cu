@@ -93,7 +93,7 @@ histogram_kernel(const uint8_t *__restrict__ sym, uint64_t n, uint32_t *__restri
 // elements is rejected by the host code), the products 64-bit.
 __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__restrict__ freq,
                                  uint32_t *__restrict__ enc_tab, uint32_t *__restrict__ misc,
-                                 uint16_t *__restrict__ container_freq) {
+                                 uint16_t *__restrict__ container_freq, uint32_t low_pb) {
   __shared__ int32_t f[256];
   __shared__ uint64_t red64[8];
   __shared__ uint32_t red32[8];
@@ -121,7 +121,7 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
     total += red64[w];
     distinct += red32[w];
   }
-  const uint32_t pb = distinct <= 32 ? 10u : (distinct <= 64 ? 11u : 12u);
+  const uint32_t pb = distinct <= 32 ? low_pb : (distinct <= 64 ? 11u : 12u);
   const uint32_t M = 1u << pb;
   int32_t v = 0;
   if (total == 0) {
@@ -522,7 +522,7 @@ uint64_t container_bound(uint64_t n, uint32_t S) {
 
 int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container,
                      uint64_t container_cap, void *scratch, uint64_t scratch_bytes,
-                     cudaStream_t st) {
+                     cudaStream_t st, uint32_t low_prob_bits) {
   const ScratchLayout L = scratch_layout(n, S);
   if (scratch_bytes < L.total) {
     set_error("encode: scratch of %llu bytes is smaller than the %llu required",
@@ -543,7 +543,7 @@ int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container
                                       (uint16_t *)(sc + kScratchFreq),
                                       (uint32_t *)(sc + kScratchTab),
                                       (uint32_t *)(sc + kScratchMisc),
-                                      (uint16_t *)(cont + kFreqOffset));
+                                      (uint16_t *)(cont + kFreqOffset), low_prob_bits);
   NZ_LAUNCH_CHECK("normalize_kernel");
   if (nu) {
     uint32_t blocks = (nu + kEncWarps - 1) / kEncWarps;
@@ -623,7 +623,7 @@ extern "C" int nz_encode_exponents(const void *exp_in, uint64_t n, uint32_t lane
     return NZ_E_ARG;
   }
   return nz::encode_exponents(exp_in, n, lane_symbols, container, container_cap, scratch,
-                              scratch_bytes, (cudaStream_t)stream);
+                              scratch_bytes, (cudaStream_t)stream, nz::kDefaultLowProbBits);
 }
 
 // ---------------------------------------------------------------------------
@@ -701,7 +701,7 @@ extern "C" int nz_encode_exponents_static_scratch(const void *exp_in, uint64_t n
   // (a memset on the stream) before counting; every other region is written in
   // full for the units of this call before it is read.
   return nz::encode_exponents(exp_in, n, lane_symbols, container, container_cap, scratch,
-                              kStaticScratchBytes, (cudaStream_t)stream);
+                              kStaticScratchBytes, (cudaStream_t)stream, nz::kDefaultLowProbBits);
 }
 
 extern "C" int nz_container_bytes(const void *container, uint64_t *total_bytes,

@@ -51,7 +51,7 @@
  * (S/2 words is the lane's share of the raw unit) or when the coded form is
  * not smaller than the raw form.
  *
- * rANS: 32-bit state x in [2^16, 2^32), prob_bits-bit probabilities (10, 11 or
+ * rANS: 32-bit state x in [2^16, 2^32), prob_bits-bit probabilities (9 to
  * 12), 16-bit renormalisation.  Decoding one symbol, with M = 2^prob_bits:
  *     slot = x & (M-1); s = symbol whose [cum, cum+freq) holds slot;
  *     x = freq[s]*(x >> prob_bits) + slot - cum[s];
@@ -61,13 +61,18 @@
  * prob_bits is chosen from the number of distinct symbols d of the tensor:
  * 10 for d <= 32, 11 for d <= 64, else 12.  Exponent streams of network
  * weights have about 30 distinct values, and a 1024-slot decode table can be
- * replicated across all 32 shared-memory banks of the GPU decoder.
+ * replicated across the shared-memory banks of the GPU decoder.  The
+ * whole-tensor compressor lowers the first step to 9 bits at precision 7
+ * (nzo_choose_prob_bits_for): with 8 fraction bits stored per element the
+ * exponent stream is a quarter of the stored bytes, the coarser table costs
+ * 0.2 % of them, and 512 slots leave one table copy per bank.
  */
 #include <stdint.h>
 #include <stddef.h>
 #include <stdlib.h>
 #include <string.h>
 
+#define NZO_MIN_PROB_BITS 9
 #define NZO_MAX_PROB_BITS 12
 #define NZO_MAX_PROB_SCALE (1u << NZO_MAX_PROB_BITS)
 #define NZO_STATE_LOW (1u << 16)
@@ -80,7 +85,7 @@ typedef struct nzo_header {
   uint32_t lane_symbols;   /* S */
   uint32_t len_quantum;    /* lenq: words per length-byte step */
   uint32_t n_units;
-  uint32_t prob_bits;      /* 10, 11 or 12 */
+  uint32_t prob_bits;      /* 9 .. 12 */
   uint64_t payload_offset; /* byte offset of the payload in the container */
   uint64_t payload_words;  /* payload length in 16-bit words */
   uint64_t total_bytes;    /* container length, multiple of 16 */
@@ -183,6 +188,12 @@ uint32_t nzo_choose_prob_bits(const uint64_t *hist) {
   uint32_t d = 0;
   for (int i = 0; i < 256; ++i) d += hist[i] != 0;
   return d <= 32 ? 10u : (d <= 64 ? 11u : 12u);
+}
+
+/* The same for a tensor compressed at precision s (0, 1, 3 or 7). */
+uint32_t nzo_choose_prob_bits_for(const uint64_t *hist, int s) {
+  const uint32_t pb = nzo_choose_prob_bits(hist);
+  return (s == 7 && pb == 10u) ? NZO_MIN_PROB_BITS : pb;
 }
 
 /* Integer-only normalisation of a histogram to prob_bits-bit frequencies
@@ -354,12 +365,12 @@ uint64_t nzo_encode(const uint8_t *sym, uint64_t n, uint32_t lane_symbols,
 
   uint16_t freq[256], cum[257];
   uint32_t pb = prob_bits;
-  if (freq_in && pb >= 10 && pb <= NZO_MAX_PROB_BITS) {
+  if (freq_in && pb >= NZO_MIN_PROB_BITS && pb <= NZO_MAX_PROB_BITS) {
     memcpy(freq, freq_in, sizeof(freq));
   } else {
     uint64_t hist[256];
     nzo_histogram(sym, n, hist);
-    if (pb < 10 || pb > NZO_MAX_PROB_BITS) pb = nzo_choose_prob_bits(hist);
+    if (pb < NZO_MIN_PROB_BITS || pb > NZO_MAX_PROB_BITS) pb = nzo_choose_prob_bits(hist);
     nzo_normalize(hist, pb, freq);
   }
   uint32_t pad = 0;
@@ -495,7 +506,7 @@ int nzo_decode(const uint8_t *in, uint64_t in_bytes, uint8_t *sym_out,
   if (h->total_bytes > in_bytes) return -7;
 
   const uint32_t pb = h->prob_bits;
-  if (pb < 10 || pb > NZO_MAX_PROB_BITS) return -4;
+  if (pb < NZO_MIN_PROB_BITS || pb > NZO_MAX_PROB_BITS) return -4;
   const uint32_t M = 1u << pb;
   const uint16_t *freq = (const uint16_t *)(in + 64);
   uint16_t cum[257];
@@ -535,8 +546,11 @@ int nzo_decode(const uint8_t *in, uint64_t in_bytes, uint8_t *sym_out,
 uint64_t nzo_compress_bf16(const uint16_t *v, uint64_t n, int s,
                            uint32_t lane_symbols, uint8_t *exp_scratch,
                            uint8_t *frac_out, uint8_t *cont_out, uint64_t cap) {
+  uint64_t hist[256];
   nzo_split(v, n, s, exp_scratch, frac_out);
-  return nzo_encode(exp_scratch, n, lane_symbols, NULL, 0, cont_out, cap);
+  nzo_histogram(exp_scratch, n, hist);
+  return nzo_encode(exp_scratch, n, lane_symbols, NULL, nzo_choose_prob_bits_for(hist, s),
+                    cont_out, cap);
 }
 
 /* decompress = decode + merge */

@@ -50,7 +50,8 @@ def main():
         same = int((O.merge(ea, fa, s) == allp).sum())
         assert same == expected_from_survey["roundtrip_identical_patterns"][str(s)]
         S = O.default_lane_symbols(s)
-        cont = O.encode(exp, S)
+        cont, frac_c = O.compress_bf16(bits, s, S)       # the whole-tensor compressor's choices
+        assert np.array_equal(frac_c, frac)
         rt = O.decompress_bf16(cont, frac, n, s, canonical_nan=True)
         h = O.histogram(exp).astype(np.float64)
         p = h[h > 0] / h.sum()
@@ -62,6 +63,7 @@ def main():
             "exp_crc32": hex(O.crc32(exp)), "frac_crc32": hex(O.crc32(frac)),
             "lane_symbols": S, "container_bytes": int(cont.size),
             "container_crc32": hex(O.crc32(cont)), "roundtrip_crc32": hex(O.crc32(rt)),
+            "prob_bits": O.parse_header(cont)["prob_bits"],
             "roundtrip_identical_patterns": same, "exponent_entropy_bits": entropy,
             "ideal_bytes": ideal, "stored_bytes": int(cont.size + frac.size),
             "max_abs_error": err,

@@ -77,7 +77,9 @@ def test_config1_golden_values():
         e, f = O.split(bits, s)
         assert hex(O.crc32(e)) == g["exp_crc32"]
         assert hex(O.crc32(f)) == g["frac_crc32"]
-        cont = O.encode(e, g["lane_symbols"])
+        cont, f2 = O.compress_bf16(bits, s, g["lane_symbols"])
+        assert np.array_equal(f2, f)
+        assert O.parse_header(cont)["prob_bits"] == g["prob_bits"]
         assert cont.size == g["container_bytes"]
         assert hex(O.crc32(cont)) == g["container_crc32"]
         rt = O.decompress_bf16(cont, f, bits.size, s, canonical_nan=True)
@@ -180,10 +182,24 @@ def test_external_frequency_table_is_honoured():
     a = O.encode(exp, 256)
     b = O.encode(exp, 256, freq=f, prob_bits=O.choose_prob_bits(hist))
     assert np.array_equal(a, b)
-    for pb in (10, 11, 12):       # every resolution round-trips
+    for pb in (9, 10, 11, 12):    # every resolution round-trips
         c = O.encode(exp, 256, prob_bits=pb)
         assert O.parse_header(c)["prob_bits"] == pb
         assert np.array_equal(O.decode(c, exp.size), exp)
+
+
+def test_lossless_compress_uses_nine_bit_probabilities():
+    bits = gaussian_bits(50000, 5)
+    hist = O.histogram(O.split(bits, 7)[0])
+    assert O.choose_prob_bits(hist) == 10 and O.choose_prob_bits(hist, 7) == 9
+    assert O.choose_prob_bits(hist, 3) == 10
+    for s, pb in ((7, 9), (3, 10), (1, 10), (0, 10)):
+        cont, frac = O.compress_bf16(bits, s)
+        assert O.parse_header(cont)["prob_bits"] == pb
+        assert np.array_equal(O.decompress_bf16(cont, frac, bits.size, s),
+                              O.merge(*O.split(bits, s), s))
+    wide = np.arange(65536, dtype=np.uint16)          # every exponent: 12 bits at any precision
+    assert O.parse_header(O.compress_bf16(wide, 7)[0])["prob_bits"] == 12
 
 
 def test_corrupt_containers_are_rejected_or_decode_without_crashing():
