@@ -107,47 +107,81 @@ struct LutView {
   uint32_t mask;    // 2^pb - 1
   uint32_t stride;  // bytes between slots (4 x copies)
   uint32_t pb;      // probability bits
-  uint32_t one, two, k64k;  // 1, 2 and 65536 in registers the compiler cannot fold
-  uint32_t neg4096;         // -4096 likewise
+  uint32_t k64k;    // 65536 in a register: keeps the shift-in an integer multiply-add
 };
 
-// One symbol.  Returns the table entry (symbol | bias << 8 | freq << 20); the
-// symbol is its low byte.  Written in PTX so that the renormalisation stays
-// predicated (no divergent branch), the 16-bit stream word is loaded straight
-// into a 32-bit register, and the address / shift-in / pointer arithmetic is
-// expressed as integer multiply-adds: the integer ALU pipe (64 lanes per clock
-// per SM) is this kernel's limiter, the FMA pipe that runs IMAD is idle.
+// Table entry: symbol << 23 | freq << 12 | (slot - first slot of the symbol).
+// Frequencies never exceed 2047 (the encoder's choice of resolution sees to
+// that, the table build checks it), so bit 31 is clear.  The symbol sits where
+// the exponent of the upper bf16 of an output word goes, and 16 bits above
+// where the exponent of the lower one goes.
+constexpr uint32_t kEntSymShift = 23;
+constexpr uint32_t kEntFreqShift = 12;
+constexpr uint32_t kEntLowMask = (1u << kEntSymShift) - 1u;   // freq << 12 | offset
+__device__ __forceinline__ uint32_t entry_symbol(uint32_t ent) { return ent >> kEntSymShift; }
+
+// One symbol.  Returns the table entry.  Written in PTX so that the
+// renormalisation stays predicated (no divergent branch) and the 16-bit stream
+// word is loaded straight into a 32-bit register.  ROW is log2 of the bytes
+// between table slots when the caller knows it at compile time (0 = use
+// lv.stride): a constant shift folds into the address add, which shortens the
+// dependent chain x -> slot -> entry -> x that bounds a lane's rate.
+// The state update uses f*(q - 4096) + (f*4096 + offset) = f*q + offset
+// (mod 2^32), so that the entry's low 23 bits serve as the addend unshifted.
+template <int ROW>
 __device__ __forceinline__ uint32_t decode_step(LaneState &st, const LutView &lv) {
   uint32_t ent;
-  asm volatile(
-      "{\n\t"
-      ".reg .b32 a, q, f, b;\n\t"
-      ".reg .pred r;\n\t"
-      "and.b32 a, %1, %5;\n\t"
-      "mad.lo.u32 a, a, %6, %4;\n\t"         // slot * stride + lane's table base
-      "ld.shared.u32 %0, [a];\n\t"
-      "shr.u32 q, %1, %7;\n\t"
-      "mad.lo.u32 q, q, %8, %11;\n\t"        // q - 4096 (see below), on the FMA pipe
-      "shr.u32 f, %0, 20;\n\t"
-      "shr.u32 b, %0, 8;\n\t"                // freq << 12 | bias
-      "mad.lo.u32 %1, f, q, b;\n\t"          // f*(q-4096) + (f*4096 + bias) = f*q + bias (mod 2^32)
-      "setp.lt.u32 r, %1, 65536;\n\t"
-      "@r mad.lo.u32 %1, %1, %9, %3;\n\t"    // x = x * 65536 + w
-      "@r mad.lo.u32 %2, %8, %10, %2;\n\t"   // p += 2
-      "@r ld.shared.u16 %3, [%2];\n\t"
-      "}"
-      : "=&r"(ent), "+r"(st.x), "+r"(st.p), "+r"(st.w)
-      : "r"(lv.base), "r"(lv.mask), "r"(lv.stride), "r"(lv.pb), "r"(lv.one), "r"(lv.k64k),
-        "r"(lv.two), "r"(lv.neg4096));
+  if (ROW > 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 a, q, f, b;\n\t"
+        ".reg .pred r;\n\t"
+        "and.b32 a, %1, %5;\n\t"
+        "shl.b32 a, a, %8;\n\t"
+        "add.u32 a, a, %4;\n\t"                // slot * 2^ROW + lane's table base
+        "ld.shared.u32 %0, [a];\n\t"
+        "shr.u32 q, %1, %6;\n\t"
+        "add.s32 q, q, -4096;\n\t"
+        "and.b32 b, %0, 0x7FFFFF;\n\t"         // freq << 12 | offset
+        "shr.u32 f, b, 12;\n\t"
+        "mad.lo.u32 %1, f, q, b;\n\t"
+        "setp.lt.u32 r, %1, 65536;\n\t"
+        "@r mad.lo.u32 %1, %1, %7, %3;\n\t"    // x = x * 65536 + w
+        "@r add.u32 %2, %2, 2;\n\t"
+        "@r ld.shared.u16 %3, [%2];\n\t"
+        "}"
+        : "=&r"(ent), "+r"(st.x), "+r"(st.p), "+r"(st.w)
+        : "r"(lv.base), "r"(lv.mask), "r"(lv.pb), "r"(lv.k64k), "n"(ROW));
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 a, q, f, b;\n\t"
+        ".reg .pred r;\n\t"
+        "and.b32 a, %1, %5;\n\t"
+        "mad.lo.u32 a, a, %6, %4;\n\t"         // slot * stride + lane's table base
+        "ld.shared.u32 %0, [a];\n\t"
+        "shr.u32 q, %1, %7;\n\t"
+        "add.s32 q, q, -4096;\n\t"
+        "and.b32 b, %0, 0x7FFFFF;\n\t"         // freq << 12 | offset
+        "shr.u32 f, b, 12;\n\t"
+        "mad.lo.u32 %1, f, q, b;\n\t"
+        "setp.lt.u32 r, %1, 65536;\n\t"
+        "@r mad.lo.u32 %1, %1, %8, %3;\n\t"    // x = x * 65536 + w
+        "@r add.u32 %2, %2, 2;\n\t"
+        "@r ld.shared.u16 %3, [%2];\n\t"
+        "}"
+        : "=&r"(ent), "+r"(st.x), "+r"(st.p), "+r"(st.w)
+        : "r"(lv.base), "r"(lv.mask), "r"(lv.stride), "r"(lv.pb), "r"(lv.k64k));
+  }
   return ent;
 }
 
-// Merge two decoded symbols (low bytes of ea, eb) with their fields.
+// Merge two decoded symbols (table entries ea, eb) with their fields.
 template <int S>
 __device__ __forceinline__ uint32_t merge_pair_generic(uint32_t ea, uint32_t eb, uint32_t fa,
                                                        uint32_t fb, bool canon) {
   uint32_t out[2];
-  const uint32_t e[2] = {ea & 0xFFu, eb & 0xFFu};
+  const uint32_t e[2] = {entry_symbol(ea), entry_symbol(eb)};
   const uint32_t f[2] = {fa, fb};
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
@@ -171,11 +205,12 @@ __device__ __forceinline__ uint32_t field_of(uint64_t bits, int j) {
   return (uint32_t)(bits >> (8 * byte + shift)) & ((1u << FB) - 1u);
 }
 
-// Lossless fast path: two symbols + two fraction bytes -> one 32-bit word.
+// Lossless fast path: two entries + two fraction bytes -> one 32-bit word.
 //   sel picks the two fraction bytes (a in both low bytes, b in both high).
+// The upper halves of the two entries already hold the exponents in place.
 __device__ __forceinline__ uint32_t merge_pair_s7(uint32_t ea, uint32_t eb, uint32_t fw,
                                                   uint32_t sel) {
-  const uint32_t e = __byte_perm(ea, eb, 0x4400) << 7;   // exp_a<<7 | exp_b<<23 (+spill)
+  const uint32_t e = __byte_perm(ea, eb, 0x7632);        // ea >> 16 | eb & 0xFFFF0000
   const uint32_t g = __byte_perm(fw, 0, sel);            // fa fa fb fb
   return (e & 0x7F807F80u) | (g & 0x807F807Fu);
 }
@@ -282,10 +317,13 @@ __device__ __forceinline__ void raise(uint32_t *status, uint32_t bits) {
 
 // Exponent-only output: the 8 symbols of a lane's block as one 64-bit store.
 __device__ __forceinline__ void store_exp_block(const uint32_t (&ent)[8], uint8_t *exp) {
-  const uint32_t lo = __byte_perm(__byte_perm(ent[0], ent[1], 0x0040),
-                                  __byte_perm(ent[2], ent[3], 0x0040), 0x5410);
-  const uint32_t hi = __byte_perm(__byte_perm(ent[4], ent[5], 0x0040),
-                                  __byte_perm(ent[6], ent[7], 0x0040), 0x5410);
+  uint32_t b[8];                                          // symbol in the top byte
+#pragma unroll
+  for (int k = 0; k < 8; ++k) b[k] = ent[k] << (24 - kEntSymShift);
+  const uint32_t lo = __byte_perm(__byte_perm(b[0], b[1], 0x0073),
+                                  __byte_perm(b[2], b[3], 0x0073), 0x5410);
+  const uint32_t hi = __byte_perm(__byte_perm(b[4], b[5], 0x0073),
+                                  __byte_perm(b[6], b[7], 0x0073), 0x5410);
   __stcs(reinterpret_cast<uint2 *>(exp), make_uint2(lo, hi));
 }
 
@@ -294,7 +332,7 @@ __device__ __forceinline__ void decode_one_block(LaneState &st, const LutView &l
                                                  uint16_t *out, uint8_t *exp) {
   uint32_t ent[8];
 #pragma unroll
-  for (int t = 0; t < 8; ++t) ent[t] = decode_step(st, lut);
+  for (int t = 0; t < 8; ++t) ent[t] = decode_step<0>(st, lut);
   if (MERGE) {
     store_block<S, CANON>(ent, fbits, out);
   } else {
@@ -350,7 +388,7 @@ __device__ __forceinline__ void emit_guarded(uint32_t sym, uint64_t e, const Dec
     const uint64_t bit = e * (S + 1);
     const uint32_t shift = 7 - S - (uint32_t)(bit & 7);
     const uint32_t field = ((uint32_t)a.frac[bit >> 3] >> shift) & ((2u << S) - 1u);
-    a.out_bf16[e] = (uint16_t)merge_pair_generic<S>(sym, 0, field, 0, a.canon != 0);
+    a.out_bf16[e] = (uint16_t)merge_pair_generic<S>(sym << kEntSymShift, 0, field, 0, a.canon != 0);
   } else {
     a.out_exp[e] = (uint8_t)sym;
   }
@@ -383,6 +421,7 @@ __device__ __forceinline__ uint64_t frac_from_ring(uint32_t addr) {
 }
 
 constexpr int kChains = NZ_DECODE_CHAINS;        // units a warp decodes side by side
+constexpr int kFastRow = 7;                      // 128-byte table rows: one copy per bank
 constexpr int kRolled = NZ_DECODE_ROLLED;        // blocks per trip of the rolled decode loop
 constexpr uint32_t kRingSlots = 4;               // blocks of fractions in flight per unit + 1
 constexpr uint32_t kRingUnitBytes = 256;         // 32 lanes x 8 bytes
@@ -395,7 +434,7 @@ constexpr uint32_t kRingBytes = kRingSlots * kRingSlotBytes;
 // memory, fetched three blocks ahead with per-lane asynchronous copies; the
 // narrower fractions of precisions 0 and 1 (1 and 2 bytes per lane and block)
 // are fetched four blocks at a time by the whole warp.
-template <int S, bool MERGE, bool CANON>
+template <int S, bool MERGE, bool CANON, int ROW>
 __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], const LutView &lut,
                                                     uint32_t n_blocks,
                                                     const uint8_t *(&frac)[kChains],
@@ -456,9 +495,9 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
         for (int t = 0; t < 4; ++t) {
           uint32_t e0[kChains], e1[kChains];
 #pragma unroll
-          for (int c = 0; c < kChains; ++c) e0[c] = decode_step(st[c], lut);
+          for (int c = 0; c < kChains; ++c) e0[c] = decode_step<ROW>(st[c], lut);
 #pragma unroll
-          for (int c = 0; c < kChains; ++c) e1[c] = decode_step(st[c], lut);
+          for (int c = 0; c < kChains; ++c) e1[c] = decode_step<ROW>(st[c], lut);
 #pragma unroll
           for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
         }
@@ -506,9 +545,9 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
         for (int t = 0; t < 4; ++t) {
           uint32_t e0[kChains], e1[kChains];
 #pragma unroll
-          for (int c = 0; c < kChains; ++c) e0[c] = decode_step(st[c], lut);
+          for (int c = 0; c < kChains; ++c) e0[c] = decode_step<ROW>(st[c], lut);
 #pragma unroll
-          for (int c = 0; c < kChains; ++c) e1[c] = decode_step(st[c], lut);
+          for (int c = 0; c < kChains; ++c) e1[c] = decode_step<ROW>(st[c], lut);
 #pragma unroll
           for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
         }
@@ -583,9 +622,9 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
       for (int t = 0; t < 4; ++t) {
         uint32_t e0[kChains], e1[kChains];
 #pragma unroll
-        for (int c = 0; c < kChains; ++c) e0[c] = decode_step(st[c], lut);
+        for (int c = 0; c < kChains; ++c) e0[c] = decode_step<ROW>(st[c], lut);
 #pragma unroll
-        for (int c = 0; c < kChains; ++c) e1[c] = decode_step(st[c], lut);
+        for (int c = 0; c < kChains; ++c) e1[c] = decode_step<ROW>(st[c], lut);
 #pragma unroll
         for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
       }
@@ -598,7 +637,7 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
 #pragma unroll
       for (int t = 0; t < 8; ++t)
 #pragma unroll
-        for (int c = 0; c < kChains; ++c) e[c][t] = decode_step(st[c], lut);
+        for (int c = 0; c < kChains; ++c) e[c][t] = decode_step<ROW>(st[c], lut);
 #pragma unroll
       for (int c = 0; c < kChains; ++c) store_exp_block(e[c], exp[c] + k * 256);
     }
@@ -772,8 +811,8 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
     // the partial block that ends the tensor
     const uint64_t e0 = e_lane + (uint64_t)full_blocks * 256;
     for (int t = 0; t < 8; ++t) {
-      const uint32_t ent = decode_step(st, lv);
-      emit_guarded<S, MERGE>(ent & 0xFFu, e0 + t, a);
+      const uint32_t ent = decode_step<0>(st, lv);
+      emit_guarded<S, MERGE>(entry_symbol(ent), e0 + t, a);
     }
   }
 }
@@ -812,6 +851,7 @@ decode_kernel(const BatchArgs batch) {
   uint16_t *cum_sh = reinterpret_cast<uint16_t *>(smem + a.lut_bytes + 8 * 32);  // 257 entries
   uint32_t *flag_sh = reinterpret_cast<uint32_t *>(smem + a.lut_bytes + 8 * 32 + 520);
   uint32_t *pb_sh = flag_sh + 1;
+  uint32_t *wide_sh = flag_sh + 2;   // set when a frequency does not fit the table entry
   uint8_t *slots = smem + a.lut_bytes + 1024;
   (void)lut_bytes;
   const uint32_t bar = smem_u32(&bars[warp]);
@@ -826,7 +866,6 @@ decode_kernel(const BatchArgs batch) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (threadIdx.x == 0) *flag_sh = 0;
   __syncwarp();
   // Programmatic dependent launch: let the next kernel of the stream start its
   // own launch now, and do not touch global memory before the previous kernel
@@ -864,7 +903,14 @@ decode_kernel(const BatchArgs batch) {
       if (lane >= (uint32_t)o) incl += v;
     }
     uint32_t run = incl - sum;
-    if (lane == 0) cum_sh[0] = 0;
+    uint32_t widest = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) widest = max(widest, f[k]);
+    const bool too_wide = __any_sync(0xFFFFFFFFu, widest >> (kEntSymShift - kEntFreqShift));
+    if (lane == 0) {
+      cum_sh[0] = 0;
+      *wide_sh = too_wide ? 1u : 0u;
+    }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       run += f[k];
@@ -872,11 +918,12 @@ decode_kernel(const BatchArgs batch) {
     }
   }
   if (threadIdx.x == (n_warps > 1 ? 32u : 0u)) {
-    if (h->magic != kMagic || h->version != 1 || h->n_symbols != a.n || h->lane_symbols != a.S ||
-        h->n_units != a.n_units || h->len_quantum != len_quantum(a.S) ||
-        h->payload_offset != pay_off || h->payload_words > max_words ||
-        h->prob_bits < kMinProbBits || h->prob_bits > kMaxProbBits)
-      atomicOr(flag_sh, NZ_STATUS_BAD_HEADER);
+    const bool ok = h->magic == kMagic && h->version == 1 && h->n_symbols == a.n &&
+                    h->lane_symbols == a.S && h->n_units == a.n_units &&
+                    h->len_quantum == len_quantum(a.S) && h->payload_offset == pay_off &&
+                    h->payload_words <= max_words && h->prob_bits >= kMinProbBits &&
+                    h->prob_bits <= kMaxProbBits;
+    *flag_sh = ok ? 0u : (uint32_t)NZ_STATUS_BAD_HEADER;
     *pb_sh = h->prob_bits;
   }
   __syncthreads();
@@ -884,7 +931,7 @@ decode_kernel(const BatchArgs batch) {
   // computes the same verdict
   const uint32_t pb = *pb_sh;
   uint32_t bad = *flag_sh;
-  if (pb < kMinProbBits || pb > kMaxProbBits || cum_sh[256] != (1u << (pb & 15)))
+  if (pb < kMinProbBits || pb > kMaxProbBits || cum_sh[256] != (1u << (pb & 15)) || *wide_sh)
     bad |= NZ_STATUS_BAD_HEADER;
   if (bad) {
     // copies may be in flight into this warp's slots: let them land before leaving
@@ -903,18 +950,15 @@ decode_kernel(const BatchArgs batch) {
   if (row_shift > 7) row_shift = 7;                         // 32 copies are enough
   lv.stride = 1u << row_shift;
   lv.base = smem_u32(smem) + ((lane << 2) & (lv.stride - 1u));
-  lv.one = a.S ? 1u : 0u;
-  lv.two = lv.one << 1;
-  lv.k64k = lv.one << 16;
-  lv.neg4096 = 0u - (lv.one << 12);
+  lv.k64k = a.S ? 65536u : 0u;      // a.S is never 0; the compiler cannot know
   uint32_t *lut_w = reinterpret_cast<uint32_t *>(smem);
   const uint32_t wsh = row_shift - 2;                     // log2 of the words per slot row
   for (uint32_t sym = warp; sym < 256; sym += n_warps) {
     const uint32_t start = cum_sh[sym], end = cum_sh[sym + 1];
-    const uint32_t hi = (end - start) << 20;
+    const uint32_t hi = (sym << kEntSymShift) | ((end - start) << kEntFreqShift);
     const uint32_t words = (end - start) << wsh;
     uint32_t *dst = lut_w + (start << wsh);
-    for (uint32_t k = lane; k < words; k += 32) dst[k] = sym | ((k >> wsh) << 8) | hi;
+    for (uint32_t k = lane; k < words; k += 32) dst[k] = hi | (k >> wsh);
   }
   const bool canon = MERGE && a.canon && (cum_sh[256] != cum_sh[255]);
   __syncthreads();
@@ -959,9 +1003,11 @@ decode_kernel(const BatchArgs batch) {
           xb[c] = MERGE ? nullptr : a.out_exp + e;
         }
         if (canon)
-          decode_blocks_multi<S, MERGE, true>(st, lv, a.S / 8, fr, ob, xb, ring);
+          decode_blocks_multi<S, MERGE, true, 0>(st, lv, a.S / 8, fr, ob, xb, ring);
+        else if (row_shift == kFastRow)
+          decode_blocks_multi<S, MERGE, false, kFastRow>(st, lv, a.S / 8, fr, ob, xb, ring);
         else
-          decode_blocks_multi<S, MERGE, false>(st, lv, a.S / 8, fr, ob, xb, ring);
+          decode_blocks_multi<S, MERGE, false, 0>(st, lv, a.S / 8, fr, ob, xb, ring);
         bool low = true;
 #pragma unroll
         for (int c = 0; c < kChains; ++c) low = low && st[c].x == kStateLow;

@@ -97,6 +97,7 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
   __shared__ int32_t f[256];
   __shared__ uint64_t red64[8];
   __shared__ uint32_t red32[8];
+  __shared__ uint32_t redmx[8];
   __shared__ int32_t top_sh[8];
   const int t = threadIdx.x;  // 256 threads
   const int lane = t & 31, wid = t >> 5;
@@ -104,24 +105,30 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
   // total count and number of distinct symbols
   uint64_t tot = h;
   uint32_t dis = h != 0;
+  uint32_t mx = (uint32_t)h;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     tot += __shfl_xor_sync(0xFFFFFFFFu, tot, o);
     dis += __shfl_xor_sync(0xFFFFFFFFu, dis, o);
+    mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
   }
   if (lane == 0) {
     red64[wid] = tot;
     red32[wid] = dis;
+    redmx[wid] = mx;
   }
   __syncthreads();
   uint64_t total = 0;
-  uint32_t distinct = 0;
+  uint32_t distinct = 0, top_count = 0;
 #pragma unroll
   for (int w = 0; w < 8; ++w) {
     total += red64[w];
     distinct += red32[w];
+    top_count = max(top_count, redmx[w]);
   }
-  const uint32_t pb = distinct <= 32 ? low_pb : (distinct <= 64 ? 11u : 12u);
+  // 12 bits only while the largest frequency is sure to stay below 2048
+  const uint32_t wide_pb = ((uint64_t)top_count * 4096u < total * 1900u) ? 12u : 11u;
+  const uint32_t pb = distinct <= 32 ? low_pb : (distinct <= 64 ? 11u : wide_pb);
   const uint32_t M = 1u << pb;
   int32_t v = 0;
   if (total == 0) {

@@ -59,7 +59,8 @@
  * The encoder runs the lane's symbols backwards from state 2^16.
  *
  * prob_bits is chosen from the number of distinct symbols d of the tensor:
- * 10 for d <= 32, 11 for d <= 64, else 12.  Exponent streams of network
+ * 10 for d <= 32, 11 for d <= 64, else 12 (11 if one symbol has 46 % of the
+ * counts or more: no frequency may exceed 2047).  Exponent streams of network
  * weights have about 30 distinct values, and a 1024-slot decode table can be
  * replicated across the shared-memory banks of the GPU decoder.  The
  * whole-tensor compressor lowers the first step to 9 bits at precision 7
@@ -183,11 +184,22 @@ void nzo_histogram(const uint8_t *sym, size_t n, uint64_t *hist) {
 }
 
 /* Probability resolution for a histogram: 10 bits up to 32 distinct symbols,
- * 11 up to 64, else 12. */
+ * 11 up to 64, else 12 -- but 11 when the most frequent symbol holds
+ * 1900/4096 of the counts or more, so that no normalised frequency ever
+ * needs more than 11 bits (rounding and the fix-up of nzo_normalize add at
+ * most 128 to the largest entry).  The GPU decoder packs symbol, frequency
+ * and slot offset into one 32-bit table entry and relies on that bound. */
 uint32_t nzo_choose_prob_bits(const uint64_t *hist) {
   uint32_t d = 0;
-  for (int i = 0; i < 256; ++i) d += hist[i] != 0;
-  return d <= 32 ? 10u : (d <= 64 ? 11u : 12u);
+  uint64_t total = 0, top = 0;
+  for (int i = 0; i < 256; ++i) {
+    d += hist[i] != 0;
+    total += hist[i];
+    if (hist[i] > top) top = hist[i];
+  }
+  if (d <= 32) return 10u;
+  if (d <= 64) return 11u;
+  return (top * 4096u < total * 1900u) ? 12u : 11u;
 }
 
 /* The same for a tensor compressed at precision s (0, 1, 3 or 7). */

@@ -87,6 +87,8 @@ def exponent_streams():
         [np.arange(256, dtype=np.uint8), np.full(90000, 17, np.uint8)])
     yield "fifty_symbols", rng.choice(np.arange(60, 110, dtype=np.uint8), size=70000,
                                       p=np.r_[np.full(10, 0.08), np.full(40, 0.005)])
+    yield "hundred_symbols_top_40pct", rng.choice(
+        np.arange(100, 200, dtype=np.uint8), size=80000, p=np.r_[0.4, np.full(99, 0.6 / 99)])
     yield "single_element", np.array([200], np.uint8)
     yield "half_raw_half_coded", np.concatenate(
         [rng.integers(0, 256, size=32768, dtype=np.uint8), np.full(32768, 9, np.uint8)])
@@ -183,6 +185,25 @@ def test_config1_seed0_matrix_matches_golden():
     cont, frac, mw = A.compress(x, 7, 256)
     out, _ = A.decompress(cont, frac, x.numel(), 7, 256, mw)
     assert torch.equal(out.view(torch.int16), x.view(torch.int16))
+
+
+def test_wide_alphabets_keep_frequencies_in_eleven_bits():
+    rng = np.random.default_rng(11)
+    for top in (0.3, 0.45, 0.47, 0.6, 0.95):
+        sym = rng.choice(np.arange(256, dtype=np.uint8), size=120000,
+                         p=np.r_[top, np.full(255, (1 - top) / 255)])
+        cont, mw = A.encode(A.dev_u8(sym), 256)
+        hdr = O.parse_header(cont.cpu().numpy())
+        assert hdr["prob_bits"] == (12 if top < 0.46 else 11)
+        assert int(np.frombuffer(cont.cpu().numpy()[64:576].tobytes(), np.uint16).max()) <= 2047
+        exp, status = A.decode_exponents(cont, sym.size, 256, mw)
+        assert status == 0 and np.array_equal(exp.cpu().numpy(), sym)
+    # a container whose table holds a wider frequency is refused, not decoded wrongly
+    sym = np.concatenate([np.arange(256, dtype=np.uint8), np.full(90000, 17, np.uint8)])
+    forged = O.encode(sym, 256, prob_bits=12)
+    assert np.array_equal(O.decode(forged, sym.size), sym)
+    exp, status = A.decode_exponents(A.dev_u8(forged), sym.size, 256, 0)
+    assert status & 0x1                      # NZ_STATUS_BAD_HEADER
 
 
 # -------------------------------------------------------- malformed containers
