@@ -43,7 +43,7 @@ UNIT = "GB/s"
 # DRAM traffic of one decode launch on the largest matrix (4096x11008, precision 7),
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture summarised in
 # profiles/kernels_precision7_4096x11008.md; scaled to the average launch by elements.
-NCU_TRAFFIC_BYTES_45M = 60.34e6 + 32.8e6   # read + written by kernel end; the rest of the
+NCU_TRAFFIC_BYTES_45M = 60.49e6 + 31.9e6   # read + written by kernel end; the rest of the
 # 90 MB output is still in L2 then and is written back while the next launch runs
 NCU_TRAFFIC_ELEMENTS = 4096 * 11008
 
