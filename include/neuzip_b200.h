@@ -41,6 +41,7 @@ extern "C" {
 #define NZ_STATUS_BAD_LANES 0x4u   /* lane lengths inconsistent with the unit  */
 #define NZ_STATUS_BAD_STATE 0x8u   /* a lane did not end in the initial state  */
 #define NZ_STATUS_TIMEOUT 0x10u    /* a bounded wait on a bulk copy ran out    */
+#define NZ_STATUS_BAD_UNIT 0x20u   /* a unit number of a gather list is out of range */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int nz_version(void);
@@ -224,6 +225,39 @@ typedef struct nz_decompress_item {
 int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_t count,
                              int precision, uint32_t lane_symbols,
                              int canonical_nan, void *status, void *stream);
+
+/* Gather: decode only the units named in `unit_ids` (a device array of n_ids
+ * unit numbers, each < ceil(n / (32 * lane_symbols)); a unit is 32 *
+ * lane_symbols consecutive elements) and write them one after the other:
+ * unit_ids[i] goes to out_bf16[i * 32 * lane_symbols ...], which must hold
+ * n_ids units (the tensor's last unit may be shorter; only its elements are
+ * written).  A number may appear more than once.  Numbers out of range set
+ * NZ_STATUS_BAD_UNIT and write nothing.  The container is the one
+ * nz_compress_bf16 wrote: units are independently decodable by construction.
+ * Reference: Embedding.forward decompresses the whole table for every lookup
+ * (neuzip/nn/embedding.py:30-39 -> cuda/high_level.cu:223-250); with this call
+ * a lookup decodes the rows it touches. */
+int nz_decompress_bf16_units(const void *container, uint64_t container_bytes,
+                             const void *frac_in, uint64_t n, int precision,
+                             uint32_t lane_symbols, uint32_t max_unit_words,
+                             int canonical_nan, const void *unit_ids, uint32_t n_ids,
+                             void *out_bf16, void *status, void *stream);
+
+/* Row gather on top of nz_decompress_bf16_units: the tensor is a table of
+ * n / row_len rows; row rows_i64[i] (a device array of n_rows_out int64) is
+ * written to out_bf16[i * row_len ...].  Three launches, no host sync: the unit
+ * list is built on the device, those units are decoded into `scratch`
+ * (nz_gather_scratch_bytes; 16-byte aligned), the rows are copied out.  Row
+ * numbers outside the table set NZ_STATUS_BAD_UNIT and leave their output row
+ * untouched.  Reference: Embedding.forward = F.embedding(x, whole decompressed
+ * table) (neuzip/nn/embedding.py:30-39). */
+uint64_t nz_gather_scratch_bytes(uint32_t n_rows_out, uint64_t row_len, uint32_t lane_symbols);
+int nz_gather_rows_bf16(const void *container, uint64_t container_bytes,
+                        const void *frac_in, uint64_t n, int precision,
+                        uint32_t lane_symbols, uint32_t max_unit_words,
+                        int canonical_nan, uint64_t row_len, const void *rows_i64,
+                        uint32_t n_rows_out, void *out_bf16, void *scratch,
+                        uint64_t scratch_bytes, void *status, void *stream);
 
 #ifdef __cplusplus
 }

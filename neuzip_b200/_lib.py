@@ -23,6 +23,7 @@ STATUS_BITS = {
     0x4: "bad lane lengths",
     0x8: "bad final state",
     0x10: "bulk-copy wait timed out",
+    0x20: "gather list names a unit that does not exist",
 }
 
 # name -> (restype, argtypes); mirrors include/neuzip_b200.h one to one
@@ -62,6 +63,11 @@ class DecompressItem(ctypes.Structure):
 _f32 = ctypes.c_float
 SIGNATURES["nz_adamw_bf16"] = (_int, [_vp, _vp, _vp, _vp, _u64, _int, _f32, _f32, _f32, _f32, _f32,
                                        _u32, _f32, _vp])
+SIGNATURES["nz_decompress_bf16_units"] = (
+    _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _vp, _u32, _vp, _vp, _vp])
+SIGNATURES["nz_gather_scratch_bytes"] = (_u64, [_u32, _u64, _u32])
+SIGNATURES["nz_gather_rows_bf16"] = (
+    _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _u64, _vp, _u32, _vp, _vp, _u64, _vp, _vp])
 SIGNATURES["nz_decompress_bf16_batch"] = (
     _int, [ctypes.POINTER(DecompressItem), _u32, _int, _u32, _int, _vp, _vp])
 

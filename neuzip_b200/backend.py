@@ -164,6 +164,42 @@ class CodecBackend:
             _ptr(out), _ptr(self._status), _stream()))
         self._denormalize(entry, out)
 
+    def read_rows(self, name: str, rows: torch.Tensor, row_len: int) -> torch.Tensor:
+        """Rows ``rows`` (any integer tensor) of the stored tensor seen as a
+        ``[numel / row_len, row_len]`` table, as a ``[rows.numel(), row_len]`` bf16 tensor.
+        Only the units that hold those rows are decoded (``nz_gather_rows_bf16``);
+        nothing synchronises with the host.  Row numbers outside the table raise at
+        the next ``check()``.  The reference decompresses the whole
+        table for every lookup (neuzip/nn/embedding.py:30-39)."""
+        entry = self._cache.get(name)
+        if entry is None:
+            raise RuntimeError("Data not found")
+        if row_len <= 0 or entry.numel % row_len:
+            raise ValueError(f"row length {row_len} does not divide the {entry.numel} stored elements")
+        rows = rows.reshape(-1).to(device="cuda", dtype=torch.int64)
+        k = rows.numel()
+        if k == 0:
+            return torch.empty(0, row_len, dtype=torch.bfloat16, device="cuda")
+        if entry.normalizers is not None:
+            # group scales follow the flat element index: decode everything, then pick
+            return self.read(name).view(-1, row_len)[rows]
+        U = 32 * entry.lane_symbols
+        per_row = 1 if U % row_len == 0 else (row_len // U if row_len % U == 0
+                                              else (row_len + U - 1) // U + 1)
+        if k * per_row >= (entry.numel + U - 1) // U:
+            # the lookups would decode as much as the whole table holds
+            return self.read(name).view(-1, row_len)[rows]
+        out = torch.empty(k, row_len, dtype=torch.bfloat16, device="cuda")
+        L = self._lib
+        scratch_bytes = int(L.nz_gather_scratch_bytes(k, row_len, entry.lane_symbols))
+        scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device="cuda")
+        _lib.check(L.nz_gather_rows_bf16(
+            _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
+            self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
+            row_len, _ptr(rows), k, _ptr(out), _ptr(scratch), scratch_bytes, _ptr(self._status),
+            _stream()))
+        return out
+
     def _denormalize(self, entry: _Entry, out: torch.Tensor) -> None:
         if entry.normalizers is not None:
             _lib.check(self._lib.nz_denormalize_bf16(_ptr(out), entry.numel, self.normalizer_size,

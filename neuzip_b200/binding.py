@@ -112,6 +112,21 @@ class Manager:
             flats = [self._be.read(h) for h in handles]
         return [t.requires_grad_(False).reshape(self.meta_dict[h]) for t, h in zip(flats, handles)]
 
+    def read_rows(self, handle: str, rows: torch.Tensor) -> torch.Tensor:
+        """``self.read(handle)[rows]`` for a tensor of two or more dimensions, decoding
+        only the parts of the stored stream that hold those rows."""
+        shape = self.meta_dict[handle]
+        if len(shape) < 2:
+            raise ValueError("read_rows needs a tensor of at least two dimensions")
+        row_len = 1
+        for d in shape[1:]:
+            row_len *= int(d)
+        if hasattr(self._be, "read_rows"):
+            flat = self._be.read_rows(handle, rows, row_len)
+        else:
+            flat = self._be.read(handle).reshape(-1, row_len)[rows.reshape(-1).long()]
+        return flat.requires_grad_(False).reshape(tuple(rows.shape) + tuple(shape[1:]))
+
     def export_entry(self, handle: str) -> dict:
         """Stored bytes + metadata of a handle (for checkpoints)."""
         blob = self._be.export_entry(handle)

@@ -286,6 +286,8 @@ struct DecodeArgs {
   uint16_t *out_bf16;
   uint8_t *out_exp;
   uint32_t *status;
+  const uint32_t *unit_list;   // units to decode, in output order (gather launches only)
+  uint32_t n_work;             // units this launch decodes: n_units, or the length of the list
 };
 
 // One launch decodes up to kMaxBatch tensors; each tensor gets its own range of
@@ -304,6 +306,8 @@ struct BatchItem {
 };
 struct BatchArgs {
   BatchItem item[kMaxBatch];
+  const uint32_t *unit_list;   // gather launches (count == 1): units of item[0] to decode
+  uint32_t n_list;
   uint32_t count;
   uint32_t n_ctas;        // == gridDim.x
   uint32_t S, slot_bytes, lut_shift, lut_bytes, ring_offset;
@@ -381,16 +385,19 @@ __device__ __forceinline__ void decode_blocks(LaneState &st, const LutView &lut,
 
 // One element with all guards, used for the partial block at the very end of
 // the tensor and for raw units.
+// `delta` is the distance (in elements) from an element's place in the tensor
+// to its place in the output: 0 except in gather launches.
 template <int S, bool MERGE>
-__device__ __forceinline__ void emit_guarded(uint32_t sym, uint64_t e, const DecodeArgs &a) {
+__device__ __forceinline__ void emit_guarded(uint32_t sym, uint64_t e, int64_t delta,
+                                             const DecodeArgs &a) {
   if (e >= a.n) return;
   if (MERGE) {
     const uint64_t bit = e * (S + 1);
     const uint32_t shift = 7 - S - (uint32_t)(bit & 7);
     const uint32_t field = ((uint32_t)a.frac[bit >> 3] >> shift) & ((2u << S) - 1u);
-    a.out_bf16[e] = (uint16_t)merge_pair_generic<S>(sym << kEntSymShift, 0, field, 0, a.canon != 0);
+    a.out_bf16[e + delta] = (uint16_t)merge_pair_generic<S>(sym << kEntSymShift, 0, field, 0, a.canon != 0);
   } else {
-    a.out_exp[e] = (uint8_t)sym;
+    a.out_exp[e + delta] = (uint8_t)sym;
   }
 }
 
@@ -778,7 +785,7 @@ __device__ __forceinline__ bool open_unit(const UnitPlan &pl, uint32_t slot, uin
 // Decode one unit on its own (raw units, the tensor's last unit, odd counts).
 template <int S, bool MERGE>
 __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPlan &pl, uint32_t u,
-                                              uint32_t slot, const LutView &lv, bool canon,
+                                              int64_t delta, uint32_t slot, const LutView &lv, bool canon,
                                               const uint8_t *payload, uint32_t lenq,
                                               uint32_t lane) {
   const uint64_t U = 32ull * a.S;
@@ -786,7 +793,7 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
   const uint64_t count = (a.n - first < U) ? (a.n - first) : U;
   if (pl.kind == kUnitRaw) {
     const uint8_t *src = payload + pl.byte0;
-    for (uint64_t i = lane; i < count; i += 32) emit_guarded<S, MERGE>(src[i], first + i, a);
+    for (uint64_t i = lane; i < count; i += 32) emit_guarded<S, MERGE>(src[i], first + i, delta, a);
     return;
   }
   if (pl.kind != kUnitCoded) return;
@@ -798,8 +805,8 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
   const uint32_t full_blocks = (uint32_t)(count / 256);
   const uint64_t e_lane = first + lane * 8;
   const uint8_t *frac_lane = MERGE ? a.frac + e_lane * (S + 1) / 8 : nullptr;
-  uint16_t *out_lane = MERGE ? a.out_bf16 + e_lane : nullptr;
-  uint8_t *exp_lane = MERGE ? nullptr : a.out_exp + e_lane;
+  uint16_t *out_lane = MERGE ? a.out_bf16 + (e_lane + delta) : nullptr;
+  uint8_t *exp_lane = MERGE ? nullptr : a.out_exp + (e_lane + delta);
   if (canon)
     decode_blocks<S, MERGE, true>(st, lv, full_blocks, frac_lane, out_lane, exp_lane);
   else
@@ -812,12 +819,14 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
     const uint64_t e0 = e_lane + (uint64_t)full_blocks * 256;
     for (int t = 0; t < 8; ++t) {
       const uint32_t ent = decode_step<0>(st, lv);
-      emit_guarded<S, MERGE>(entry_symbol(ent), e0 + t, a);
+      emit_guarded<S, MERGE>(entry_symbol(ent), e0 + t, delta, a);
     }
   }
 }
 
-template <int S, bool MERGE>
+// LIST: gather launch -- the launch decodes the units named in batch.unit_list
+// (of the single tensor item[0]) and writes them one after the other.
+template <int S, bool MERGE, bool LIST>
 __global__ void __launch_bounds__(NZ_DECODE_MAX_WARPS * 32, 1)
 decode_kernel(const BatchArgs batch) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -844,6 +853,8 @@ decode_kernel(const BatchArgs batch) {
   a.out_bf16 = batch.item[ti].out_bf16;
   a.out_exp = batch.item[ti].out_exp;
   a.status = batch.status;
+  a.unit_list = LIST ? batch.unit_list : nullptr;
+  a.n_work = LIST ? batch.n_list : a.n_units;
   const uint32_t n_warps = blockDim.x >> 5;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t lut_bytes = 4096u << a.lut_shift;           // 2^pb slots would need 4 << shift each
@@ -881,8 +892,25 @@ decode_kernel(const BatchArgs batch) {
   uint32_t u = kChains * (cta_rank * n_warps + warp);
   uint32_t parity = 0;
   UnitPlan pl[kChains];
+  uint32_t real[kChains];      // the units behind work items u .. u+kChains-1
+  auto plan_group = [&](uint32_t w) {
 #pragma unroll
-  for (int c = 0; c < kChains; ++c) pl[c] = plan_unit(a, u + c, pay_off, max_words, lane);
+    for (int c = 0; c < kChains; ++c) {
+      real[c] = w + c;
+      if (LIST) {
+        real[c] = a.n_units;                         // "no unit": plans as nothing to do
+        if (w + c < a.n_work) {
+          real[c] = __ldg(a.unit_list + w + c);
+          if (real[c] >= a.n_units) {
+            if (lane == 0) raise(a.status, NZ_STATUS_BAD_UNIT);
+            real[c] = a.n_units;
+          }
+        }
+      }
+      pl[c] = plan_unit(a, real[c], pay_off, max_words, lane);
+    }
+  };
+  plan_group(u);
   bool staged = stage_units(a, pl, pay_off, slot0, bar, lane);
 
   const uint16_t *freq_g = reinterpret_cast<const uint16_t *>(a.container + kFreqOffset);
@@ -968,7 +996,7 @@ decode_kernel(const BatchArgs batch) {
   const uint32_t lenq = len_quantum(a.S);
   const uint64_t U = 32ull * a.S;
 
-  for (; u < a.n_units; u += stride) {
+  for (; u < a.n_work; u += stride) {
     if (staged) {
       const bool arrived = wait_staged(bar, parity);
       parity ^= 1;
@@ -980,9 +1008,10 @@ decode_kernel(const BatchArgs batch) {
         return;
       }
     }
-    bool full_group = (uint64_t)(u + kChains) * U <= a.n;
+    bool full_group = true;
 #pragma unroll
-    for (int c = 0; c < kChains; ++c) full_group = full_group && pl[c].kind == kUnitCoded;
+    for (int c = 0; c < kChains; ++c)
+      full_group = full_group && pl[c].kind == kUnitCoded && (uint64_t)(real[c] + 1) * U <= a.n;
     bool done = false;
     if (full_group) {
       LaneState st[kChains];
@@ -997,10 +1026,11 @@ decode_kernel(const BatchArgs batch) {
         uint8_t *xb[kChains];
 #pragma unroll
         for (int c = 0; c < kChains; ++c) {
-          const uint64_t e = (uint64_t)(u + c) * U + lane * 8;
+          const uint64_t e = (uint64_t)real[c] * U + lane * 8;                  // in the tensor
+          const uint64_t o = LIST ? (uint64_t)(u + c) * U + lane * 8 : e;       // in the output
           fr[c] = MERGE ? a.frac + e * (S + 1) / 8 : nullptr;
-          ob[c] = MERGE ? a.out_bf16 + e : nullptr;
-          xb[c] = MERGE ? nullptr : a.out_exp + e;
+          ob[c] = MERGE ? a.out_bf16 + o : nullptr;
+          xb[c] = MERGE ? nullptr : a.out_exp + o;
         }
         if (canon)
           decode_blocks_multi<S, MERGE, true, 0>(st, lv, a.S / 8, fr, ob, xb, ring);
@@ -1016,15 +1046,15 @@ decode_kernel(const BatchArgs batch) {
     }
     if (!done) {
 #pragma unroll
-      for (int c = 0; c < kChains; ++c)
-        decode_single<S, MERGE>(a, pl[c], u + c, slot0 + c * a.slot_bytes, lv, canon, payload, lenq,
-                                lane);
+      for (int c = 0; c < kChains; ++c) {
+        const int64_t delta = LIST ? ((int64_t)(u + c) - (int64_t)real[c]) * (int64_t)U : 0;
+        decode_single<S, MERGE>(a, pl[c], real[c], delta, slot0 + c * a.slot_bytes, lv, canon,
+                                payload, lenq, lane);
+      }
     }
     // every lane is done reading the slots: fetch this warp's next group
     __syncwarp();
-#pragma unroll
-    for (int c = 0; c < kChains; ++c)
-      pl[c] = plan_unit(a, u + stride + c, pay_off, max_words, lane);
+    plan_group(u + stride);
     staged = stage_units(a, pl, pay_off, slot0, bar, lane);
   }
 }
@@ -1038,7 +1068,14 @@ struct HostItem {
   uint32_t max_unit_words;
   void *out_bf16;
   void *out_exp;
+  const uint32_t *unit_list;   // gather: device array of unit numbers (else null)
+  uint32_t n_list;
 };
+
+// Units a launch decodes for an item.
+static inline uint64_t work_units(const HostItem &it, uint32_t S) {
+  return it.unit_list ? it.n_list : unit_count(it.n, S);
+}
 
 // Grid geometry of one launch over `count` tensors.  One CTA per SM.  Every
 // warp decodes whole units, kChains at a time, so a tensor is only as fast as its
@@ -1054,7 +1091,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
     uint64_t ub = items[t].max_unit_words ? (uint64_t)items[t].max_unit_words * 2 : U;
     if (ub > U) ub = U;
     if (ub > unit_bytes) unit_bytes = ub;
-    total_units += unit_count(items[t].n, S);
+    total_units += work_units(items[t], S);
   }
   if (unit_bytes < 160) unit_bytes = 160;
   b.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
@@ -1074,13 +1111,13 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   // (or fewer when there is not enough work to give every SM a pair of units)
   const uint32_t sms = (uint32_t)sm_count();
   uint64_t total_pairs = 0;
-  for (uint32_t t = 0; t < count; ++t) total_pairs += (unit_count(items[t].n, S) + kChains - 1) / kChains;
+  for (uint32_t t = 0; t < count; ++t) total_pairs += (work_units(items[t], S) + kChains - 1) / kChains;
   uint32_t n_ctas = sms;
   if (total_pairs < n_ctas) n_ctas = (uint32_t)total_pairs;
   if (n_ctas < count) n_ctas = count;
   uint32_t ctas[kMaxBatch], used = 0;
   for (uint32_t t = 0; t < count; ++t) {
-    const uint64_t nu = unit_count(items[t].n, S);
+    const uint64_t nu = work_units(items[t], S);
     uint64_t c = total_units ? (nu * n_ctas + total_units / 2) / total_units : 1;
     const uint64_t pairs = (nu + kChains - 1) / kChains;
     if (c > pairs) c = pairs;
@@ -1090,7 +1127,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   }
   // fix the rounding: take from / give to the tensor with the most / fewest pairs per CTA
   auto load = [&](uint32_t t, uint32_t c) {
-    return (double)((unit_count(items[t].n, S) + kChains - 1) / kChains) / (double)c;
+    return (double)((work_units(items[t], S) + kChains - 1) / kChains) / (double)c;
   };
   while (used > n_ctas) {
     uint32_t best = kMaxBatch;
@@ -1104,7 +1141,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   while (used < n_ctas) {
     uint32_t best = kMaxBatch;
     for (uint32_t t = 0; t < count; ++t) {
-      const uint64_t pairs = (unit_count(items[t].n, S) + kChains - 1) / kChains;
+      const uint64_t pairs = (work_units(items[t], S) + kChains - 1) / kChains;
       if (ctas[t] < pairs && (best == kMaxBatch || load(t, ctas[t]) > load(best, ctas[best])))
         best = t;
     }
@@ -1115,7 +1152,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   // warps per CTA: enough for the busiest CTA's pairs, spread over whole rounds
   uint32_t max_pairs = 1;
   for (uint32_t t = 0; t < count; ++t) {
-    const uint64_t pairs = (unit_count(items[t].n, S) + kChains - 1) / kChains;
+    const uint64_t pairs = (work_units(items[t], S) + kChains - 1) / kChains;
     const uint32_t per_cta = (uint32_t)((pairs + ctas[t] - 1) / ctas[t]);
     if (per_cta > max_pairs) max_pairs = per_cta;
   }
@@ -1142,9 +1179,9 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   return NZ_OK;
 }
 
-template <int S, bool MERGE>
+template <int S, bool MERGE, bool LIST = false>
 static int launch_decode(const BatchArgs &b, uint32_t warps, uint32_t smem_bytes, cudaStream_t st) {
-  auto kern = decode_kernel<S, MERGE>;
+  auto kern = decode_kernel<S, MERGE, LIST>;
   NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem_bytes));
   // Programmatic stream serialisation: this launch may begin while the previous
@@ -1189,7 +1226,18 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
       b.item[t].out_exp = (uint8_t *)live[t].out_exp;
       b.item[t].n_units = (uint32_t)unit_count(live[t].n, S);
     }
+    const bool gather = live[0].unit_list != nullptr;   // gather calls pass a single item
+    b.unit_list = live[0].unit_list;
+    b.n_list = live[0].n_list;
     n_live = 0;
+    if (gather) {
+      switch (precision) {
+        case 0: return launch_decode<0, true, true>(b, warps, smem_bytes, st);
+        case 1: return launch_decode<1, true, true>(b, warps, smem_bytes, st);
+        case 3: return launch_decode<3, true, true>(b, warps, smem_bytes, st);
+        default: return launch_decode<7, true, true>(b, warps, smem_bytes, st);
+      }
+    }
     if (!merge) return launch_decode<7, false>(b, warps, smem_bytes, st);
     switch (precision) {
       case 0: return launch_decode<0, true>(b, warps, smem_bytes, st);
@@ -1226,6 +1274,8 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   it.max_unit_words = max_unit_words;
   it.out_bf16 = out_bf16;
   it.out_exp = out_exp;
+  it.unit_list = nullptr;
+  it.n_list = 0;
   return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
@@ -1313,10 +1363,176 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
       host[i].max_unit_words = it.max_unit_words;
       host[i].out_bf16 = it.out_bf16;
       host[i].out_exp = nullptr;
+      host[i].unit_list = nullptr;
+      host[i].n_list = 0;
     }
     int rc = nz::decode_many(host, m, precision, lane_symbols, canonical_nan, true, status,
                              (cudaStream_t)stream);
     if (rc) return rc;
   }
+  return NZ_OK;
+}
+
+extern "C" int nz_decompress_bf16_units(const void *container, uint64_t container_bytes,
+                                        const void *frac_in, uint64_t n, int precision,
+                                        uint32_t lane_symbols, uint32_t max_unit_words,
+                                        int canonical_nan, const void *unit_ids, uint32_t n_ids,
+                                        void *out_bf16, void *status, void *stream) {
+  if (!nz::valid_precision(precision)) {
+    nz::set_error("nz_decompress_bf16_units: precision must be 0, 1, 3 or 7 (got %d)", precision);
+    return NZ_E_ARG;
+  }
+  int rc = check_decode_args("nz_decompress_bf16_units", container, n, lane_symbols);
+  if (rc) return rc;
+  if (n_ids == 0) return NZ_OK;
+  if (n == 0) {
+    nz::set_error("nz_decompress_bf16_units: an empty tensor has no units");
+    return NZ_E_ARG;
+  }
+  if (!unit_ids || ((uintptr_t)unit_ids & 3) || !out_bf16 || !frac_in ||
+      ((uintptr_t)out_bf16 & 15) || ((uintptr_t)frac_in & 7)) {
+    nz::set_error("nz_decompress_bf16_units: unit list must be a 4-byte aligned device pointer, "
+                  "output 16-byte, fractions 8-byte aligned");
+    return NZ_E_ARG;
+  }
+  nz::HostItem it;
+  it.container = container;
+  it.container_bytes = container_bytes;
+  it.frac = frac_in;
+  it.n = n;
+  it.max_unit_words = max_unit_words;
+  it.out_bf16 = out_bf16;
+  it.out_exp = nullptr;
+  it.unit_list = (const uint32_t *)unit_ids;
+  it.n_list = n_ids;
+  return nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
+                         (cudaStream_t)stream);
+}
+
+namespace nz {
+
+// Row gather, step 1: the units that hold each requested row.  Row r of a
+// table with rows of `row_len` elements starts at element r * row_len; it is
+// decoded as `per_row` consecutive units from the one that holds its first
+// element (numbers past the last unit are clamped: their output is not used).
+// Rows outside the table get unit n_units, which the decoder reports.
+__global__ void gather_plan_kernel(const int64_t *__restrict__ rows, uint32_t k, uint64_t row_len,
+                                   uint64_t n_rows, uint64_t U, uint32_t n_units, uint32_t per_row,
+                                   uint32_t *__restrict__ units) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (uint64_t)k * per_row) return;
+  const int64_t r = rows[i / per_row];
+  uint32_t u = n_units;
+  if (r >= 0 && (uint64_t)r < n_rows) {
+    const uint64_t v = (uint64_t)r * row_len / U + i % per_row;
+    u = v < n_units ? (uint32_t)v : n_units - 1;
+  }
+  units[i] = u;
+}
+
+// Row gather, step 3: copy each row out of the units decoded for it.  VEC = 8
+// moves 16 bytes per thread (row length and so every offset a multiple of 8).
+template <int VEC>
+__global__ void gather_copy_kernel(const int64_t *__restrict__ rows, uint32_t k, uint64_t row_len,
+                                   uint64_t n_rows, uint64_t U, uint32_t per_row,
+                                   const uint16_t *__restrict__ staging,
+                                   uint16_t *__restrict__ out) {
+  const uint64_t per = row_len / VEC;
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (uint64_t)k * per) return;
+  const uint64_t row = i / per, j = (i % per) * VEC;
+  const int64_t r = rows[row];
+  if (r < 0 || (uint64_t)r >= n_rows) return;        // flagged by the decoder; left untouched
+  const uint64_t src = row * per_row * U + ((uint64_t)r * row_len) % U + j;
+  if (VEC == 8)
+    *reinterpret_cast<uint4 *>(out + row * row_len + j) =
+        *reinterpret_cast<const uint4 *>(staging + src);
+  else
+    out[row * row_len + j] = staging[src];
+}
+
+static inline uint32_t gather_units_per_row(uint64_t row_len, uint64_t U) {
+  if (U % row_len == 0) return 1;                            // a unit holds whole rows
+  if (row_len % U == 0) return (uint32_t)(row_len / U);      // a row is whole units
+  return (uint32_t)((row_len + U - 1) / U + 1);              // rows straddle unit boundaries
+}
+
+}  // namespace nz
+
+extern "C" uint64_t nz_gather_scratch_bytes(uint32_t n_rows_out, uint64_t row_len,
+                                            uint32_t lane_symbols) {
+  if (!nz::valid_lane_symbols(lane_symbols) || row_len == 0) return 0;
+  const uint64_t U = 32ull * lane_symbols;
+  const uint64_t per_row = nz::gather_units_per_row(row_len, U);
+  // unit list (4 bytes each, rounded to 16) + the decoded units
+  return nz::align16((uint64_t)n_rows_out * per_row * 4) + (uint64_t)n_rows_out * per_row * U * 2;
+}
+
+extern "C" int nz_gather_rows_bf16(const void *container, uint64_t container_bytes,
+                                   const void *frac_in, uint64_t n, int precision,
+                                   uint32_t lane_symbols, uint32_t max_unit_words,
+                                   int canonical_nan, uint64_t row_len, const void *rows_i64,
+                                   uint32_t n_rows_out, void *out_bf16, void *scratch,
+                                   uint64_t scratch_bytes, void *status, void *stream) {
+  if (!nz::valid_precision(precision)) {
+    nz::set_error("nz_gather_rows_bf16: precision must be 0, 1, 3 or 7 (got %d)", precision);
+    return NZ_E_ARG;
+  }
+  int rc = check_decode_args("nz_gather_rows_bf16", container, n, lane_symbols);
+  if (rc) return rc;
+  if (row_len == 0 || n == 0 || n % row_len) {
+    nz::set_error("nz_gather_rows_bf16: row length %llu does not divide the %llu elements",
+                  (unsigned long long)row_len, (unsigned long long)n);
+    return NZ_E_ARG;
+  }
+  if (n_rows_out == 0) return NZ_OK;
+  if (!rows_i64 || ((uintptr_t)rows_i64 & 7) || !out_bf16 || !frac_in || !scratch ||
+      ((uintptr_t)scratch & 15) || ((uintptr_t)frac_in & 7)) {
+    nz::set_error("nz_gather_rows_bf16: null or misaligned pointer (rows and fractions 8-byte, "
+                  "scratch 16-byte aligned)");
+    return NZ_E_ARG;
+  }
+  const uint64_t need = nz_gather_scratch_bytes(n_rows_out, row_len, lane_symbols);
+  if (scratch_bytes < need) {
+    nz::set_error("nz_gather_rows_bf16: scratch of %llu bytes is smaller than the %llu required",
+                  (unsigned long long)scratch_bytes, (unsigned long long)need);
+    return NZ_E_CAPACITY;
+  }
+  const uint64_t U = 32ull * lane_symbols;
+  const uint32_t per_row = nz::gather_units_per_row(row_len, U);
+  const uint64_t n_list = (uint64_t)n_rows_out * per_row;
+  if (n_list >= (1ull << 32)) {
+    nz::set_error("nz_gather_rows_bf16: %u rows of %u units each are too many for one call",
+                  n_rows_out, per_row);
+    return NZ_E_ARG;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t *units = (uint32_t *)scratch;
+  uint16_t *staging = (uint16_t *)((uint8_t *)scratch + nz::align16(n_list * 4));
+  const uint32_t n_units = (uint32_t)nz::unit_count(n, lane_symbols);
+  const uint64_t table_rows = n / row_len;
+  nz::gather_plan_kernel<<<(unsigned)((n_list + 255) / 256), 256, 0, st>>>(
+      (const int64_t *)rows_i64, n_rows_out, row_len, table_rows, U, n_units, per_row, units);
+  NZ_LAUNCH_CHECK("gather_plan_kernel");
+  rc = nz_decompress_bf16_units(container, container_bytes, frac_in, n, precision, lane_symbols,
+                                max_unit_words, canonical_nan, units, (uint32_t)n_list, staging,
+                                status, stream);
+  if (rc) return rc;
+  const bool vec = row_len % 8 == 0 && ((uintptr_t)out_bf16 & 15) == 0;
+  const uint64_t threads = vec ? (uint64_t)n_rows_out * (row_len / 8) : (uint64_t)n_rows_out * row_len;
+  const uint64_t blocks = (threads + 255) / 256;
+  if (blocks >= (1ull << 31)) {
+    nz::set_error("nz_gather_rows_bf16: output too large for one call");
+    return NZ_E_ARG;
+  }
+  if (vec)
+    nz::gather_copy_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(
+        (const int64_t *)rows_i64, n_rows_out, row_len, table_rows, U, per_row, staging,
+        (uint16_t *)out_bf16);
+  else
+    nz::gather_copy_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(
+        (const int64_t *)rows_i64, n_rows_out, row_len, table_rows, U, per_row, staging,
+        (uint16_t *)out_bf16);
+  NZ_LAUNCH_CHECK("gather_copy_kernel");
   return NZ_OK;
 }

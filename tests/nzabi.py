@@ -121,6 +121,24 @@ def decompress(cont, frac, n, s, S, max_words=0, canon=False):
     return out, int(status.item())
 
 
+def decompress_units(cont, frac, n, s, S, units, max_words=0, canon=False, fill=0x1234):
+    """Gather-decode the listed units; returns (bf16 [len(units) * 32 * S], status).  The
+    output starts out filled with `fill` so that untouched elements are recognisable."""
+    L = lib()
+    U = 32 * S
+    ids = torch.as_tensor(np.asarray(units, dtype=np.int64), dtype=torch.int64).to(torch.int32).cuda()
+    k = ids.numel()
+    raw_o, out = guarded(2 * k * U, torch.bfloat16)
+    out.view(torch.int16).fill_(fill)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.nz_decompress_bf16_units(cont.data_ptr(), cont.numel(), frac.data_ptr(), n, s, S,
+                                          max_words, int(canon), ids.data_ptr(), k, out.data_ptr(),
+                                          status.data_ptr(), stream()))
+    torch.cuda.synchronize()
+    assert guards_intact(raw_o, 2 * k * U)
+    return out, int(status.item())
+
+
 def dev_u8(a):
     """numpy uint8 -> 16-byte aligned cuda tensor."""
     return torch.from_numpy(np.ascontiguousarray(a, dtype=np.uint8).copy()).cuda()

@@ -399,3 +399,57 @@ def test_random_shapes_and_lane_lengths_property():
         out, status = A.decompress(cont, frac, n, s, S, mw if trial % 2 else 0, canon=True)
         assert status == 0
         assert np.array_equal(A.to_bits(out), O.decompress_bf16(c_ref, f_ref, n, s, canonical_nan=True))
+
+
+# ------------------------------------------------------------------ gather
+@pytest.mark.parametrize("s", PRECISIONS)
+def test_unit_gather_equals_slices_of_the_full_decode(s):
+    rng = np.random.default_rng(21 + s)
+    for S, n in ((64, 64 * 32 * 37 + 1234), (O.default_lane_symbols(s), 3_000_000 + 77)):
+        U = 32 * S
+        x = weights(n, 30 + s).cuda()
+        cont, frac, mw = A.compress(x, s, S)
+        full, status = A.decompress(cont, frac, n, s, S, mw)
+        assert status == 0
+        full_bits = A.to_bits(full)
+        n_units = (n + U - 1) // U
+        lists = [
+            [0], [n_units - 1], list(range(n_units)), list(range(n_units - 1, -1, -1)),
+            rng.integers(0, n_units, size=1).tolist(), rng.integers(0, n_units, size=5).tolist(),
+            rng.integers(0, n_units, size=301).tolist(), [3, 3, 3, n_units - 1, n_units - 1, 0],
+        ]
+        for units in lists:
+            out, status = A.decompress_units(cont, frac, n, s, S, units, mw)
+            assert status == 0, (s, S, units[:4])
+            got = A.to_bits(out).reshape(len(units), U)
+            for i, u in enumerate(units):
+                count = min(U, n - u * U)
+                assert np.array_equal(got[i, :count], full_bits[u * U:u * U + count]), (s, S, u)
+                assert (got[i, count:] == 0x1234).all()          # past the tensor: untouched
+
+
+def test_unit_gather_with_raw_units_bad_numbers_and_empty_list():
+    rng = np.random.default_rng(5)
+    S, U = 256, 32 * 256
+    # incompressible exponents in the first half: those units are stored raw
+    bits = np.concatenate([rng.integers(0, 1 << 16, size=4 * U, dtype=np.uint16),
+                           A.to_bits(weights(5 * U + 100, 9))])
+    x = torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).cuda()
+    n = x.numel()
+    cont, frac, mw = A.compress(x, 7, S)
+    assert O.parse_header(cont.cpu().numpy())["n_raw_units"] >= 4
+    units = [9, 0, 5, 3, 8, 1]
+    out, status = A.decompress_units(cont, frac, n, 7, S, units, mw)
+    assert status == 0
+    got = A.to_bits(out).reshape(len(units), U)
+    for i, u in enumerate(units):
+        count = min(U, n - u * U)
+        assert np.array_equal(got[i, :count], bits[u * U:u * U + count])
+    # a unit number past the end: flagged, its place left alone, the others decoded
+    out, status = A.decompress_units(cont, frac, n, 7, S, [2, 10, 4], mw)
+    assert status == 0x20                                        # NZ_STATUS_BAD_UNIT
+    got = A.to_bits(out).reshape(3, U)
+    assert np.array_equal(got[0], bits[2 * U:3 * U]) and np.array_equal(got[2], bits[4 * U:5 * U])
+    assert (got[1] == 0x1234).all()
+    out, status = A.decompress_units(cont, frac, n, 7, S, [], mw)
+    assert status == 0 and out.numel() == 0

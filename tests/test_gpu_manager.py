@@ -278,3 +278,49 @@ def test_manager_with_block_normaliser_matches_oracle(precision, group):
         err_plain = (plain.read(plain.write(w)).float() - w.cuda().float()).abs().mean().item()
         err_norm = (got.float() - w.cuda().float()).abs().mean().item()
         assert err_norm <= err_plain * 1.05
+
+
+@pytest.mark.parametrize("precision", (7, 3))
+@pytest.mark.parametrize("rows,dim", ((1000, 4096), (333, 16384), (5000, 96), (70, 20000), (32000, 512)))
+def test_read_rows_and_embedding_lookup_decode_only_what_they_need(precision, rows, dim):
+    """Row gather against indexing the fully decompressed table: rows that share a
+    unit, rows made of whole units, and rows that straddle unit boundaries."""
+    g = torch.Generator().manual_seed(rows + dim)
+    table = (torch.randn(rows, dim, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    manager = neuzip.Manager(precision=precision)
+    handle = manager.write(table)
+    full = manager.read(handle)
+    idx = torch.randint(0, rows, (3, 17), generator=g)
+    idx[0, 0], idx[0, 1], idx[2, 16] = 0, rows - 1, rows - 1        # first, last, a repeat
+    got = manager.read_rows(handle, idx.cuda())
+    assert got.shape == (3, 17, dim) and got.dtype == torch.bfloat16
+    assert torch.equal(got.view(torch.int16), full[idx.cuda()].view(torch.int16))
+    assert manager.read_rows(handle, torch.zeros(0, dtype=torch.long)).shape == (0, dim)
+    manager.check()
+    emb = torch.nn.Embedding(rows, dim, padding_idx=1).to(torch.bfloat16).cuda()
+    with torch.no_grad():
+        emb.weight.copy_(table)
+    ce = neuzip.nn.Embedding(manager, emb)
+    ref = torch.nn.functional.embedding(idx.cuda(), manager.read(ce._p._handle))
+    assert torch.equal(ce(idx.cuda()).view(torch.int16), ref.view(torch.int16))
+
+
+def test_read_rows_reports_rows_outside_the_table():
+    table = weights((4000, 512), 8).cuda()
+    manager = neuzip.Manager(precision=7)
+    handle = manager.write(table)
+    got = manager.read_rows(handle, torch.tensor([3, 4000, 7]).cuda())
+    assert torch.equal(got[0].view(torch.int16), table[3].view(torch.int16))
+    assert torch.equal(got[2].view(torch.int16), table[7].view(torch.int16))
+    with pytest.raises(RuntimeError):
+        manager.check()
+
+
+def test_read_rows_with_block_normaliser_falls_back_to_a_full_read():
+    g = torch.Generator().manual_seed(3)
+    table = (torch.randn(600, 1024, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    manager = neuzip.Manager(precision=3, normalizer_size=512)
+    handle = manager.write(table)
+    idx = torch.tensor([5, 599, 0, 5]).cuda()
+    assert torch.equal(manager.read_rows(handle, idx).view(torch.int16),
+                       manager.read(handle)[idx].view(torch.int16))
