@@ -210,6 +210,20 @@ def main():
     res["layerwise_blocks"] = len(hooks) // 2
     res["peak_memory_bytes_compressed_run"] = torch.cuda.max_memory_allocated()
     res["ratio_vs_dense_tok_s"] = res["neuzip_layerwise_tok_s"] / res["dense_tok_s"]
+
+    # single-token steps multiply while decoding (no bf16 write-back); the prompt keeps
+    # the batched decode.  Same fp32 arithmetic, different order of the sums.
+    if args.batch == 1:
+        for h in hooks:
+            h.remove()
+        layerwise.attach(model, manager, fuse_single_token=True)
+        timed_generate(model, ids, 8)
+        out3, t_gpu, _ = timed_generate(model, ids, args.new)
+        out3, t_gpu, _ = timed_generate(model, ids, args.new)
+        manager.check()
+        res["neuzip_fused_tok_s"] = args.batch * args.new / t_gpu
+        res["fused_tokens_equal_fraction"] = float((out3 == ref_out).float().mean().item())
+        res["fused_ratio_vs_dense_tok_s"] = res["neuzip_fused_tok_s"] / res["dense_tok_s"]
     print(json.dumps(res))
 
 

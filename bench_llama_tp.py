@@ -142,6 +142,8 @@ def main():
     ap.add_argument("--new", type=int, default=32)
     ap.add_argument("--precision", type=int, default=3)
     ap.add_argument("--skip-dense", action="store_true")
+    ap.add_argument("--fused", action="store_true",
+                    help="single-token steps multiply while decoding (batch 1 only)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -182,7 +184,8 @@ def main():
     manager._be.release_scratch()
     torch.cuda.empty_cache()
     res["stored_weight_bytes_per_rank"] = manager.total_size()
-    layerwise.attach(model, manager)
+    layerwise.attach(model, manager, fuse_single_token=args.fused and args.batch == 1)
+    res["fused_single_token"] = bool(args.fused and args.batch == 1)
     generate(model, prompt, args.new)
     out, t_tok = generate(model, prompt, args.new)
     manager.check()

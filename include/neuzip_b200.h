@@ -259,6 +259,25 @@ int nz_gather_rows_bf16(const void *container, uint64_t container_bytes,
                         uint32_t n_rows_out, void *out_bf16, void *scratch,
                         uint64_t scratch_bytes, void *status, void *stream);
 
+/* y = W x (+ bias) for one input vector, with W the compressed [out, in]
+ * row-major bf16 matrix of n = out * in elements: the weights are multiplied as
+ * they are decoded and never written back.  in_features must be a multiple of
+ * 256.  x_f32 is the input vector in fp32 (in entries, 16-byte aligned), bias
+ * (bf16, out entries) may be NULL, y_bf16 receives out bf16 values (products
+ * and sums in fp32, one rounding at the end).  Two launches, no host sync:
+ * the decode kernel leaves per-unit partial sums in `scratch`
+ * (nz_linear_vec_scratch_bytes, 16-byte aligned), a second kernel adds them
+ * per row in a fixed order, so the result is reproducible run to run.
+ * Reference: Manager::linear / linear_without_bias = full decompress, then a
+ * library GEMM (cuda/high_level.cu:252-263; neuzip/nn/module.py:27-28). */
+uint64_t nz_linear_vec_scratch_bytes(uint64_t n, uint64_t in_features, uint32_t lane_symbols);
+int nz_linear_vec_bf16(const void *container, uint64_t container_bytes,
+                       const void *frac_in, uint64_t n, int precision,
+                       uint32_t lane_symbols, uint32_t max_unit_words,
+                       int canonical_nan, uint64_t in_features, const void *x_f32,
+                       const void *bias_bf16, void *y_bf16, void *scratch,
+                       uint64_t scratch_bytes, void *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

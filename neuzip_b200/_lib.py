@@ -68,6 +68,9 @@ SIGNATURES["nz_decompress_bf16_units"] = (
 SIGNATURES["nz_gather_scratch_bytes"] = (_u64, [_u32, _u64, _u32])
 SIGNATURES["nz_gather_rows_bf16"] = (
     _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _u64, _vp, _u32, _vp, _vp, _u64, _vp, _vp])
+SIGNATURES["nz_linear_vec_scratch_bytes"] = (_u64, [_u64, _u64, _u32])
+SIGNATURES["nz_linear_vec_bf16"] = (
+    _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp])
 SIGNATURES["nz_decompress_bf16_batch"] = (
     _int, [ctypes.POINTER(DecompressItem), _u32, _int, _u32, _int, _vp, _vp])
 

@@ -89,6 +89,13 @@ class CodecBackend:
         self._scratch: Optional[torch.Tensor] = None
         self._status: Optional[torch.Tensor] = None
         self.canonical_nan = True           # NaN -> 0x7FFF like cuda/kernels.cuh:214-216
+        # single-vector linear calls multiply while decoding (see _linear_vec); off by
+        # default because the sums are ordered differently from the library GEMM's
+        self.fused_vector_linear = False
+        self._vec_src: Optional[torch.Tensor] = None
+        self._vec_ver = -1
+        self._vec_x: Optional[torch.Tensor] = None
+        self._vec_scratch: Dict[tuple, torch.Tensor] = {}
 
     # -- helpers ---------------------------------------------------------
     def _ensure_device(self) -> None:
@@ -283,14 +290,61 @@ class CodecBackend:
     def linear(self, name: str, input: torch.Tensor, shape: Sequence[int],
                bias: torch.Tensor) -> torch.Tensor:
         """cuda/high_level.cu:252-257."""
+        fused = self._linear_vec(name, input, shape, bias)
+        if fused is not None:
+            return fused
         weight = self.read(name).view(*shape)
         return torch.nn.functional.linear(input, weight, bias)
 
     def linear_without_bias(self, name: str, input: torch.Tensor,
                             shape: Sequence[int]) -> torch.Tensor:
         """cuda/high_level.cu:259-263."""
+        fused = self._linear_vec(name, input, shape, None)
+        if fused is not None:
+            return fused
         weight = self.read(name).view(*shape)
         return torch.matmul(input, weight.t())
+
+    def _linear_vec(self, name: str, input: torch.Tensor, shape: Sequence[int],
+                    bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """A single input vector (one token of one sequence, the decode step of
+        generation): multiply while decoding instead of writing the bf16 weights out
+        and reading them back (``nz_linear_vec_bf16``).  Returns None when the call does
+        not qualify; products and sums are fp32 with one rounding to bf16, like the
+        library GEMM, but the order of the sums differs, so the last bit may."""
+        if not self.fused_vector_linear:
+            return None
+        entry = self._cache.get(name)
+        if entry is None or entry.normalizers is not None or len(shape) != 2:
+            return None
+        out_f, in_f = int(shape[0]), int(shape[1])
+        if (input.dtype != torch.bfloat16 or not input.is_cuda or input.numel() != in_f
+                or in_f % 256 or out_f * in_f != entry.numel):
+            return None
+        if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_cuda
+                                 or bias.numel() != out_f):
+            return None
+        if torch.is_grad_enabled() and (input.requires_grad or (bias is not None and bias.requires_grad)):
+            return None
+        L = self._lib
+        if self._vec_src is not input or self._vec_ver != input._version:
+            # q/k/v and gate/up are called with the same tensor: convert it once
+            self._vec_x = input.detach().reshape(-1).float()
+            self._vec_src, self._vec_ver = input, input._version
+        y = torch.empty(input.shape[:-1] + (out_f,), dtype=torch.bfloat16, device="cuda")
+        # partial sums: one buffer per matrix size, reused (calls are ordered on the stream)
+        scratch = self._vec_scratch.get((entry.numel, in_f))
+        if scratch is None:
+            nbytes = int(L.nz_linear_vec_scratch_bytes(entry.numel, in_f, entry.lane_symbols))
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+            self._vec_scratch[(entry.numel, in_f)] = scratch
+        scratch_bytes = scratch.numel()
+        _lib.check(L.nz_linear_vec_bf16(
+            _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
+            self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
+            in_f, _ptr(self._vec_x), _ptr(bias.contiguous() if bias is not None else None),
+            _ptr(y), _ptr(scratch), scratch_bytes, _ptr(self._status), _stream()))
+        return y
 
     def split(self, tensor: torch.Tensor) -> List[torch.Tensor]:
         """cuda/high_level.cu:301-321: always full mantissa (f_bits_save = 7, :289);

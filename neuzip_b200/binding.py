@@ -127,6 +127,13 @@ class Manager:
             flat = self._be.read(handle).reshape(-1, row_len)[rows.reshape(-1).long()]
         return flat.requires_grad_(False).reshape(tuple(rows.shape) + tuple(shape[1:]))
 
+    def fuse_vector_linear(self, enabled: bool = True) -> None:
+        """Let `linear` with a single input vector (batch 1, one token) multiply while
+        decoding instead of decompressing the weight first.  Same fp32 arithmetic as
+        the library GEMM but a different order of the sums."""
+        if hasattr(self._be, "fused_vector_linear"):
+            self._be.fused_vector_linear = bool(enabled)
+
     def export_entry(self, handle: str) -> dict:
         """Stored bytes + metadata of a handle (for checkpoints)."""
         blob = self._be.export_entry(handle)

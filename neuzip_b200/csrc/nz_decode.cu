@@ -30,6 +30,7 @@
 // pointers), output and fraction addresses never depend on coded data, and
 // the wait on the bulk copy is bounded.
 #include <string.h>
+#include <type_traits>
 
 #include "nz_common.cuh"
 
@@ -288,6 +289,10 @@ struct DecodeArgs {
   uint32_t *status;
   const uint32_t *unit_list;   // units to decode, in output order (gather launches only)
   uint32_t n_work;             // units this launch decodes: n_units, or the length of the list
+  const float *gx;             // matrix-vector launches: input vector (fp32, `in` entries)
+  float *partial;              //   partial sums, `seg` places per unit
+  uint32_t in;                 //   row length of the [out, in] matrix, a multiple of 256
+  uint32_t seg;                //   rows a unit can touch
 };
 
 // One launch decodes up to kMaxBatch tensors; each tensor gets its own range of
@@ -308,6 +313,9 @@ struct BatchArgs {
   BatchItem item[kMaxBatch];
   const uint32_t *unit_list;   // gather launches (count == 1): units of item[0] to decode
   uint32_t n_list;
+  const float *gx;             // matrix-vector launches (count == 1), see DecodeArgs
+  float *partial;
+  uint32_t in, seg;
   uint32_t count;
   uint32_t n_ctas;        // == gridDim.x
   uint32_t S, slot_bytes, lut_shift, lut_bytes, ring_offset;
@@ -435,17 +443,93 @@ constexpr uint32_t kRingUnitBytes = 256;         // 32 lanes x 8 bytes
 constexpr uint32_t kRingSlotBytes = kChains * kRingUnitBytes;
 constexpr uint32_t kRingBytes = kRingSlots * kRingSlotBytes;
 
+// Where the four words (8 bf16) that a lane produces per block and chain go.
+// StoreSink writes them to the output tensor.
+struct StoreSink {
+  uint16_t *out[kChains];
+  __device__ __forceinline__ void begin(int) {}
+  __device__ __forceinline__ void put(int c, int k, const uint32_t (&w)[4]) {
+    __stcs(reinterpret_cast<uint4 *>(out[c] + k * 256), make_uint4(w[0], w[1], w[2], w[3]));
+  }
+  __device__ __forceinline__ void advance(int blocks) {
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) out[c] += blocks * 256;
+  }
+};
+
+// One lane's running dot product of a weight row with the input vector.  The
+// tensor is a row-major [out, in] matrix with `in` a multiple of 256, so the 256
+// elements of a block lie in one row and the end of a row is the same event for
+// all lanes of the warp.  At the end of a row (and of the unit) the warp's sum
+// goes to the next partial-sum place of the unit; a finishing kernel adds the
+// partial sums of each row in unit order, so results do not depend on timing.
+struct DotLane {
+  const float *x;      // input vector, fp32
+  uint32_t in;         // row length
+  uint32_t col;        // this lane's column of the next block (block start + lane * 8)
+  float acc;
+  float *part;         // next partial-sum place of the unit
+  __device__ __forceinline__ void start(const float *xv, uint32_t in_features, uint64_t first_elem,
+                                        float *unit_part, uint32_t lane) {
+    x = xv;
+    in = in_features;
+    col = (uint32_t)(first_elem % in_features) + lane * 8;
+    acc = 0.f;
+    part = unit_part;
+  }
+  __device__ __forceinline__ void emit(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    if ((threadIdx.x & 31) == 0) *part = v;
+    ++part;
+  }
+  // The 8 input values of a block are requested before the block's symbols are
+  // decoded and used after, so that their latency hides behind the decode steps.
+  float4 xa, xb;
+  __device__ __forceinline__ void begin() {
+    xa = __ldg(reinterpret_cast<const float4 *>(x + col));
+    xb = __ldg(reinterpret_cast<const float4 *>(x + col + 4));
+  }
+  __device__ __forceinline__ void put(const uint32_t (&w)[4]) {
+    float a = acc;
+    a = fmaf(__uint_as_float(w[0] << 16), xa.x, a);
+    a = fmaf(__uint_as_float(w[0] & 0xFFFF0000u), xa.y, a);
+    a = fmaf(__uint_as_float(w[1] << 16), xa.z, a);
+    a = fmaf(__uint_as_float(w[1] & 0xFFFF0000u), xa.w, a);
+    a = fmaf(__uint_as_float(w[2] << 16), xb.x, a);
+    a = fmaf(__uint_as_float(w[2] & 0xFFFF0000u), xb.y, a);
+    a = fmaf(__uint_as_float(w[3] << 16), xb.z, a);
+    a = fmaf(__uint_as_float(w[3] & 0xFFFF0000u), xb.w, a);
+    acc = a;
+    col += 256;
+    if (col >= in) {          // same verdict in every lane: in - (col - lane*8) is a multiple of 256
+      emit(acc);
+      acc = 0.f;
+      col -= in;
+    }
+  }
+  // end of the unit: a row that is still open gives its partial sum
+  __device__ __forceinline__ void finish() {
+    if (col & ~255u) emit(acc);
+  }
+};
+struct DotSink {
+  DotLane lane[kChains];
+  __device__ __forceinline__ void begin(int c) { lane[c].begin(); }
+  __device__ __forceinline__ void put(int c, int, const uint32_t (&w)[4]) { lane[c].put(w); }
+  __device__ __forceinline__ void advance(int) {}
+};
+
 // kChains units interleaved in one lane: the rANS chains are independent, so
 // each hides the shared-memory and multiply latency of the others.  For
 // precisions 3 and 7 the packed fractions travel through a small ring in shared
 // memory, fetched three blocks ahead with per-lane asynchronous copies; the
 // narrower fractions of precisions 0 and 1 (1 and 2 bytes per lane and block)
 // are fetched four blocks at a time by the whole warp.
-template <int S, bool MERGE, bool CANON, int ROW>
+template <int S, bool MERGE, bool CANON, int ROW, typename Sink>
 __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], const LutView &lut,
                                                     uint32_t n_blocks,
-                                                    const uint8_t *(&frac)[kChains],
-                                                    uint16_t *(&out)[kChains],
+                                                    const uint8_t *(&frac)[kChains], Sink &sink,
                                                     uint8_t *(&exp)[kChains], uint32_t ring) {
   constexpr uint32_t kFracStride = 32u * (S + 1);
   constexpr bool kAsync = MERGE && (S == 7 || S == 3);
@@ -497,6 +581,8 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
         for (int c = 0; c < kChains; ++c)
           bits[c] = (S == 1) ? lds_u16(src + c * kRingUnitBytes + k * 64)
                              : lds_u8(src + c * kRingUnitBytes + k * 32);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) sink.begin(c);
         uint32_t w[kChains][4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -509,12 +595,9 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
           for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
         }
 #pragma unroll
-        for (int c = 0; c < kChains; ++c)
-          __stcs(reinterpret_cast<uint4 *>(out[c] + k * 256),
-                 make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]));
+        for (int c = 0; c < kChains; ++c) sink.put(c, k, w[c]);
       }
-#pragma unroll
-      for (int c = 0; c < kChains; ++c) out[c] += 4 * 256;
+      sink.advance(4);
     }
     return;
   }
@@ -547,6 +630,8 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
 #pragma unroll
         for (int c = 0; c < kChains; ++c)
           bits[c] = frac_from_ring<S>(ring + (bk & 3) * kRingSlotBytes + c * kRingUnitBytes);
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) sink.begin(c);
         uint32_t w[kChains][4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -559,15 +644,11 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
           for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
         }
 #pragma unroll
-        for (int c = 0; c < kChains; ++c)
-          __stcs(reinterpret_cast<uint4 *>(out[c] + k * 256),
-                 make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]));
+        for (int c = 0; c < kChains; ++c) sink.put(c, k, w[c]);
       }
 #pragma unroll
-      for (int c = 0; c < kChains; ++c) {
-        frac[c] += kRolled * kFracStride;
-        out[c] += kRolled * 256;
-      }
+      for (int c = 0; c < kChains; ++c) frac[c] += kRolled * kFracStride;
+      sink.advance(kRolled);
     }
     frac_wait<0>();
     return;
@@ -624,6 +705,8 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
     if (MERGE) {
       // two symbols of each chain, then their output words: the table entries do
       // not have to stay live for the whole block
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) sink.begin(c);
       uint32_t w[kChains][4];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
@@ -636,9 +719,7 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
         for (int c = 0; c < kChains; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
       }
 #pragma unroll
-      for (int c = 0; c < kChains; ++c)
-        __stcs(reinterpret_cast<uint4 *>(out[c] + k * 256),
-               make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]));
+      for (int c = 0; c < kChains; ++c) sink.put(c, k, w[c]);
     } else {
       uint32_t e[kChains][8];
 #pragma unroll
@@ -654,11 +735,11 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
     for (int c = 0; c < kChains; ++c) {
       if (MERGE) {
         frac[c] += kAhead * kFracStride;
-        out[c] += kAhead * 256;
       } else {
         exp[c] += kAhead * 256;
       }
     }
+    if (MERGE) sink.advance(kAhead);
   };
   if ((n_blocks & 3) == 0) {
     for (uint32_t b = 0; b < n_blocks; b += kAhead) {
@@ -824,11 +905,118 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
   }
 }
 
-// LIST: gather launch -- the launch decodes the units named in batch.unit_list
-// (of the single tensor item[0]) and writes them one after the other.
-template <int S, bool MERGE, bool LIST>
-__global__ void __launch_bounds__(NZ_DECODE_MAX_WARPS * 32, 1)
+__device__ __forceinline__ void init_sink(StoreSink &sk, int c, const DecodeArgs &a, uint32_t,
+                                          uint64_t out_elem, uint32_t) {
+  sk.out[c] = a.out_bf16 ? a.out_bf16 + out_elem : nullptr;
+}
+__device__ __forceinline__ void init_sink(DotSink &sk, int c, const DecodeArgs &a, uint32_t unit,
+                                          uint64_t, uint32_t lane) {
+  sk.lane[c].start(a.gx, a.in, (uint64_t)unit * (32ull * a.S), a.partial + (uint64_t)unit * a.seg,
+                   lane);
+}
+__device__ __forceinline__ void finish_sink(StoreSink &) {}
+__device__ __forceinline__ void finish_sink(DotSink &sk) {
+#pragma unroll
+  for (int c = 0; c < kChains; ++c) sk.lane[c].finish();
+}
+
+// Matrix-vector launches, units that do not take the fast path (raw units, the
+// tensor's last unit, units whose neighbour in the group is one of those).  The
+// partial sums of unit u go to partial[u * seg ...], one per row the unit
+// touches, in row order -- the same places the fast path fills.
+template <int S>
+__device__ __forceinline__ void dot_single(const DecodeArgs &a, const UnitPlan &pl, uint32_t u,
+                                           uint32_t slot, const LutView &lv, bool canon,
+                                           const uint8_t *payload, uint32_t lenq, uint32_t lane) {
+  if (u >= a.n_units) return;
+  const uint64_t U = 32ull * a.S;
+  const uint64_t first = (uint64_t)u * U;
+  const uint64_t count = (a.n - first < U) ? (a.n - first) : U;
+  float *part = a.partial + (uint64_t)u * a.seg;
+  const uint64_t row0 = first / a.in, row1 = (first + count - 1) / a.in;
+  bool filled = false;
+  if (pl.kind == kUnitRaw) {
+    const uint8_t *src = payload + pl.byte0;
+    for (uint64_t r = row0; r <= row1; ++r) {
+      const uint64_t lo = r * a.in > first ? r * a.in : first;
+      const uint64_t hi = (r + 1) * a.in < first + count ? (r + 1) * a.in : first + count;
+      float acc = 0.f;
+      for (uint64_t e = lo + lane; e < hi; e += 32) {
+        const uint64_t bit = e * (S + 1);
+        const uint32_t shift = 7 - S - (uint32_t)(bit & 7);
+        const uint32_t field = ((uint32_t)a.frac[bit >> 3] >> shift) & ((2u << S) - 1u);
+        const uint32_t v = merge_pair_generic<S>((uint32_t)src[e - first] << kEntSymShift, 0, field,
+                                                 0, a.canon != 0);
+        acc = fmaf(__uint_as_float(v << 16), a.gx[e - r * a.in], acc);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+      if (lane == 0) part[r - row0] = acc;
+    }
+    filled = true;
+  } else if (pl.kind == kUnitCoded) {
+    LaneState st;
+    if (open_unit(pl, slot, lenq, lane, st)) {
+      // the row length is a multiple of 256, so is the element count: whole blocks only
+      const uint32_t n_blocks = (uint32_t)(count / 256);
+      const uint8_t *frac_lane = a.frac + (first + lane * 8) * (S + 1) / 8;
+      DotLane d;
+      d.start(a.gx, a.in, first, part, lane);
+      for (uint32_t b = 0; b < n_blocks; ++b) {
+        const uint64_t fbits = load_frac<S>(frac_lane + (uint64_t)b * 32u * (S + 1));
+        uint32_t ent[8], w[4];
+        d.begin();
+#pragma unroll
+        for (int t = 0; t < 8; ++t) ent[t] = decode_step<0>(st, lv);
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          w[t] = canon ? merge_word<S, true>(ent[2 * t], ent[2 * t + 1], fbits, t)
+                       : merge_word<S, false>(ent[2 * t], ent[2 * t + 1], fbits, t);
+        d.put(w);
+      }
+      d.finish();
+      if (count == U && __any_sync(0xFFFFFFFFu, st.x != kStateLow) && lane == 0)
+        raise(a.status, NZ_STATUS_BAD_STATE);
+      filled = true;
+    } else if (lane == 0) {
+      raise(a.status, NZ_STATUS_BAD_LANES);
+    }
+  }
+  if (!filled && lane == 0)          // a unit that could not be decoded contributes zeros
+    for (uint64_t r = row0; r <= row1; ++r) part[r - row0] = 0.f;
+}
+
+// Adds the partial sums of each output row in unit order, adds the bias and
+// rounds to bf16 (round to nearest even, like the library GEMM's epilogue).
+__global__ void dot_finish_kernel(const float *__restrict__ partial, uint32_t seg, uint64_t U,
+                                  uint32_t in, uint32_t out_features,
+                                  const uint16_t *__restrict__ bias, uint16_t *__restrict__ y) {
+  const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= out_features) return;
+  const uint64_t e_lo = (uint64_t)r * in, e_hi = e_lo + in - 1;
+  float sum = 0.f;
+  for (uint64_t u = e_lo / U; u <= e_hi / U; ++u)
+    sum += partial[u * seg + (r - (uint32_t)(u * U / in))];
+  if (bias) sum += __uint_as_float((uint32_t)bias[r] << 16);
+  uint32_t bits = __float_as_uint(sum);
+  if ((bits & 0x7F800000u) == 0x7F800000u && (bits & 0x007FFFFFu))
+    bits = 0x7FFF0000u;                                  // NaN
+  else
+    bits += 0x7FFFu + ((bits >> 16) & 1u);               // round to nearest even
+  y[r] = (uint16_t)(bits >> 16);
+}
+
+// MODE kModeList: gather launch -- the launch decodes the units named in
+// batch.unit_list (of the single tensor item[0]) and writes them one after the other.
+// MODE kModeDot: matrix-vector launch -- nothing is written back; every unit's
+// elements are multiplied with the input vector as they are decoded.
+constexpr int kModeTensor = 0, kModeList = 1, kModeDot = 2;
+constexpr int kDotMaxWarps = NZ_DECODE_MAX_WARPS;
+template <int S, bool MERGE, int MODE>
+__global__ void __launch_bounds__((MODE == kModeDot ? kDotMaxWarps : NZ_DECODE_MAX_WARPS) * 32, 1)
 decode_kernel(const BatchArgs batch) {
+  constexpr bool LIST = MODE == kModeList;
+  constexpr bool DOT = MODE == kModeDot;
   extern __shared__ __align__(128) uint8_t smem[];
   // which tensor this CTA works on, and its rank among that tensor's CTAs
   uint32_t ti = 0;
@@ -855,6 +1043,10 @@ decode_kernel(const BatchArgs batch) {
   a.status = batch.status;
   a.unit_list = LIST ? batch.unit_list : nullptr;
   a.n_work = LIST ? batch.n_list : a.n_units;
+  a.gx = DOT ? batch.gx : nullptr;
+  a.partial = DOT ? batch.partial : nullptr;
+  a.in = DOT ? batch.in : 0;
+  a.seg = DOT ? batch.seg : 0;
   const uint32_t n_warps = blockDim.x >> 5;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t lut_bytes = 4096u << a.lut_shift;           // 2^pb slots would need 4 << shift each
@@ -1022,22 +1214,23 @@ decode_kernel(const BatchArgs batch) {
       if (ok) {
         done = true;
         const uint8_t *fr[kChains];
-        uint16_t *ob[kChains];
         uint8_t *xb[kChains];
+        typename std::conditional<DOT, DotSink, StoreSink>::type sink;
 #pragma unroll
         for (int c = 0; c < kChains; ++c) {
           const uint64_t e = (uint64_t)real[c] * U + lane * 8;                  // in the tensor
           const uint64_t o = LIST ? (uint64_t)(u + c) * U + lane * 8 : e;       // in the output
           fr[c] = MERGE ? a.frac + e * (S + 1) / 8 : nullptr;
-          ob[c] = MERGE ? a.out_bf16 + o : nullptr;
           xb[c] = MERGE ? nullptr : a.out_exp + o;
+          init_sink(sink, c, a, real[c], o, lane);
         }
         if (canon)
-          decode_blocks_multi<S, MERGE, true, 0>(st, lv, a.S / 8, fr, ob, xb, ring);
+          decode_blocks_multi<S, MERGE, true, 0>(st, lv, a.S / 8, fr, sink, xb, ring);
         else if (row_shift == kFastRow)
-          decode_blocks_multi<S, MERGE, false, kFastRow>(st, lv, a.S / 8, fr, ob, xb, ring);
+          decode_blocks_multi<S, MERGE, false, kFastRow>(st, lv, a.S / 8, fr, sink, xb, ring);
         else
-          decode_blocks_multi<S, MERGE, false, 0>(st, lv, a.S / 8, fr, ob, xb, ring);
+          decode_blocks_multi<S, MERGE, false, 0>(st, lv, a.S / 8, fr, sink, xb, ring);
+        finish_sink(sink);
         bool low = true;
 #pragma unroll
         for (int c = 0; c < kChains; ++c) low = low && st[c].x == kStateLow;
@@ -1047,9 +1240,13 @@ decode_kernel(const BatchArgs batch) {
     if (!done) {
 #pragma unroll
       for (int c = 0; c < kChains; ++c) {
-        const int64_t delta = LIST ? ((int64_t)(u + c) - (int64_t)real[c]) * (int64_t)U : 0;
-        decode_single<S, MERGE>(a, pl[c], real[c], delta, slot0 + c * a.slot_bytes, lv, canon,
-                                payload, lenq, lane);
+        if (DOT) {
+          dot_single<S>(a, pl[c], real[c], slot0 + c * a.slot_bytes, lv, canon, payload, lenq, lane);
+        } else {
+          const int64_t delta = LIST ? ((int64_t)(u + c) - (int64_t)real[c]) * (int64_t)U : 0;
+          decode_single<S, MERGE>(a, pl[c], real[c], delta, slot0 + c * a.slot_bytes, lv, canon,
+                                  payload, lenq, lane);
+        }
       }
     }
     // every lane is done reading the slots: fetch this warp's next group
@@ -1070,6 +1267,9 @@ struct HostItem {
   void *out_exp;
   const uint32_t *unit_list;   // gather: device array of unit numbers (else null)
   uint32_t n_list;
+  const float *gx;             // matrix-vector: input vector (else null), partial sums,
+  float *partial;              //   row length and partial-sum places per unit
+  uint32_t in, seg;
 };
 
 // Units a launch decodes for an item.
@@ -1097,7 +1297,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   b.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
   const uint32_t guard = ((S + 8) * 2 + 127) & ~127u;
   const uint32_t sm_smem = 227u * 1024u;
-  const uint32_t kMaxWarps = NZ_DECODE_MAX_WARPS;
+  const uint32_t kMaxWarps = items[0].gx ? (uint32_t)kDotMaxWarps : (uint32_t)NZ_DECODE_MAX_WARPS;
   const uint32_t per_warp = kChains * b.slot_bytes + kRingBytes;
   const uint32_t min_fixed = 16 * 1024 + 1024 + guard;
   if (min_fixed + per_warp > sm_smem) {
@@ -1108,24 +1308,24 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   if (cap > kMaxWarps) cap = kMaxWarps;
 
   // CTAs per tensor: proportional to units, at least one, summing to the SM count
-  // (or fewer when there is not enough work to give every SM a pair of units)
+  // (or fewer when there is not enough work to give every SM a group of units)
   const uint32_t sms = (uint32_t)sm_count();
-  uint64_t total_pairs = 0;
-  for (uint32_t t = 0; t < count; ++t) total_pairs += (work_units(items[t], S) + kChains - 1) / kChains;
+  uint64_t total_groups = 0;
+  for (uint32_t t = 0; t < count; ++t) total_groups += (work_units(items[t], S) + kChains - 1) / kChains;
   uint32_t n_ctas = sms;
-  if (total_pairs < n_ctas) n_ctas = (uint32_t)total_pairs;
+  if (total_groups < n_ctas) n_ctas = (uint32_t)total_groups;
   if (n_ctas < count) n_ctas = count;
   uint32_t ctas[kMaxBatch], used = 0;
   for (uint32_t t = 0; t < count; ++t) {
     const uint64_t nu = work_units(items[t], S);
     uint64_t c = total_units ? (nu * n_ctas + total_units / 2) / total_units : 1;
-    const uint64_t pairs = (nu + kChains - 1) / kChains;
-    if (c > pairs) c = pairs;
+    const uint64_t groups = (nu + kChains - 1) / kChains;
+    if (c > groups) c = groups;
     if (c < 1) c = 1;
     ctas[t] = (uint32_t)c;
     used += ctas[t];
   }
-  // fix the rounding: take from / give to the tensor with the most / fewest pairs per CTA
+  // fix the rounding: take from / give to the tensor with the most / fewest groups per CTA
   auto load = [&](uint32_t t, uint32_t c) {
     return (double)((work_units(items[t], S) + kChains - 1) / kChains) / (double)c;
   };
@@ -1141,23 +1341,23 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   while (used < n_ctas) {
     uint32_t best = kMaxBatch;
     for (uint32_t t = 0; t < count; ++t) {
-      const uint64_t pairs = (work_units(items[t], S) + kChains - 1) / kChains;
-      if (ctas[t] < pairs && (best == kMaxBatch || load(t, ctas[t]) > load(best, ctas[best])))
+      const uint64_t groups = (work_units(items[t], S) + kChains - 1) / kChains;
+      if (ctas[t] < groups && (best == kMaxBatch || load(t, ctas[t]) > load(best, ctas[best])))
         best = t;
     }
     if (best == kMaxBatch) break;
     ++ctas[best];
     ++used;
   }
-  // warps per CTA: enough for the busiest CTA's pairs, spread over whole rounds
-  uint32_t max_pairs = 1;
+  // warps per CTA: enough for the busiest CTA's groups, spread over whole rounds
+  uint32_t max_groups = 1;
   for (uint32_t t = 0; t < count; ++t) {
-    const uint64_t pairs = (work_units(items[t], S) + kChains - 1) / kChains;
-    const uint32_t per_cta = (uint32_t)((pairs + ctas[t] - 1) / ctas[t]);
-    if (per_cta > max_pairs) max_pairs = per_cta;
+    const uint64_t groups = (work_units(items[t], S) + kChains - 1) / kChains;
+    const uint32_t per_cta = (uint32_t)((groups + ctas[t] - 1) / ctas[t]);
+    if (per_cta > max_groups) max_groups = per_cta;
   }
-  const uint32_t rounds = (max_pairs + cap - 1) / cap;
-  warps = (max_pairs + rounds - 1) / rounds;
+  const uint32_t rounds = (max_groups + cap - 1) / cap;
+  warps = (max_groups + rounds - 1) / rounds;
   if (warps < 1) warps = 1;
   // largest table that still leaves room for these warps
   b.lut_shift = 2;
@@ -1179,9 +1379,9 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   return NZ_OK;
 }
 
-template <int S, bool MERGE, bool LIST = false>
+template <int S, bool MERGE, int MODE = kModeTensor>
 static int launch_decode(const BatchArgs &b, uint32_t warps, uint32_t smem_bytes, cudaStream_t st) {
-  auto kern = decode_kernel<S, MERGE, LIST>;
+  auto kern = decode_kernel<S, MERGE, MODE>;
   NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem_bytes));
   // Programmatic stream serialisation: this launch may begin while the previous
@@ -1229,13 +1429,26 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
     const bool gather = live[0].unit_list != nullptr;   // gather calls pass a single item
     b.unit_list = live[0].unit_list;
     b.n_list = live[0].n_list;
+    const bool dot = live[0].gx != nullptr;             // so do matrix-vector calls
+    b.gx = live[0].gx;
+    b.partial = live[0].partial;
+    b.in = live[0].in;
+    b.seg = live[0].seg;
     n_live = 0;
     if (gather) {
       switch (precision) {
-        case 0: return launch_decode<0, true, true>(b, warps, smem_bytes, st);
-        case 1: return launch_decode<1, true, true>(b, warps, smem_bytes, st);
-        case 3: return launch_decode<3, true, true>(b, warps, smem_bytes, st);
-        default: return launch_decode<7, true, true>(b, warps, smem_bytes, st);
+        case 0: return launch_decode<0, true, kModeList>(b, warps, smem_bytes, st);
+        case 1: return launch_decode<1, true, kModeList>(b, warps, smem_bytes, st);
+        case 3: return launch_decode<3, true, kModeList>(b, warps, smem_bytes, st);
+        default: return launch_decode<7, true, kModeList>(b, warps, smem_bytes, st);
+      }
+    }
+    if (dot) {
+      switch (precision) {
+        case 0: return launch_decode<0, true, kModeDot>(b, warps, smem_bytes, st);
+        case 1: return launch_decode<1, true, kModeDot>(b, warps, smem_bytes, st);
+        case 3: return launch_decode<3, true, kModeDot>(b, warps, smem_bytes, st);
+        default: return launch_decode<7, true, kModeDot>(b, warps, smem_bytes, st);
       }
     }
     if (!merge) return launch_decode<7, false>(b, warps, smem_bytes, st);
@@ -1276,6 +1489,9 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   it.out_exp = out_exp;
   it.unit_list = nullptr;
   it.n_list = 0;
+  it.gx = nullptr;
+  it.partial = nullptr;
+  it.in = it.seg = 0;
   return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
@@ -1365,6 +1581,9 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
       host[i].out_exp = nullptr;
       host[i].unit_list = nullptr;
       host[i].n_list = 0;
+      host[i].gx = nullptr;
+      host[i].partial = nullptr;
+      host[i].in = host[i].seg = 0;
     }
     int rc = nz::decode_many(host, m, precision, lane_symbols, canonical_nan, true, status,
                              (cudaStream_t)stream);
@@ -1405,6 +1624,9 @@ extern "C" int nz_decompress_bf16_units(const void *container, uint64_t containe
   it.out_exp = nullptr;
   it.unit_list = (const uint32_t *)unit_ids;
   it.n_list = n_ids;
+  it.gx = nullptr;
+  it.partial = nullptr;
+  it.in = it.seg = 0;
   return nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                          (cudaStream_t)stream);
 }
@@ -1534,5 +1756,76 @@ extern "C" int nz_gather_rows_bf16(const void *container, uint64_t container_byt
         (const int64_t *)rows_i64, n_rows_out, row_len, table_rows, U, per_row, staging,
         (uint16_t *)out_bf16);
   NZ_LAUNCH_CHECK("gather_copy_kernel");
+  return NZ_OK;
+}
+
+namespace nz {
+// Rows of an [out, in] matrix that one unit of U elements can touch.
+static inline uint32_t dot_segments(uint64_t in_features, uint64_t U) {
+  return (uint32_t)((U - 1) / in_features + 2);
+}
+}  // namespace nz
+
+extern "C" uint64_t nz_linear_vec_scratch_bytes(uint64_t n, uint64_t in_features,
+                                                uint32_t lane_symbols) {
+  if (!nz::valid_lane_symbols(lane_symbols) || in_features == 0) return 0;
+  const uint64_t U = 32ull * lane_symbols;
+  return nz::align16(nz::unit_count(n, lane_symbols) * nz::dot_segments(in_features, U) * 4);
+}
+
+extern "C" int nz_linear_vec_bf16(const void *container, uint64_t container_bytes,
+                                  const void *frac_in, uint64_t n, int precision,
+                                  uint32_t lane_symbols, uint32_t max_unit_words,
+                                  int canonical_nan, uint64_t in_features, const void *x_f32,
+                                  const void *bias_bf16, void *y_bf16, void *scratch,
+                                  uint64_t scratch_bytes, void *status, void *stream) {
+  if (!nz::valid_precision(precision)) {
+    nz::set_error("nz_linear_vec_bf16: precision must be 0, 1, 3 or 7 (got %d)", precision);
+    return NZ_E_ARG;
+  }
+  int rc = check_decode_args("nz_linear_vec_bf16", container, n, lane_symbols);
+  if (rc) return rc;
+  if (n == 0 || in_features == 0 || in_features % 256 || n % in_features ||
+      in_features >= (1ull << 31) || n / in_features >= (1ull << 31)) {
+    nz::set_error("nz_linear_vec_bf16: the matrix must have rows of a multiple of 256 elements "
+                  "(got %llu elements, rows of %llu)", (unsigned long long)n,
+                  (unsigned long long)in_features);
+    return NZ_E_ARG;
+  }
+  if (!x_f32 || ((uintptr_t)x_f32 & 15) || !y_bf16 || !frac_in || ((uintptr_t)frac_in & 7) ||
+      !scratch || ((uintptr_t)scratch & 15)) {
+    nz::set_error("nz_linear_vec_bf16: null or misaligned pointer (input vector and scratch "
+                  "16-byte, fractions 8-byte aligned)");
+    return NZ_E_ARG;
+  }
+  const uint64_t need = nz_linear_vec_scratch_bytes(n, in_features, lane_symbols);
+  if (scratch_bytes < need) {
+    nz::set_error("nz_linear_vec_bf16: scratch of %llu bytes is smaller than the %llu required",
+                  (unsigned long long)scratch_bytes, (unsigned long long)need);
+    return NZ_E_CAPACITY;
+  }
+  const uint64_t U = 32ull * lane_symbols;
+  nz::HostItem it;
+  it.container = container;
+  it.container_bytes = container_bytes;
+  it.frac = frac_in;
+  it.n = n;
+  it.max_unit_words = max_unit_words;
+  it.out_bf16 = nullptr;
+  it.out_exp = nullptr;
+  it.unit_list = nullptr;
+  it.n_list = 0;
+  it.gx = (const float *)x_f32;
+  it.partial = (float *)scratch;
+  it.in = (uint32_t)in_features;
+  it.seg = nz::dot_segments(in_features, U);
+  rc = nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
+                       (cudaStream_t)stream);
+  if (rc) return rc;
+  const uint32_t out_features = (uint32_t)(n / in_features);
+  nz::dot_finish_kernel<<<(out_features + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      (const float *)scratch, it.seg, U, it.in, out_features, (const uint16_t *)bias_bf16,
+      (uint16_t *)y_bf16);
+  NZ_LAUNCH_CHECK("dot_finish_kernel");
   return NZ_OK;
 }

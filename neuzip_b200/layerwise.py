@@ -31,11 +31,25 @@ def default_block_filter(module: torch.nn.Module) -> bool:
     return name.endswith(("DecoderLayer", "Block", "EncoderLayer")) and bool(_compressed_linears(module))
 
 
+def _single_vector(args, kwargs) -> bool:
+    """True when the block is called with one token of one sequence."""
+    x = args[0] if args else kwargs.get("hidden_states")
+    return torch.is_tensor(x) and x.dim() >= 1 and x.numel() == x.shape[-1]
+
+
 def attach(model: torch.nn.Module, manager,
-           is_block: Optional[Callable[[torch.nn.Module], bool]] = None) -> List:
-    """Install the hooks; returns the hook handles (call .remove() on each to undo)."""
+           is_block: Optional[Callable[[torch.nn.Module], bool]] = None,
+           fuse_single_token: bool = False) -> List:
+    """Install the hooks; returns the hook handles (call .remove() on each to undo).
+
+    With ``fuse_single_token`` a block that is called with a single token (the
+    decode step of batch-1 generation) is not decoded ahead: its Linears multiply
+    while decoding (``Manager.fuse_vector_linear``), which never writes the bf16
+    weights out.  Larger inputs keep the batched decode."""
     is_block = is_block or default_block_filter
     backend = manager._be
+    if fuse_single_token:
+        manager.fuse_vector_linear(True)
     blocks = [m for m in model.modules() if is_block(m)]
     # shared decode buffers: slot k is as large as the k-th Linear of the largest block
     sizes: List[int] = []
@@ -56,12 +70,14 @@ def attach(model: torch.nn.Module, manager,
             views = [buffers[k][:int(torch.Size(p._shape).numel())].view(p._shape)
                      for k, p in enumerate(params)]
 
-            def pre(mod, args, _params=params, _views=views, _batch=batch):
+            def pre(mod, args, kwargs, _params=params, _views=views, _batch=batch):
+                if fuse_single_token and _single_vector(args, kwargs):
+                    return
                 backend.run_batch(_batch)
                 for p, v in zip(_params, _views):
                     p._staged = v
         else:   # a backend without batched decode (the pass-through one)
-            def pre(mod, args, _params=params, _names=names):
+            def pre(mod, args, kwargs, _params=params, _names=names):
                 for p, w in zip(_params, manager.read_many(_names)):
                     p._staged = w
 
@@ -69,6 +85,6 @@ def attach(model: torch.nn.Module, manager,
             for p in _params:
                 p._staged = None
 
-        handles.append(block.register_forward_pre_hook(pre))
+        handles.append(block.register_forward_pre_hook(pre, with_kwargs=True))
         handles.append(block.register_forward_hook(post))
     return handles

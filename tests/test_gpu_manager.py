@@ -324,3 +324,101 @@ def test_read_rows_with_block_normaliser_falls_back_to_a_full_read():
     idx = torch.tensor([5, 599, 0, 5]).cuda()
     assert torch.equal(manager.read_rows(handle, idx).view(torch.int16),
                        manager.read(handle)[idx].view(torch.int16))
+
+
+@pytest.mark.parametrize("precision", (7, 3, 1, 0))
+@pytest.mark.parametrize("out_f,in_f", ((4096, 4096), (1000, 11008), (11008, 4096), (33, 768),
+                                        (5, 256), (257, 28672)))
+def test_fused_vector_linear_matches_decode_then_matmul(precision, out_f, in_f):
+    w = weights((out_f, in_f), out_f + in_f)
+    manager = neuzip.Manager(precision=precision)
+    handle = manager.write(w.cuda())
+    decoded = manager.read(handle).float()
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, 1, in_f, generator=g).to(torch.bfloat16).cuda()
+    bias = (torch.randn(out_f, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    manager.fuse_vector_linear(True)
+    for b in (None, bias):
+        ref = x.float().reshape(-1) @ decoded.t()                 # fp32 products and sums
+        if b is not None:
+            ref = ref + b.float()
+        got = manager.linear(handle, x, b)
+        assert got.shape == (1, 1, out_f) and got.dtype == torch.bfloat16
+        # one bf16 rounding of an fp32 sum whose order differs: half an ulp plus summation noise
+        err = (got.float().reshape(-1) - ref).abs()
+        tol = ref.abs() * 2.0 ** -8 + 1e-3 * decoded.abs().max() * x.float().abs().sum() / in_f ** 0.5
+        assert (err <= tol).all(), float((err - tol).max())
+        again = manager.linear(handle, x, b)                      # reproducible run to run
+        assert torch.equal(got.view(torch.int16), again.view(torch.int16))
+    # calls that do not qualify keep the decode + GEMM path, bit for bit
+    x2 = torch.randn(2, in_f, generator=g).to(torch.bfloat16).cuda()
+    manager.fuse_vector_linear(False)
+    plain = manager.linear(handle, x2)
+    manager.fuse_vector_linear(True)
+    assert torch.equal(manager.linear(handle, x2).view(torch.int16), plain.view(torch.int16))
+    manager.check()
+
+
+def test_fused_vector_linear_with_raw_units_and_short_lanes():
+    """Incompressible weights (units stored raw) and a backend with short lane streams
+    (units smaller than a row)."""
+    rng = np.random.default_rng(3)
+    out_f, in_f = 64, 2048
+    bits = rng.integers(0, 1 << 16, size=out_f * in_f, dtype=np.uint16)
+    bits[(bits & 0x7F80) == 0x7F80] = 0x3C00                      # no inf / NaN
+    bits[out_f * in_f // 2:] = bits_of(weights((out_f * in_f // 2,), 4))
+    w = torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).reshape(out_f, in_f).cuda()
+    # keep magnitudes finite for the comparison
+    w = torch.where(w.float().abs() < 1e4, w, torch.zeros_like(w))
+    for lane_symbols in (None, 64):
+        manager = neuzip.Manager(precision=7)
+        if lane_symbols:
+            manager._be.lane_symbols = lane_symbols
+        handle = manager.write(w)
+        manager.fuse_vector_linear(True)
+        x = torch.randn(in_f, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).cuda()
+        ref = manager.read(handle).float() @ x.float()
+        got = manager.linear(handle, x).float()
+        assert got.shape == (out_f,)
+        assert torch.allclose(got, ref, rtol=2.0 ** -7, atol=1e-2 * float(ref.abs().max()))
+        manager.check()
+
+
+def test_layerwise_fused_single_token_generation():
+    """With fuse_single_token the one-token steps of greedy generation multiply while
+    decoding; the prompt (many tokens) still takes the batched decode, bit for bit."""
+    transformers = pytest.importorskip("transformers")
+    from neuzip_b200 import layerwise
+    cfg = transformers.LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=768,
+                                   num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, max_position_embeddings=64)
+    torch.manual_seed(2)
+    model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+    m = neuzip.Manager()
+    m.convert(model)
+    ids = torch.randint(0, 512, (1, 9), device="cuda")
+    with torch.no_grad():
+        ref_prompt = model(ids).logits
+        ref_step = model(ids[:, :1]).logits                      # a one-token call, unfused
+    calls = {"n": 0}
+    inner = m._be._linear_vec
+
+    def spy(name, input, shape, bias):
+        out = inner(name, input, shape, bias)
+        calls["n"] += out is not None
+        return out
+
+    m._be._linear_vec = spy
+    hooks = layerwise.attach(model, m, fuse_single_token=True)
+    with torch.no_grad():
+        assert torch.equal(model(ids).logits, ref_prompt)        # 9 tokens: batched decode
+        assert calls["n"] == 0
+        step = model(ids[:, :1]).logits                          # 1 token: fused, 7 Linears x 2 blocks
+    assert calls["n"] == 14
+    assert torch.allclose(step.float(), ref_step.float(), rtol=0.05, atol=0.05)
+    with torch.no_grad():
+        out = model.generate(ids, max_new_tokens=6, do_sample=False)
+    assert out.shape == (1, 15)
+    for h in hooks:
+        h.remove()
+    m.check()
