@@ -603,7 +603,12 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
   }
   if (kAsync && (n_blocks % kRolled) == 0) {
     // Rolled form: the loop body covers kRolled blocks, so that the instruction
-    // working set of a CTA's warps stays small.
+    // working set of a CTA's warps stays small.  A trip starts at a multiple of
+    // kRolled: when that is a multiple of the ring size, a block's ring slot is a
+    // compile-time constant.
+    auto ring_slot = [](uint32_t block, int in_trip) -> uint32_t {
+      return (kRolled % kRingSlots == 0) ? (uint32_t)in_trip % kRingSlots : block % kRingSlots;
+    };
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
       if ((uint32_t)k < n_blocks) {
@@ -621,7 +626,7 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
         if (bk + 3 < n_blocks) {
 #pragma unroll
           for (int c = 0; c < kChains; ++c)
-            frac_async<S>(ring + ((bk + 3) & 3) * kRingSlotBytes + c * kRingUnitBytes,
+            frac_async<S>(ring + ring_slot(bk + 3, k + 3) * kRingSlotBytes + c * kRingUnitBytes,
                           frac[c] + (k + 3) * kFracStride);
         }
         frac_commit();
@@ -629,7 +634,7 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
         uint64_t bits[kChains];
 #pragma unroll
         for (int c = 0; c < kChains; ++c)
-          bits[c] = frac_from_ring<S>(ring + (bk & 3) * kRingSlotBytes + c * kRingUnitBytes);
+          bits[c] = frac_from_ring<S>(ring + ring_slot(bk, k) * kRingSlotBytes + c * kRingUnitBytes);
 #pragma unroll
         for (int c = 0; c < kChains; ++c) sink.begin(c);
         uint32_t w[kChains][4];
