@@ -6,22 +6,24 @@
 // fractions straight into the bf16 output, so the exponent stream never makes
 // the round trip through HBM.
 //
-// Work decomposition.  One warp decodes one unit (32 lane streams of S
-// symbols).  The unit's coded bytes are staged into the warp's shared-memory
-// slot with one bulk asynchronous copy (cp.async.bulk + mbarrier, no
-// multicast); each lane then walks its own stream with a private read pointer,
-// so a renormalisation costs one predicated 16-bit shared load and no
-// warp-wide vote.  A lane produces 8 consecutive tensor elements per step and
+// Work decomposition.  One CTA per SM; a warp decodes kChains units side by
+// side (32 lane streams of S symbols each: the independent rANS chains hide one
+// another's latency).  The units' coded bytes are staged into the warp's
+// shared-memory slots with bulk asynchronous copies (cp.async.bulk + mbarrier,
+// no multicast); each lane then walks its own stream with a private read
+// pointer, so a renormalisation costs one predicated 16-bit shared load and no
+// warp-wide vote.  A lane produces 8 consecutive tensor elements per block and
 // writes them with one 128-bit store; the warp's stores are 512 contiguous
-// bytes.
+// bytes.  The same kernel, instantiated differently, decodes a list of units
+// (gather) or feeds the decoded words to a dot product instead of a store.
 //
-// Decode table.  One entry per slot (symbol | bias << 8 | freq << 20), built
-// once per CTA from the container's frequency table.  Random table lookups by
-// 32 lanes would collide in the 32 shared-memory banks (3.5 wavefronts per
-// lookup on average, which made the shared-memory pipe the limiter), so the
-// table is replicated: with 2^10 slots every lane reads its own copy in its own
-// bank (always one wavefront), with 2^11 slots two lanes share a copy, with 2^12
-// four.  The replicated table always fills 128 KB; one CTA runs per SM.
+// Decode table.  One 32-bit entry per slot (symbol << 23 | freq << 12 | offset
+// inside the symbol's slot range), built once per CTA from the container's
+// frequency table.  Random table lookups by 32 lanes would collide in the 32
+// shared-memory banks (3.5 wavefronts per lookup on average, which made the
+// shared-memory pipe the limiter), so the table is replicated across banks as
+// far as the shared memory left by the slots allows (64 KB for lossless
+// tensors: 32 copies of a 2^9-slot table, one per bank; 16 of a 2^10-slot one).
 //
 // Robustness.  Header, offset table and lane lengths are validated before
 // use; a malformed container sets bits in the caller's status word and the
