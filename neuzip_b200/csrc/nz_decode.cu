@@ -1389,8 +1389,16 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
 template <int S, bool MERGE, int MODE = kModeTensor>
 static int launch_decode(const BatchArgs &b, uint32_t warps, uint32_t smem_bytes, cudaStream_t st) {
   auto kern = decode_kernel<S, MERGE, MODE>;
-  NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)smem_bytes));
+  // the opt-in to large dynamic shared memory is per kernel and device: set it when a
+  // launch needs more than any earlier one on this device did
+  static uint32_t opted[64] = {};
+  int dev = 0;
+  NZ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || opted[dev] < smem_bytes) {
+    NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes));
+    if (dev >= 0 && dev < 64) opted[dev] = smem_bytes;
+  }
   // Programmatic stream serialisation: this launch may begin while the previous
   // kernel of the stream drains; the kernel itself waits (griddepcontrol.wait)
   // before it reads or writes global memory, so ordering is preserved.

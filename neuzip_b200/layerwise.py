@@ -31,6 +31,14 @@ def default_block_filter(module: torch.nn.Module) -> bool:
     return name.endswith(("DecoderLayer", "Block", "EncoderLayer")) and bool(_compressed_linears(module))
 
 
+class _Stage:
+    """Which block's weights the shared decode buffers hold (-1: none)."""
+    __slots__ = ("current",)
+
+    def __init__(self) -> None:
+        self.current = -1
+
+
 def _single_vector(args, kwargs) -> bool:
     """True when the block is called with one token of one sequence."""
     x = args[0] if args else kwargs.get("hidden_states")
@@ -61,29 +69,41 @@ def attach(model: torch.nn.Module, manager,
             else:
                 sizes[k] = max(sizes[k], n)
     buffers = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for n in sizes]
+    stage = _Stage()
     handles = []
-    for block in blocks:
+    for number, block in enumerate(blocks):
         params = [lin._p for lin in _compressed_linears(block)]
         names = [p._handle for p in params]
         if hasattr(backend, "make_batch"):
+            # The Linears keep their views of the shared buffers for good; a view counts
+            # only while `stage.current` names its block, so staging a block is one
+            # batched decode and one assignment, and un-staging is one assignment.
             batch = backend.make_batch(names, buffers[:len(names)])
-            views = [buffers[k][:int(torch.Size(p._shape).numel())].view(p._shape)
-                     for k, p in enumerate(params)]
+            for k, p in enumerate(params):
+                p._staged = buffers[k][:int(torch.Size(p._shape).numel())].view(p._shape)
+                p._stage_tag = (stage, number)
 
-            def pre(mod, args, kwargs, _params=params, _views=views, _batch=batch):
+            def pre(mod, args, kwargs, _batch=batch, _number=number):
                 if fuse_single_token and _single_vector(args, kwargs):
                     return
                 backend.run_batch(_batch)
-                for p, v in zip(_params, _views):
-                    p._staged = v
+                stage.current = _number
+
+            def post(mod, args, output):
+                stage.current = -1
         else:   # a backend without batched decode (the pass-through one)
-            def pre(mod, args, kwargs, _params=params, _names=names):
+            own = _Stage()
+
+            def pre(mod, args, kwargs, _params=params, _names=names, _own=own):
                 for p, w in zip(_params, manager.read_many(_names)):
                     p._staged = w
+                    p._stage_tag = (_own, 0)
+                _own.current = 0
 
-        def post(mod, args, output, _params=params):
-            for p in _params:
-                p._staged = None
+            def post(mod, args, output, _params=params, _own=own):
+                _own.current = -1
+                for p in _params:
+                    p._staged = None
 
         handles.append(block.register_forward_pre_hook(pre, with_kwargs=True))
         handles.append(block.register_forward_hook(post))

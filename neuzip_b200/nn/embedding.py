@@ -22,7 +22,7 @@ class Embedding(torch.nn.Module):
         self._p = Parameter(manager, embedding.weight)
 
     def forward(self, x):
-        staged = getattr(self._p, "_staged", None)
+        staged = self._p.staged()
         if self.max_norm is not None or staged is not None or not hasattr(self.manager, "read_rows"):
             return F.embedding(x, self._p(), self.padding_idx, self.max_norm, self.norm_type,
                                self.scale_grad_by_freq, self.sparse)

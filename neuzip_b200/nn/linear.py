@@ -21,6 +21,10 @@ class Linear(torch.nn.Module):
         return self._p
 
     def forward(self, x):
+        if not torch.is_grad_enabled():
+            staged = self._p.staged()
+            if staged is not None:          # decoded ahead for the whole block: a plain linear
+                return torch.nn.functional.linear(x, staged, self.bias)
         if not (torch.is_grad_enabled() and (x.requires_grad or self._p.requires_grad)):
             # inference: same arithmetic without the autograd.Function round trip
             if torch.is_autocast_enabled():

@@ -15,18 +15,27 @@ class Parameter(torch.nn.Parameter):
         self._shape = data.shape
         self._gradient = None
         self._handle = manager.write(data)
+        self._staged = None        # view of a shared decode buffer (neuzip_b200.layerwise)
+        self._stage_tag = None     # (stage, block number): the view is valid while they agree
         return self
+
+    def staged(self):
+        """The already decoded weight, if a layer-wise prefetch holds it right now."""
+        tag = self._stage_tag
+        if tag is not None and tag[0].current == tag[1]:
+            return self._staged
+        return None
 
     @torch.no_grad()
     def __call__(self) -> torch.Tensor:
-        staged = getattr(self, "_staged", None)
+        staged = self.staged()
         if staged is not None:
             return staged
         w = self._manager.read(self._handle).reshape(self._shape)
         return w.to(self.device).requires_grad_(False)
 
     def linear(self, inputs, bias=None):
-        staged = getattr(self, "_staged", None)
+        staged = self.staged()
         if staged is not None:
             # a layer-wise prefetch (neuzip_b200.layerwise) already decoded this weight
             return torch.nn.functional.linear(inputs, staged, bias)
