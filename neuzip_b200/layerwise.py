@@ -68,13 +68,14 @@ def attach(model: torch.nn.Module, manager,
                 sizes.append(n)
             else:
                 sizes[k] = max(sizes[k], n)
-    buffers = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for n in sizes]
+    batched = hasattr(backend, "make_batch")
+    buffers = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for n in sizes] if batched else []
     stage = _Stage()
     handles = []
     for number, block in enumerate(blocks):
         params = [lin._p for lin in _compressed_linears(block)]
         names = [p._handle for p in params]
-        if hasattr(backend, "make_batch"):
+        if batched:
             # The Linears keep their views of the shared buffers for good; a view counts
             # only while `stage.current` names its block, so staging a block is one
             # batched decode and one assignment, and un-staging is one assignment.

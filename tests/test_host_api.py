@@ -225,3 +225,54 @@ def test_state_dict_round_trip_keeps_the_compressed_weights(tmp_path):
     assert not torch.equal(dst(ids), expect)
     dst.load_state_dict(torch.load(path, weights_only=False))
     assert torch.equal(dst(ids), expect)
+
+
+class TwoBlocks(torch.nn.Module):
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(16, 16, bias=False)
+            self.b = torch.nn.Linear(16, 16, bias=True)
+
+        def forward(self, x):
+            return self.b(torch.relu(self.a(x)))
+
+    def __init__(self):
+        super().__init__()
+        self.blocks = torch.nn.ModuleList([TwoBlocks.Block(), TwoBlocks.Block()])
+
+    def forward(self, x):
+        for blk in self.blocks:
+            x = blk(x)
+        return x
+
+
+def test_layerwise_hooks_stage_one_block_at_a_time_on_cpu():
+    """Host logic of neuzip_b200.layerwise with the CPU stand-in backend: a block's
+    weights are staged while it runs and only then; results match the per-Linear path."""
+    from neuzip_b200 import layerwise
+    torch.manual_seed(0)
+    model = TwoBlocks().to(torch.bfloat16)
+    m = cpu_manager()
+    m.convert(model)
+    x = torch.randn(3, 16).to(torch.bfloat16)
+    with torch.no_grad():
+        ref = model(x)
+    hooks = layerwise.attach(model, m)
+    assert len(hooks) == 4
+    seen = []
+    for i, blk in enumerate(model.blocks):
+        blk.a.register_forward_pre_hook(
+            lambda mod, args, i=i: seen.append([b.a._p.staged() is not None for b in model.blocks]))
+    with torch.no_grad():
+        got = model(x)
+    assert torch.equal(got, ref)
+    assert seen == [[True, False], [False, True]]
+    assert all(b.a._p.staged() is None for b in model.blocks)      # nothing stays staged
+    # training through the hooks: gradients land in _gradient as without them
+    model(x).float().sum().backward()
+    assert all(b.a._p._gradient is not None for b in model.blocks)
+    for h in hooks:
+        h.remove()
+    with torch.no_grad():
+        assert torch.equal(model(x), ref)
