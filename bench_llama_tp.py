@@ -15,7 +15,6 @@ and rank): a synthetic stand-in for the Llama checkpoints.
 """
 import argparse
 import json
-import math
 import os
 import time
 

@@ -14,8 +14,7 @@ codec is deterministic.
 """
 from __future__ import annotations
 
-import math
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, Iterable, List
 
 import torch
 import torch.distributed as dist
