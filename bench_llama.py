@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Model-level check of the codec: a random-init Llama-architecture model,
-dense vs. converted with neuzip.Manager (BASELINE configs 3 and 4 shapes).
+dense vs. converted with neuzip.Manager (configurations 3 and 4 of the benchmark list).
 
     python bench_llama.py --config 7b --prompt 128 --new 256 [--precision 7]
 
@@ -40,7 +40,7 @@ def timed_generate(model, ids, new_tokens):
 
 
 def train_mode(args):
-    """BASELINE config 4 shape: AdamW training with lossless compressed weights,
+    """Configuration 4 of the benchmark list: AdamW training with lossless compressed weights,
     per-layer decode in forward and backward, data-parallel over the ranks."""
     import os
     import torch.distributed as dist

@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Tensor-parallel Llama-architecture decode with compressed weights
-(BASELINE config 5 shape: 70B, 80 layers, d_model 8192, 64 heads / 8 KV heads,
+(the 70B inference configuration of the benchmark list: 70B, 80 layers, d_model 8192, 64 heads / 8 KV heads,
 FFN 28672, vocab 32000, precision 3), dense vs. neuzip, on the ranks of one node.
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \

@@ -3,7 +3,7 @@
 The reference only ships an in-backward SGD step for compressed parameters
 (`compressed_lomo_hook`, neuzip/__init__.py:25-35: decompress, add -lr * grad,
 recompress).  This optimiser keeps that read -> update -> write shape and adds
-what BASELINE's training configuration asks for: AdamW moments (fp32, kept
+what the training configuration of the benchmark list asks for: AdamW moments (fp32, kept
 uncompressed) and, under torch.distributed, an all-reduce of each compressed
 weight's gradient.  The reference accumulates that gradient in the side
 attribute `_gradient` (neuzip/ops/linear.py:37-40), which DDP never sees, so its

@@ -2,7 +2,7 @@
 
 Run from the repository root:  python tests/golden/make_golden.py
 
-The input is BASELINE config 1: torch.manual_seed(0) on the CPU generator,
+The input is configuration 1 of the benchmark list: torch.manual_seed(0) on the CPU generator,
 (randn(4096, 4096) * 0.02).to(bfloat16).  `input_crc32`, `exp_crc32` and
 `frac_crc32` were first derived independently (from cuda/kernels.cuh:120-155 of
 the reference) when the reference was surveyed; `expected_from_survey` below
