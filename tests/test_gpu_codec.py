@@ -251,6 +251,27 @@ def test_argument_errors():
     assert L.nz_split_bf16(x.data_ptr() + 2, 8, 7, e.data_ptr(), e.data_ptr(), 0) == _lib.NZ_E_ARG
     assert L.nz_decode_exponents(e.data_ptr(), 64, 64, 12, 0, e.data_ptr(), 0, 0) == _lib.NZ_E_ARG
     assert L.nz_encode_exponents(e.data_ptr(), 64, 256, e.data_ptr(), 64, e.data_ptr(), 64, 0) == _lib.NZ_E_CAPACITY
+    # gather and matrix-vector entry points: bad geometry and short scratch are refused
+    w = weights(4096 * 8, 1).cuda()
+    cont, frac, mw = A.compress(w, 7, 256)
+    n = w.numel()
+    y = torch.zeros(4096, dtype=torch.bfloat16, device="cuda")
+    xf = torch.zeros(4096, dtype=torch.float32, device="cuda")
+    sc = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    rows = torch.zeros(4, dtype=torch.int64, device="cuda")
+    args = (cont.data_ptr(), cont.numel(), frac.data_ptr(), n, 7, 256, mw, 0)
+    assert L.nz_linear_vec_bf16(*args, 100, xf.data_ptr(), None, y.data_ptr(), sc.data_ptr(),
+                                sc.numel(), None, 0) == _lib.NZ_E_ARG          # rows not a multiple of 256
+    assert b"multiple of 256" in L.nz_last_error()
+    assert L.nz_linear_vec_bf16(*args, 4096, xf.data_ptr(), None, y.data_ptr(), sc.data_ptr(),
+                                16, None, 0) == _lib.NZ_E_CAPACITY
+    assert L.nz_linear_vec_scratch_bytes(n, 4096, 256) <= sc.numel()
+    assert L.nz_gather_rows_bf16(*args, 1000, rows.data_ptr(), 4, y.data_ptr(), sc.data_ptr(),
+                                 sc.numel(), None, 0) == _lib.NZ_E_ARG        # 1000 does not divide n
+    assert L.nz_gather_rows_bf16(*args, 4096, rows.data_ptr(), 4, y.data_ptr(), sc.data_ptr(),
+                                 64, None, 0) == _lib.NZ_E_CAPACITY
+    assert L.nz_decompress_bf16_units(*args, None, 3, y.data_ptr(), None, 0) == _lib.NZ_E_ARG
+    assert L.nz_decompress_bf16_units(*args, None, 0, y.data_ptr(), None, 0) == _lib.NZ_OK
 
 
 # ------------------------------------------------------------- batched decode
