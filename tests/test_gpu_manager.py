@@ -422,3 +422,34 @@ def test_layerwise_fused_single_token_generation():
     for h in hooks:
         h.remove()
     m.check()
+
+
+def test_batched_decode_can_be_captured_in_a_cuda_graph():
+    """The decode entry points only enqueue work on the caller's stream (no allocation, no
+    host synchronisation), so a serving loop can record them in a CUDA graph."""
+    manager = neuzip.Manager(precision=7)
+    shapes = [(512, 1024), (1024, 512), (256, 2048)]
+    ws = [weights(s, 40 + i).cuda() for i, s in enumerate(shapes)]
+    handles = [manager.write(w) for w in ws]
+    be = manager._be
+    outs = [torch.zeros(w.numel(), dtype=torch.bfloat16, device="cuda") for w in ws]
+    batch = be.make_batch(handles, outs)
+    be.run_batch(batch)                                   # warm-up outside capture
+    torch.cuda.synchronize()
+    for o in outs:
+        o.zero_()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            be.run_batch(batch)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        for o in outs:
+            o.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for o, w in zip(outs, ws):
+            assert torch.equal(o.view(torch.int16), w.view(-1).view(torch.int16))
+    manager.check()
