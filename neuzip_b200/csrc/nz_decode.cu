@@ -273,6 +273,36 @@ __device__ __forceinline__ uint32_t merge_word(uint32_t ea, uint32_t eb, uint64_
     const uint32_t half = (pair < 2) ? (uint32_t)fbits : (uint32_t)(fbits >> 32);
     return merge_pair_s7(ea, eb, half, (pair & 1) ? 0x3322 : 0x1100);
   }
+  if (!CANON) {
+    // Lossy precisions: the pair's (s+1)-bit fields share one byte B of the packed
+    // fractions.  One multiplication lays copies of B side by side (the shifts are
+    // far enough apart that the copies never overlap, so nothing carries) such that
+    // every sign and mantissa bit has a copy at its place in the output word; a mask
+    // keeps those places.  The exponents come in place from the two entries' upper
+    // halves, as in the lossless path.
+    const uint32_t e = __byte_perm(ea, eb, 0x7632) & 0x7F807F80u;
+    const uint32_t f = (uint32_t)fbits;
+    if (S == 3) {
+      // B = [sa ma2 ma1 ma0 sb mb2 mb1 mb0]: ma -> bits 4..6 (shift 0), sa -> 15 (8),
+      // mb -> 20..22 (20), sb -> 31 (28)
+      const uint32_t B = __byte_perm(f, 0, 0x4440 | pair);
+      return e | ((B * 0x10100101u) & 0x80708070u);
+    }
+    if (S == 1) {
+      // B holds four 2-bit fields [s m]; the pair is the upper or the lower two of them
+      const uint32_t B = __byte_perm(f, 0, 0x4440 | (pair >> 1));
+      // upper two: sa bit 7 -> 15 (8), ma bit 6 -> 6 (0), sb bit 5 -> 31 (26), mb bit 4 -> 22 (18)
+      // lower two: sa bit 3 -> 15 (12), ma bit 2 -> 6 (4), sb bit 1 -> 31 (30), mb bit 0 -> 22 (22)
+      const uint32_t m = (pair & 1) ? 0x40401010u : 0x04040101u;
+      return e | ((B * m) & 0x80408040u);
+    }
+    if (S == 0) {
+      // B holds the block's eight sign bits, first element in bit 7:
+      // sa bit 7-2p -> 15 (8+2p), sb bit 6-2p -> 31 (25+2p)
+      const uint32_t B = f & 0xFFu;
+      return e | ((B * ((1u << (8 + 2 * pair)) + (1u << (25 + 2 * pair)))) & 0x80008000u);
+    }
+  }
   return merge_pair_generic<S>(ea, eb, field_of<S>(fbits, 2 * pair), field_of<S>(fbits, 2 * pair + 1),
                                CANON);
 }
