@@ -474,9 +474,17 @@ constexpr int kChains = NZ_DECODE_CHAINS;        // units a warp decodes side by
 constexpr int kFastRow = 7;                      // 128-byte table rows: one copy per bank
 constexpr int kRolled = NZ_DECODE_ROLLED;        // blocks per trip of the rolled decode loop
 constexpr uint32_t kRingSlots = 4;               // blocks of fractions in flight per unit + 1
-constexpr uint32_t kRingUnitBytes = 256;         // 32 lanes x 8 bytes
-constexpr uint32_t kRingSlotBytes = kChains * kRingUnitBytes;
-constexpr uint32_t kRingBytes = kRingSlots * kRingSlotBytes;
+// Shared-memory ring of a warp for the packed fractions, by precision.  One unit's
+// place holds, for precisions 7 and 3, one block (32 lanes x 8 or 4 bytes; four such
+// slots) and, for precisions 1 and 0, a group of four blocks (32 lanes x 8 or 4
+// bytes; two buffers).
+__host__ __device__ constexpr uint32_t ring_unit_bytes(int precision) {
+  return (precision == 7 || precision == 1) ? 256u : 128u;
+}
+__host__ __device__ constexpr uint32_t ring_warp_bytes(int precision) {
+  return ((precision == 7 || precision == 3) ? kRingSlots : 2u) * kChains *
+         ring_unit_bytes(precision);
+}
 
 // Where the four words (8 bf16) that a lane produces per block and chain go.
 // StoreSink writes them to the output tensor.
@@ -569,6 +577,8 @@ __device__ __forceinline__ void decode_blocks_multi(LaneState (&st)[kChains], co
   constexpr uint32_t kFracStride = 32u * (S + 1);
   constexpr bool kAsync = MERGE && (S == 7 || S == 3);
   constexpr int kAhead = 4;
+  constexpr uint32_t kRingUnitBytes = ring_unit_bytes(S);
+  constexpr uint32_t kRingSlotBytes = kChains * kRingUnitBytes;
   if (MERGE && (S == 0 || S == 1) && (n_blocks & 3) == 0) {
     // Narrow fractions: four blocks of a unit are 128 (s=0) or 256 (s=1) contiguous
     // bytes, copied by the whole warp (4 or 8 bytes per lane) into a double-buffered
@@ -1100,7 +1110,8 @@ decode_kernel(const BatchArgs batch) {
   const uint32_t bar = smem_u32(&bars[warp]);
   const uint32_t slot0 = smem_u32(slots + (uint64_t)(kChains * warp) * a.slot_bytes);
   // per-warp ring for the packed fractions, behind all slots and their guard band
-  const uint32_t ring = smem_u32(smem) + a.ring_offset + warp * kRingBytes + lane * (S == 7 ? 8 : 4);
+  const uint32_t ring =
+      smem_u32(smem) + a.ring_offset + warp * ring_warp_bytes(S) + lane * (S == 7 ? 8 : 4);
 
   // Each warp owns one mbarrier; its lane 0 initialises it and is the only
   // thread that ever arms it.
@@ -1323,8 +1334,8 @@ static inline uint64_t work_units(const HostItem &it, uint32_t S) {
 // same number of warps, every warp the same number of unit groups (within one).
 // The decode table gets what shared memory the slots and rings leave (more
 // copies = fewer bank conflicts), at most 128 KB.
-static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, BatchArgs &b,
-                           uint32_t &warps, uint32_t &smem_bytes) {
+static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, uint32_t ring_bytes,
+                           BatchArgs &b, uint32_t &warps, uint32_t &smem_bytes) {
   const uint64_t U = 32ull * S;
   uint64_t unit_bytes = 0, total_units = 0;
   for (uint32_t t = 0; t < count; ++t) {
@@ -1338,7 +1349,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   const uint32_t guard = ((S + 8) * 2 + 127) & ~127u;
   const uint32_t sm_smem = 227u * 1024u;
   const uint32_t kMaxWarps = items[0].gx ? (uint32_t)kDotMaxWarps : (uint32_t)NZ_DECODE_MAX_WARPS;
-  const uint32_t per_warp = kChains * b.slot_bytes + kRingBytes;
+  const uint32_t per_warp = kChains * b.slot_bytes + ring_bytes;
   const uint32_t min_fixed = 16 * 1024 + 1024 + guard;
   if (min_fixed + per_warp > sm_smem) {
     set_error("decode: a warp's units of %u symbols do not fit in shared memory", (unsigned)U);
@@ -1409,7 +1420,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, Ba
   }
   b.lut_bytes = 4096u << b.lut_shift;
   b.ring_offset = b.lut_bytes + 1024 + guard + warps * kChains * b.slot_bytes;
-  smem_bytes = b.ring_offset + warps * kRingBytes;
+  smem_bytes = b.ring_offset + warps * ring_bytes;
   uint32_t begin = 0;
   for (uint32_t t = 0; t < count; ++t) {
     b.item[t].cta_begin = begin;
@@ -1459,7 +1470,9 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
     BatchArgs b;
     memset(&b, 0, sizeof(b));
     uint32_t warps = 0, smem_bytes = 0;
-    int rc = decode_geometry(live, n_live, S, b, warps, smem_bytes);
+    // the exponent-only kernel is the precision-7 instantiation
+    int rc = decode_geometry(live, n_live, S, ring_warp_bytes(merge ? precision : 7), b, warps,
+                             smem_bytes);
     if (rc) return rc;
     b.count = n_live;
     b.S = S;
