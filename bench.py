@@ -214,6 +214,8 @@ def make_batches(stack, outs_per_layer):
             arr[k].frac_in = f.data_ptr()
             arr[k].n = n
             arr[k].max_unit_words = mw
+            # the stack was compressed (and the device synchronised) before any timed pass
+            arr[k].flags = _lib.NZ_ITEM_INPUTS_STABLE
             arr[k].out_bf16 = outs_per_layer[(base // per_layer) % len(outs_per_layer)][k].data_ptr()
         batches.append((arr, len(chunk), chunk[0][3]))
     return batches

@@ -203,6 +203,14 @@ int nz_adamw_bf16(void *weight_bf16, const void *grad_bf16, void *exp_avg,
                   float beta1, float beta2, float eps, float weight_decay,
                   uint32_t step, float grad_scale, void *stream);
 
+/* Item flag: the container and the fractions were complete (written and
+ * visible) before the kernel that precedes this call on the stream was
+ * launched -- true for weights that were compressed earlier and are decoded
+ * again and again.  When every item of a launch says so, the launch builds its
+ * decode table while the previous kernel drains instead of after it.  Never
+ * set it for data written by the work enqueued just before the call. */
+#define NZ_ITEM_INPUTS_STABLE 0x1u
+
 /* One tensor of a batched decompress. */
 typedef struct nz_decompress_item {
   const void *container;     /* NZR1 container, 16-byte aligned            */
@@ -210,7 +218,7 @@ typedef struct nz_decompress_item {
   const void *frac_in;       /* packed fractions, 8-byte aligned           */
   uint64_t n;                /* elements                                   */
   uint32_t max_unit_words;   /* from nz_container_bytes, 0 = worst case    */
-  uint32_t reserved;
+  uint32_t flags;            /* NZ_ITEM_* bits, 0 = none                   */
   void *out_bf16;            /* bf16[n], 16-byte aligned                   */
 } nz_decompress_item;
 

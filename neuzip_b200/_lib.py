@@ -16,6 +16,7 @@ _SO_PATH = os.path.join(_PKG_DIR, "libneuzip_b200.so")
 _CSRC = os.path.join(_PKG_DIR, "csrc")
 
 NZ_OK = 0
+NZ_ITEM_INPUTS_STABLE = 0x1
 NZ_E_ARG, NZ_E_CUDA, NZ_E_CAPACITY, NZ_E_FORMAT, NZ_E_DEVICE = -1, -2, -3, -4, -5
 STATUS_BITS = {
     0x1: "bad header",
@@ -57,7 +58,7 @@ SIGNATURES = {
 class DecompressItem(ctypes.Structure):
     """struct nz_decompress_item"""
     _fields_ = [("container", _vp), ("container_bytes", _u64), ("frac_in", _vp), ("n", _u64),
-                ("max_unit_words", _u32), ("reserved", _u32), ("out_bf16", _vp)]
+                ("max_unit_words", _u32), ("flags", _u32), ("out_bf16", _vp)]
 
 
 _f32 = ctypes.c_float

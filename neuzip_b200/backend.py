@@ -96,6 +96,9 @@ class CodecBackend:
         self._vec_ver = -1
         self._vec_x: Optional[torch.Tensor] = None
         self._vec_scratch: Dict[tuple, torch.Tensor] = {}
+        # True while the last thing this backend enqueued wrote compressed bytes: the
+        # next decode launch must then wait for it before it reads them
+        self._fresh_writes = True
 
     # -- helpers ---------------------------------------------------------
     def _ensure_device(self) -> None:
@@ -153,6 +156,7 @@ class CodecBackend:
         container = staging[: total.value].clone()
         self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac,
                                    normalizers)
+        self._fresh_writes = True
 
     def read(self, name: str) -> torch.Tensor:
         """cuda/high_level.cu:223-250 (+ _decompress_and_merge :164-206); no host sync."""
@@ -237,10 +241,12 @@ class CodecBackend:
                 items[k].frac_in = _ptr(e.fractions)
                 items[k].n = e.numel
                 items[k].max_unit_words = e.max_unit_words
+                items[k].flags = 0 if self._fresh_writes else _lib.NZ_ITEM_INPUTS_STABLE
                 items[k].out_bf16 = _ptr(outs[i])
             _lib.check(self._lib.nz_decompress_bf16_batch(
                 items, len(idx), self.precision, S, int(self.canonical_nan), _ptr(self._status),
                 _stream()))
+            self._fresh_writes = False
         for e, out in zip(entries, outs):
             self._denormalize(e, out)
         return outs
@@ -254,22 +260,30 @@ class CodecBackend:
         S = {e.lane_symbols for e in entries}
         if len(S) != 1:
             raise ValueError("a batch must share one lane_symbols value")
-        items = (_lib.DecompressItem * len(entries))()
-        for k, (e, out) in enumerate(zip(entries, outs)):
-            if out.numel() < e.numel or out.dtype != torch.bfloat16 or not out.is_cuda:
-                raise ValueError("output buffers must be CUDA bf16 tensors of at least numel elements")
-            items[k].container = _ptr(e.container)
-            items[k].container_bytes = e.container.numel()
-            items[k].frac_in = _ptr(e.fractions)
-            items[k].n = e.numel
-            items[k].max_unit_words = e.max_unit_words
-            items[k].out_bf16 = _ptr(out)
+        # two argument blocks: with and without the promise that the inputs are stable
+        blocks = []
+        for flags in (0, _lib.NZ_ITEM_INPUTS_STABLE):
+            items = (_lib.DecompressItem * len(entries))()
+            for k, (e, out) in enumerate(zip(entries, outs)):
+                if out.numel() < e.numel or out.dtype != torch.bfloat16 or not out.is_cuda:
+                    raise ValueError(
+                        "output buffers must be CUDA bf16 tensors of at least numel elements")
+                items[k].container = _ptr(e.container)
+                items[k].container_bytes = e.container.numel()
+                items[k].frac_in = _ptr(e.fractions)
+                items[k].n = e.numel
+                items[k].max_unit_words = e.max_unit_words
+                items[k].flags = flags
+                items[k].out_bf16 = _ptr(out)
+            blocks.append(items)
         # keep the tensors alive as long as the batch exists
-        return (items, len(entries), S.pop(), [e.container for e in entries],
+        return (blocks, len(entries), S.pop(), [e.container for e in entries],
                 [e.fractions for e in entries], list(outs), entries)
 
     def run_batch(self, batch) -> None:
-        items, count, S = batch[0], batch[1], batch[2]
+        blocks, count, S = batch[0], batch[1], batch[2]
+        items = blocks[0] if self._fresh_writes else blocks[1]
+        self._fresh_writes = False
         rc = self._lib.nz_decompress_bf16_batch(items, count, self.precision, S,
                                                 int(self.canonical_nan), _ptr(self._status),
                                                 _stream())
@@ -387,6 +401,7 @@ class CodecBackend:
             normalizers = normalizers.to(device="cuda", dtype=torch.uint8).contiguous()
         self._cache[name] = _Entry(n, torch.bfloat16, int(blob["lane_symbols"]),
                                    int(blob["max_unit_words"]), container, fractions, normalizers)
+        self._fresh_writes = True
 
     # -- extras -----------------------------------------------------------
     def erase(self, name: str) -> None:

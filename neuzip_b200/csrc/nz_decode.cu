@@ -351,6 +351,7 @@ struct BatchArgs {
   const float *gx;             // matrix-vector launches (count == 1), see DecodeArgs
   float *partial;
   uint32_t in, seg;
+  uint32_t inputs_stable;      // containers and fractions were complete before the previous kernel
   uint32_t count;
   uint32_t n_ctas;        // == gridDim.x
   uint32_t S, slot_bytes, lut_shift, lut_bytes, ring_offset;
@@ -1123,9 +1124,14 @@ decode_kernel(const BatchArgs batch) {
   __syncwarp();
   // Programmatic dependent launch: let the next kernel of the stream start its
   // own launch now, and do not touch global memory before the previous kernel
-  // has completed.  Both are no-ops for an ordinary launch.
+  // of the stream has completed.  When the caller vouches that the compressed
+  // inputs were complete before that kernel was launched, only the outputs (and
+  // the input vector of a matrix-vector launch) depend on it: the wait then
+  // moves behind the table build, which overlaps the previous kernel's tail.
+  // Both instructions are no-ops for an ordinary launch.
+  const bool early = MODE != kModeList && batch.inputs_stable != 0;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- start fetching the first group of units, build the decode table meanwhile
   const Header *h = reinterpret_cast<const Header *>(a.container);
@@ -1233,6 +1239,7 @@ decode_kernel(const BatchArgs batch) {
   }
   const bool canon = MERGE && a.canon && (cum_sh[256] != cum_sh[255]);
   __syncthreads();
+  if (early) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- units, kChains at a time
   const uint8_t *payload = a.container + pay_off;
@@ -1321,6 +1328,7 @@ struct HostItem {
   const float *gx;             // matrix-vector: input vector (else null), partial sums,
   float *partial;              //   row length and partial-sum places per unit
   uint32_t in, seg;
+  uint32_t flags;              // NZ_ITEM_* of the C interface
 };
 
 // Units a launch decodes for an item.
@@ -1495,6 +1503,9 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
     b.partial = live[0].partial;
     b.in = live[0].in;
     b.seg = live[0].seg;
+    b.inputs_stable = 1;
+    for (uint32_t t = 0; t < n_live; ++t)
+      if (!(live[t].flags & NZ_ITEM_INPUTS_STABLE)) b.inputs_stable = 0;
     n_live = 0;
     if (gather) {
       switch (precision) {
@@ -1553,6 +1564,7 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   it.gx = nullptr;
   it.partial = nullptr;
   it.in = it.seg = 0;
+  it.flags = 0;
   return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
@@ -1645,6 +1657,7 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
       host[i].gx = nullptr;
       host[i].partial = nullptr;
       host[i].in = host[i].seg = 0;
+      host[i].flags = it.flags;
     }
     int rc = nz::decode_many(host, m, precision, lane_symbols, canonical_nan, true, status,
                              (cudaStream_t)stream);
@@ -1688,6 +1701,7 @@ extern "C" int nz_decompress_bf16_units(const void *container, uint64_t containe
   it.gx = nullptr;
   it.partial = nullptr;
   it.in = it.seg = 0;
+  it.flags = 0;
   return nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                          (cudaStream_t)stream);
 }
@@ -1880,6 +1894,7 @@ extern "C" int nz_linear_vec_bf16(const void *container, uint64_t container_byte
   it.partial = (float *)scratch;
   it.in = (uint32_t)in_features;
   it.seg = nz::dot_segments(in_features, U);
+  it.flags = 0;
   rc = nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                        (cudaStream_t)stream);
   if (rc) return rc;

@@ -453,3 +453,36 @@ def test_batched_decode_can_be_captured_in_a_cuda_graph():
         for o, w in zip(outs, ws):
             assert torch.equal(o.view(torch.int16), w.view(-1).view(torch.int16))
     manager.check()
+
+
+def test_back_to_back_batches_with_stable_inputs_share_buffers_safely():
+    """Launches that were told their inputs are stable build their tables while the previous
+    kernel drains; their stores must still wait for it.  Two batches decode into the same
+    buffers in turn, with a reader of those buffers between them."""
+    manager = neuzip.Manager(precision=7)
+    be = manager._be
+    shapes = [(1024, 1024), (512, 4096), (2048, 768)]
+    sets = []
+    for base in (0, 10):
+        ws = [weights(s, base + i).cuda() for i, s in enumerate(shapes)]
+        sets.append((ws, [manager.write(w) for w in ws]))
+    outs = [torch.empty(int(np.prod(s)), dtype=torch.bfloat16, device="cuda") for s in shapes]
+    batches = [be.make_batch(handles, outs) for _, handles in sets]
+    assert be._fresh_writes                       # the first decode after the writes waits for them
+    expected = [[w.view(-1).float().sum() for w in ws] for ws, _ in sets]
+    sums = []
+    for it in range(40):
+        be.run_batch(batches[it % 2])
+        assert not be._fresh_writes
+        sums.append([o.float().sum() for o in outs])          # a reader between the two writers
+    torch.cuda.synchronize()
+    for it, got in enumerate(sums):
+        for g, e in zip(got, expected[it % 2]):
+            assert float(g) == float(e)
+    # a write in between makes the next launch conservative again
+    manager.write(sets[0][0][0], sets[0][1][0])
+    assert be._fresh_writes
+    be.run_batch(batches[0])
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0].view(torch.int16), sets[0][0][0].view(-1).view(torch.int16))
+    manager.check()
