@@ -165,6 +165,16 @@ def build_stacks(L, torch, layers, precisions, rank):
     staging = torch.empty(cap_max, dtype=torch.uint8, device="cuda")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gen = torch.Generator(device="cuda")
+    # untimed warm-up of the compress pipeline (kernel loading) at every precision
+    warm = torch.zeros(1 << 20, dtype=torch.bfloat16, device="cuda")
+    for s in precisions:
+        S = int(L.nz_default_lane_symbols(s))
+        frac = torch.empty(int(L.nz_frac_bytes(warm.numel(), s)), dtype=torch.uint8, device="cuda")
+        _lib.check(L.nz_compress_bf16(warm.data_ptr(), warm.numel(), s, S, frac.data_ptr(),
+                                      staging.data_ptr(), staging.numel(), scratch.data_ptr(),
+                                      scratch.numel(), st))
+    torch.cuda.synchronize()
+    del warm
     for layer in range(layers):
         for j, shape in enumerate(LAYER_SHAPES):
             gen.manual_seed(1000 + 7 * layer + j + 100000 * rank)
