@@ -311,3 +311,46 @@ def decode_python(container: np.ndarray, n: int) -> np.ndarray:
             assert x == 1 << 16
             p += int(lens[j])
     return out
+
+
+# --------------------------------------------------------------------------
+# The reference's own split / merge kernels (GPU), compiled from the reference
+# tree by `make -C oracle ref` into oracle/_ref/libnz_ref_kernels.so.  The tree is
+# only present where the project is built; the library travels with the built
+# files.  Used by the GPU parity tests to pin this oracle and the product's
+# kernels to reference-run outputs.
+
+_REF_SO = os.path.join(_HERE, "_ref", "libnz_ref_kernels.so")
+REFERENCE_DIR = os.environ.get("NZ_REFERENCE_DIR", "/root/reference")
+REF_GROUPS = (0, 1, 2, 4, 8, 16, 32, 1024)   # 0 = normalized=false; see ref_kernels.cu
+_ref_lib = None
+
+
+def build_ref() -> Optional[str]:
+    """Compile the reference kernels when the reference tree is present; returns the
+    library path, or None when neither the tree nor a built library exists."""
+    kernels = os.path.join(REFERENCE_DIR, "cuda", "kernels.cuh")
+    if os.path.exists(kernels):
+        harness = os.path.join(_HERE, "ref_kernels.cu")
+        stale = (not os.path.exists(_REF_SO)
+                 or os.path.getmtime(_REF_SO) < max(os.path.getmtime(harness),
+                                                    os.path.getmtime(kernels)))
+        if stale:
+            subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_DIR={REFERENCE_DIR}"],
+                           check=True, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    return _REF_SO if os.path.exists(_REF_SO) else None
+
+
+def ref_lib() -> Optional[ctypes.CDLL]:
+    """The reference-kernel library (needs `import torch` first: it links libc10),
+    or None when it has not been built."""
+    global _ref_lib
+    if _ref_lib is None and os.path.exists(_REF_SO):
+        import torch  # noqa: F401  (loads libc10 / libtorch the harness links against)
+        L = ctypes.CDLL(_REF_SO)
+        vp = ctypes.c_void_p
+        for fn in (L.nzref_split, L.nzref_merge):
+            fn.argtypes = [ctypes.c_int, ctypes.c_int, vp, vp, vp, vp, ctypes.c_size_t, vp]
+            fn.restype = ctypes.c_int
+        _ref_lib = L
+    return _ref_lib
