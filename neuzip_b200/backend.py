@@ -42,6 +42,36 @@ class _Entry:
     container: torch.Tensor   # uint8, right-sized NZR1 container
     fractions: torch.Tensor   # uint8, packed sign+mantissa stream
     normalizers: Optional[torch.Tensor] = None   # uint8, one byte per group (normalizer_size > 0)
+    stamp: int = 0            # number of the library operation that wrote these bytes
+
+
+# Every operation that any backend of this process enqueues gets a number.  A decode
+# may promise NZ_ITEM_INPUTS_STABLE for an entry only when some other operation was
+# enqueued between the entry's write and the decode: then the write is not "the work
+# enqueued just before the call", whichever Manager or handle it went through.
+_op_counter = 0
+
+
+def _next_op() -> int:
+    global _op_counter
+    _op_counter += 1
+    return _op_counter
+
+
+def _stable_flag(entries, op: int) -> int:
+    return _lib.NZ_ITEM_INPUTS_STABLE if all(e.stamp < op - 1 for e in entries) else 0
+
+
+class _Batch:
+    """Argument blocks of a batched decode, rebuilt when an entry is replaced."""
+    __slots__ = ("names", "outs", "entries", "blocks", "lane_symbols")
+
+    def __init__(self, names, outs) -> None:
+        self.names = list(names)
+        self.outs = list(outs)
+        self.entries = []
+        self.blocks = None
+        self.lane_symbols = 0
 
 
 def _ptr(t: Optional[torch.Tensor]) -> int:
@@ -96,9 +126,6 @@ class CodecBackend:
         self._vec_ver = -1
         self._vec_x: Optional[torch.Tensor] = None
         self._vec_scratch: Dict[tuple, torch.Tensor] = {}
-        # True while the last thing this backend enqueued wrote compressed bytes: the
-        # next decode launch must then wait for it before it reads them
-        self._fresh_writes = True
 
     # -- helpers ---------------------------------------------------------
     def _ensure_device(self) -> None:
@@ -155,8 +182,7 @@ class CodecBackend:
         _lib.check(L.nz_container_bytes(_ptr(staging), total, max_words, st))
         container = staging[: total.value].clone()
         self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac,
-                                   normalizers)
-        self._fresh_writes = True
+                                   normalizers, _next_op())
 
     def read(self, name: str) -> torch.Tensor:
         """cuda/high_level.cu:223-250 (+ _decompress_and_merge :164-206); no host sync."""
@@ -169,6 +195,7 @@ class CodecBackend:
 
     def read_into(self, name: str, out: torch.Tensor) -> None:
         entry = self._cache[name]
+        _next_op()
         _lib.check(self._lib.nz_decompress_bf16(
             _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
             self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
@@ -234,6 +261,7 @@ class CodecBackend:
             by_s.setdefault(e.lane_symbols, []).append(i)
         for S, idx in by_s.items():
             items = (_lib.DecompressItem * len(idx))()
+            flags = _stable_flag([entries[i] for i in idx], _next_op())
             for k, i in enumerate(idx):
                 e = entries[i]
                 items[k].container = _ptr(e.container)
@@ -241,22 +269,28 @@ class CodecBackend:
                 items[k].frac_in = _ptr(e.fractions)
                 items[k].n = e.numel
                 items[k].max_unit_words = e.max_unit_words
-                items[k].flags = 0 if self._fresh_writes else _lib.NZ_ITEM_INPUTS_STABLE
+                items[k].flags = flags
                 items[k].out_bf16 = _ptr(outs[i])
             _lib.check(self._lib.nz_decompress_bf16_batch(
                 items, len(idx), self.precision, S, int(self.canonical_nan), _ptr(self._status),
                 _stream()))
-            self._fresh_writes = False
         for e, out in zip(entries, outs):
             self._denormalize(e, out)
         return outs
 
-    def make_batch(self, names: Sequence[str], outs: Sequence[torch.Tensor]):
+    def make_batch(self, names: Sequence[str], outs: Sequence[torch.Tensor]) -> _Batch:
         """Pre-build the argument block of a batched decode of `names` into the given
         flat bf16 output tensors; returns an object for `run_batch`.  Lets a caller that
         decodes the same tensors again and again (every forward of a layer) skip all
-        per-call Python work."""
-        entries = [self._cache[n] for n in names]
+        per-call Python work.  The batch follows the handles, not the bytes: when a
+        handle is written again (an optimiser step, a loaded checkpoint) the next
+        `run_batch` picks up the new container."""
+        batch = _Batch(names, outs)
+        self._bind_batch(batch)
+        return batch
+
+    def _bind_batch(self, batch: _Batch) -> None:
+        entries = [self._cache[n] for n in batch.names]
         S = {e.lane_symbols for e in entries}
         if len(S) != 1:
             raise ValueError("a batch must share one lane_symbols value")
@@ -264,7 +298,7 @@ class CodecBackend:
         blocks = []
         for flags in (0, _lib.NZ_ITEM_INPUTS_STABLE):
             items = (_lib.DecompressItem * len(entries))()
-            for k, (e, out) in enumerate(zip(entries, outs)):
+            for k, (e, out) in enumerate(zip(entries, batch.outs)):
                 if out.numel() < e.numel or out.dtype != torch.bfloat16 or not out.is_cuda:
                     raise ValueError(
                         "output buffers must be CUDA bf16 tensors of at least numel elements")
@@ -276,21 +310,23 @@ class CodecBackend:
                 items[k].flags = flags
                 items[k].out_bf16 = _ptr(out)
             blocks.append(items)
-        # keep the tensors alive as long as the batch exists
-        return (blocks, len(entries), S.pop(), [e.container for e in entries],
-                [e.fractions for e in entries], list(outs), entries)
+        # the entries keep their tensors alive as long as the batch refers to them
+        batch.entries, batch.blocks, batch.lane_symbols = entries, blocks, S.pop()
 
-    def run_batch(self, batch) -> None:
-        blocks, count, S = batch[0], batch[1], batch[2]
-        items = blocks[0] if self._fresh_writes else blocks[1]
-        self._fresh_writes = False
-        rc = self._lib.nz_decompress_bf16_batch(items, count, self.precision, S,
-                                                int(self.canonical_nan), _ptr(self._status),
-                                                _stream())
+    def run_batch(self, batch: _Batch) -> None:
+        cache = self._cache
+        for name, entry in zip(batch.names, batch.entries):
+            if cache.get(name) is not entry:       # written, imported or erased since
+                self._bind_batch(batch)
+                break
+        items = batch.blocks[1 if _stable_flag(batch.entries, _next_op()) else 0]
+        rc = self._lib.nz_decompress_bf16_batch(items, len(batch.names), self.precision,
+                                                batch.lane_symbols, int(self.canonical_nan),
+                                                _ptr(self._status), _stream())
         if rc:
             _lib.check(rc)
         if self.normalizer_size:
-            for e, out in zip(batch[6], batch[5]):
+            for e, out in zip(batch.entries, batch.outs):
                 self._denormalize(e, out)
 
     def size(self, name: str) -> int:
@@ -400,8 +436,8 @@ class CodecBackend:
         if normalizers is not None:
             normalizers = normalizers.to(device="cuda", dtype=torch.uint8).contiguous()
         self._cache[name] = _Entry(n, torch.bfloat16, int(blob["lane_symbols"]),
-                                   int(blob["max_unit_words"]), container, fractions, normalizers)
-        self._fresh_writes = True
+                                   int(blob["max_unit_words"]), container, fractions, normalizers,
+                                   _next_op())
 
     # -- extras -----------------------------------------------------------
     def erase(self, name: str) -> None:

@@ -23,6 +23,8 @@ constexpr uint32_t kFreqOffset = 64;
 constexpr uint32_t kOffsetsOffset = 576;
 constexpr uint32_t kRawFlag = 0x80000000u;
 constexpr uint32_t kMaxLaneSymbols = 1024;
+constexpr uint32_t kMaxDynamicSmem = 227u * 1024u;   // dynamic shared memory a CTA can opt in to
+constexpr int kMaxDeviceOrdinals = 64;               // per-device bookkeeping tables
 
 // Container header; must match struct nzo_header of the specification.
 struct Header {

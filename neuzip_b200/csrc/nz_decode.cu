@@ -32,6 +32,7 @@
 // pointers), output and fraction addresses never depend on coded data, and
 // the wait on the bulk copy is bounded.
 #include <string.h>
+#include <mutex>
 #include <type_traits>
 
 #include "nz_common.cuh"
@@ -1211,6 +1212,10 @@ decode_kernel(const BatchArgs batch) {
   if (pb < kMinProbBits || pb > kMaxProbBits || cum_sh[256] != (1u << (pb & 15)) || *wide_sh)
     bad |= NZ_STATUS_BAD_HEADER;
   if (bad) {
+    // Every exit path orders itself behind the previous kernel of the stream first: the
+    // status word is shared with it, and a kernel that retired without waiting would let
+    // the next programmatically serialised launch overtake that kernel's reads.
+    if (early) asm volatile("griddepcontrol.wait;" ::: "memory");
     // copies may be in flight into this warp's slots: let them land before leaving
     if (staged) wait_staged(bar, parity);
     if (threadIdx.x == 0 && cta_rank == 0) raise(a.status, bad);
@@ -1441,15 +1446,20 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, ui
 template <int S, bool MERGE, int MODE = kModeTensor>
 static int launch_decode(const BatchArgs &b, uint32_t warps, uint32_t smem_bytes, cudaStream_t st) {
   auto kern = decode_kernel<S, MERGE, MODE>;
-  // the opt-in to large dynamic shared memory is per kernel and device: set it when a
-  // launch needs more than any earlier one on this device did
-  static uint32_t opted[64] = {};
-  int dev = 0;
-  NZ_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || opted[dev] < smem_bytes) {
-    NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem_bytes));
-    if (dev >= 0 && dev < 64) opted[dev] = smem_bytes;
+  // The opt-in to large dynamic shared memory is per kernel and device.  It is made once
+  // per (instantiation, device), for the most a CTA can have, under a lock: concurrent
+  // callers can then never leave the attribute below what a launch needs.
+  {
+    static std::mutex mu;
+    static bool opted[kMaxDeviceOrdinals] = {};
+    int dev = 0;
+    NZ_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= kMaxDeviceOrdinals || !opted[dev]) {
+      NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kMaxDynamicSmem));
+      if (dev >= 0 && dev < kMaxDeviceOrdinals) opted[dev] = true;
+    }
   }
   // Programmatic stream serialisation: this launch may begin while the previous
   // kernel of the stream drains; the kernel itself waits (griddepcontrol.wait)

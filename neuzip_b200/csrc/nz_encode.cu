@@ -566,8 +566,20 @@ int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container
   if (nu) {
     const uint32_t cell_bytes = ((16 + 32 * lane_cap_words(S) + 7) & ~7u) * 2;
     const uint32_t cmp_smem_bytes = kCompactWarps * cell_bytes;
-    NZ_CUDA_TRY(cudaFuncSetAttribute(compact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)cmp_smem_bytes));
+    {
+      // once per device, under a lock, for the most a CTA can have
+      static std::mutex mu;
+      static bool opted[kMaxDeviceOrdinals] = {};
+      int dev = 0;
+      NZ_CUDA_TRY(cudaGetDevice(&dev));
+      std::lock_guard<std::mutex> lock(mu);
+      if (dev < 0 || dev >= kMaxDeviceOrdinals || !opted[dev]) {
+        NZ_CUDA_TRY(cudaFuncSetAttribute(compact_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kMaxDynamicSmem));
+        if (dev >= 0 && dev < kMaxDeviceOrdinals) opted[dev] = true;
+      }
+    }
     uint32_t blocks = (nu + kCompactWarps - 1) / kCompactWarps;
     const uint32_t capb = (uint32_t)sm_count() * 16;
     if (blocks > capb) blocks = capb;

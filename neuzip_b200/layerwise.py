@@ -25,10 +25,23 @@ def _compressed_linears(module: torch.nn.Module) -> List[Linear]:
 
 
 def default_block_filter(module: torch.nn.Module) -> bool:
-    """A block = a module whose class name ends in 'DecoderLayer' / 'Block' /
-    'EncoderLayer' and that contains compressed Linears."""
-    name = type(module).__name__
-    return name.endswith(("DecoderLayer", "Block", "EncoderLayer")) and bool(_compressed_linears(module))
+    """A block = an element of a ``torch.nn.ModuleList`` that contains compressed
+    Linears (how transformer implementations hold their layers); attach() marks those.
+    Modules whose class name ends in 'DecoderLayer' / 'Block' / 'EncoderLayer' count
+    too, for models that keep their layers elsewhere."""
+    if not _compressed_linears(module):
+        return False
+    if getattr(module, "_nz_in_module_list", False):
+        return True
+    return type(module).__name__.endswith(("DecoderLayer", "Block", "EncoderLayer"))
+
+
+def _mark_module_list_children(model: torch.nn.Module) -> None:
+    for m in model.modules():
+        if isinstance(m, torch.nn.ModuleList):
+            for child in m:
+                # outermost list wins: children of a marked block are not blocks themselves
+                child._nz_in_module_list = True
 
 
 class _Stage:
@@ -58,7 +71,12 @@ def attach(model: torch.nn.Module, manager,
     backend = manager._be
     if fuse_single_token:
         manager.fuse_vector_linear(True)
-    blocks = [m for m in model.modules() if is_block(m)]
+    _mark_module_list_children(model)
+    blocks = []
+    for m in model.modules():
+        # a block inside a block (nested lists) is decoded with its parent
+        if is_block(m) and not any(m is not b and any(m is c for c in b.modules()) for b in blocks):
+            blocks.append(m)
     # shared decode buffers: slot k is as large as the k-th Linear of the largest block
     sizes: List[int] = []
     for block in blocks:
@@ -69,7 +87,8 @@ def attach(model: torch.nn.Module, manager,
             else:
                 sizes[k] = max(sizes[k], n)
     batched = hasattr(backend, "make_batch")
-    buffers = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for n in sizes] if batched else []
+    device = next((lin._p.device for b in blocks for lin in _compressed_linears(b)), "cuda")
+    buffers = [torch.empty(n, dtype=torch.bfloat16, device=device) for n in sizes] if batched else []
     stage = _Stage()
     handles = []
     for number, block in enumerate(blocks):

@@ -11,9 +11,17 @@ data-parallel replicas drift apart; here the all-reduce is started from a
 post-accumulate-grad hook as soon as a layer's backward has produced the
 gradient, and `step()` waits for it.  Replicas stay bit-identical because the
 codec is deterministic.
+
+Gradient accumulation: every backward's contribution is taken out of `_gradient`
+and reduced as a tensor of its own, so a later micro-batch never adds to a tensor
+that NCCL is still summing; `step()` adds the reduced pieces.  Inside
+`with optimizer.no_sync():` nothing is reduced and micro-batches accumulate locally
+(as with DistributedDataParallel.no_sync), to be reduced once by the first backward
+outside the context, or by `step()`.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Dict, Iterable, List
 
 import torch
@@ -41,7 +49,8 @@ class CompressedAdamW:
         from . import _lib
         self._lib_mod = _lib
         self._lib = _lib.load()
-        self._pending: Dict[int, object] = {}
+        self._pending: Dict[int, list] = {}     # id(p) -> [(tensor being reduced, work)]
+        self._sync = True
         self._hooks = []
         if self.world > 1 and overlap_allreduce:
             for p in self.compressed:
@@ -49,11 +58,37 @@ class CompressedAdamW:
 
     # gradient of a compressed weight is ready: start summing it over the ranks
     def _start_allreduce(self, p: Parameter) -> None:
-        if p._gradient is not None and id(p) not in self._pending:
-            self._pending[id(p)] = dist.all_reduce(p._gradient, group=self.group, async_op=True)
+        if not self._sync or p._gradient is None:
+            return
+        piece, p._gradient = p._gradient, None     # later backwards start a fresh tensor
+        work = dist.all_reduce(piece, group=self.group, async_op=True)
+        self._pending.setdefault(id(p), []).append((piece, work))
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backwards inside this context accumulate their weight gradients locally
+        without starting an all-reduce (all micro-batches of a step but the last)."""
+        previous, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = previous
+
+    def _reduced_gradient(self, p: Parameter):
+        """Sum over ranks and micro-batches of the weight gradient of `p` (not yet
+        divided by the world size), or None when there is none."""
+        total = p._gradient
+        if total is not None and self.world > 1:
+            dist.all_reduce(total, group=self.group)        # accumulated but never reduced
+        for piece, work in self._pending.pop(id(p), []):
+            work.wait()
+            total = piece if total is None else total.add_(piece)
+        return total
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         for p in self.compressed:
+            for _, work in self._pending.pop(id(p), []):
+                work.wait()
             p._gradient = None
             p.grad = None
         if self.plain is not None:
@@ -71,15 +106,9 @@ class CompressedAdamW:
                         q.grad.div_(self.world)
         stream = torch.cuda.current_stream().cuda_stream
         for p in self.compressed:
-            g = p._gradient
+            g = self._reduced_gradient(p)
             if g is None:
                 continue
-            if self.world > 1:
-                work = self._pending.pop(id(p), None)
-                if work is None:
-                    dist.all_reduce(g, group=self.group)
-                else:
-                    work.wait()
             g = g.contiguous()
             if g.dtype != torch.bfloat16:
                 g = g.to(torch.bfloat16)

@@ -467,13 +467,18 @@ def test_back_to_back_batches_with_stable_inputs_share_buffers_safely():
         ws = [weights(s, base + i).cuda() for i, s in enumerate(shapes)]
         sets.append((ws, [manager.write(w) for w in ws]))
     outs = [torch.empty(int(np.prod(s)), dtype=torch.bfloat16, device="cuda") for s in shapes]
+    from neuzip_b200 import backend as B
+    from neuzip_b200 import _lib
     batches = [be.make_batch(handles, outs) for _, handles in sets]
-    assert be._fresh_writes                       # the first decode after the writes waits for them
+    # the first decode after the writes waits for them: the last write is the operation
+    # enqueued just before it
+    assert B._stable_flag(batches[1].entries, B._op_counter + 1) == 0
     expected = [[w.view(-1).float().sum() for w in ws] for ws, _ in sets]
     sums = []
     for it in range(40):
         be.run_batch(batches[it % 2])
-        assert not be._fresh_writes
+        assert B._stable_flag(batches[0].entries + batches[1].entries, B._op_counter + 1) == \
+            _lib.NZ_ITEM_INPUTS_STABLE
         sums.append([o.float().sum() for o in outs])          # a reader between the two writers
     torch.cuda.synchronize()
     for it, got in enumerate(sums):
@@ -481,8 +486,81 @@ def test_back_to_back_batches_with_stable_inputs_share_buffers_safely():
             assert float(g) == float(e)
     # a write in between makes the next launch conservative again
     manager.write(sets[0][0][0], sets[0][1][0])
-    assert be._fresh_writes
+    assert B._stable_flag([be.entry(sets[0][1][0])], B._op_counter + 1) == 0
     be.run_batch(batches[0])
     torch.cuda.synchronize()
     assert torch.equal(outs[0].view(torch.int16), sets[0][0][0].view(-1).view(torch.int16))
     manager.check()
+
+
+def test_stable_input_promise_is_tracked_per_entry_across_managers():
+    """A container written through a second Manager just before a batched decode of
+    another Manager's handles must not be promised as stable, and a batch follows a
+    handle that is written again (new bytes, not the ones it was built with)."""
+    from neuzip_b200 import backend as B
+    from neuzip_b200 import _lib
+    m1, m2 = neuzip.Manager(precision=7), neuzip.Manager(precision=7)
+    w1, w2 = weights((512, 1024), 1).cuda(), weights((512, 1024), 2).cuda()
+    h1 = m1.write(w1)
+    out = torch.empty(w1.numel(), dtype=torch.bfloat16, device="cuda")
+    batch = m1._be.make_batch([h1], [out])
+    for _ in range(3):
+        m1._be.run_batch(batch)
+    e1 = m1._be.entry(h1)
+    assert B._stable_flag([e1], B._op_counter + 1) == _lib.NZ_ITEM_INPUTS_STABLE
+    h2 = m2.write(w2)                              # another Manager, same stream
+    e2 = m2._be.entry(h2)
+    assert B._stable_flag([e2], B._op_counter + 1) == 0
+    assert B._stable_flag([e1], B._op_counter + 1) == _lib.NZ_ITEM_INPUTS_STABLE
+    got = m2.read_many([h2])[0]
+    assert torch.equal(got.view(torch.int16), w2.view(torch.int16))
+    # the same handle written again: the batch must decode the new bytes
+    m1.write(w2, h1)
+    m1._be.run_batch(batch)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), w2.view(-1).view(torch.int16))
+    m1.check()
+    m2.check()
+
+
+def test_layerwise_hooks_follow_weight_updates_and_loaded_checkpoints():
+    """After an optimiser step (every weight is written again) and after
+    load_state_dict, a model with the layer-wise hooks attached must compute with the new
+    weights, exactly like the same model without hooks."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from neuzip_b200 import layerwise
+    from neuzip_b200.optim import CompressedAdamW
+    torch.manual_seed(3)
+    cfg = LlamaConfig(vocab_size=128, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=64)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).cuda()
+    m = neuzip.Manager(precision=7)
+    m.convert(model)
+    before = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in model.state_dict().items()}
+    ids = torch.randint(0, 128, (2, 16), device="cuda")
+    hooks = layerwise.attach(model, m)
+    opt = CompressedAdamW(model.parameters(), lr=1e-2)
+    loss = model(ids, labels=ids).loss
+    loss.backward()
+    opt.step()
+    opt.zero_grad()
+    with torch.no_grad():
+        hooked = model(ids).logits.float()
+    for h in hooks:
+        h.remove()
+    with torch.no_grad():
+        plain = model(ids).logits.float()
+    assert torch.equal(hooked, plain)
+    # load the earlier checkpoint with the hooks attached
+    hooks = layerwise.attach(model, m)
+    with torch.no_grad():
+        model(ids)
+    model.load_state_dict(before)
+    with torch.no_grad():
+        hooked = model(ids).logits.float()
+    for h in hooks:
+        h.remove()
+    with torch.no_grad():
+        plain = model(ids).logits.float()
+    assert torch.equal(hooked, plain)
+    m.check()

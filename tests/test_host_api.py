@@ -276,3 +276,36 @@ def test_layerwise_hooks_stage_one_block_at_a_time_on_cpu():
         h.remove()
     with torch.no_grad():
         assert torch.equal(model(x), ref)
+
+
+def test_layerwise_hooks_follow_writes_and_loaded_state_on_cpu():
+    """A handle that is written again after attach() (an optimiser step, a loaded
+    checkpoint) must be decoded from its new bytes by the block's batched decode."""
+    from neuzip_b200 import layerwise
+    torch.manual_seed(1)
+    model = TwoBlocks().to(torch.bfloat16)
+    m = cpu_manager()
+    m.convert(model)
+    x = torch.randn(3, 16).to(torch.bfloat16)
+    saved = {k: v for k, v in model.state_dict().items()}
+    hooks = layerwise.attach(model, m)
+    with torch.no_grad():
+        first = model(x)
+    # in-backward style update of every compressed weight: read -> change -> write
+    for blk in model.blocks:
+        for lin in (blk.a, blk.b):
+            w = lin._p()
+            m.write((w.float() * 1.5).to(torch.bfloat16), lin._p._handle)
+    with torch.no_grad():
+        hooked = model(x)
+    for h in hooks:
+        h.remove()
+    with torch.no_grad():
+        plain = model(x)
+    assert torch.equal(hooked, plain) and not torch.equal(hooked, first)
+    hooks = layerwise.attach(model, m)
+    model.load_state_dict(saved)
+    with torch.no_grad():
+        assert torch.equal(model(x), first)
+    for h in hooks:
+        h.remove()
