@@ -5,17 +5,24 @@
  * the shipped package may call it; only the test-suite, the smoke check and the
  * CPU-baseline leg of the benchmark load it.
  *
- * PARITY STATUS: "parity unpinned".  The reference ships no tests, no golden
- * vectors and no CPU path, and its entropy stage is the closed-source nvcomp
- * library, so there is nothing reference-run to pin against.  What pins this
- * file instead:
+ * PARITY STATUS: pinned to reference-run split / merge.  The reference ships no
+ * tests, no golden vectors and no CPU path, and its entropy stage is the
+ * closed-source nvcomp library; but its two kernels, kernel_aligned_split and
+ * kernel_aligned_merge (cuda/kernels.cuh:53-217), compile from the reference
+ * tree without nvcomp (oracle/ref_kernels.cu, `make -C oracle ref`) and were run
+ * on a B200.  What pins this file:
+ *   - the GPU tests (tests/test_gpu_reference_pin.py) require nzo_split_literal(),
+ *     nzo_split(), nzo_merge() with NaN canonicalisation and, for the group
+ *     sizes whose reduction is well defined in the reference (1..32 and 1024),
+ *     nzo_normalize_groups() / nzo_denormalize_groups() to equal the reference
+ *     kernels' outputs bit for bit on all 65 536 bf16 patterns, on the seed-0
+ *     4096x4096 matrix and on seeded weights;
+ *   - CRC-32s of those reference-run outputs are committed
+ *     (tests/golden/reference_pin.json) and checked on the CPU too;
  *   - nzo_split_literal() follows cuda/kernels.cuh:120-155 one statement at a
- *     time (including the 8-bit truncations of the C types used there), and
- *     nzo_split() is the closed form of the same arithmetic; the tests compare
- *     the two on all 65 536 bf16 bit patterns for every precision;
- *   - nzo_merge() follows cuda/kernels.cuh:197-216;
- *   - CRC-32 values of both streams on the seed-0 4096x4096 matrix, derived
- *     independently from the same reference lines, are committed as fixtures.
+ *     time (including the 8-bit truncations of the C types used there),
+ *     nzo_split() is the closed form of the same arithmetic, nzo_merge()
+ *     follows cuda/kernels.cuh:197-216.
  *
  * The entropy stage (cuda/high_level.cu:103-115 compress, :184-192 decompress
  * call nvcomp's ANS manager) has no observable byte format in the reference:

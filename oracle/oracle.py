@@ -2,8 +2,8 @@
 
 Only the test-suite, the smoke check and the CPU-baseline leg of the benchmark
 may import this module; the shipped package never does.  See the header of
-``nz_oracle.c`` for the parity status ("parity unpinned": the reference has no
-CPU path, no tests and no golden vectors) and for the container specification.
+``nz_oracle.c`` for the parity status (pinned to outputs of the reference's own
+split / merge kernels run on a B200) and for the container specification.
 
 Every function takes and returns numpy arrays; bf16 tensors travel as their
 uint16 bit patterns.

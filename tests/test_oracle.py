@@ -234,3 +234,31 @@ def test_hypothesis_roundtrip():
         assert np.array_equal(O.decode(O.encode(sym, S), sym.size), sym)
 
     run()
+
+
+def test_oracle_reproduces_the_reference_run_fixture():
+    """tests/golden/reference_pin.json holds CRC-32s of what the reference's own
+    kernel_aligned_split / kernel_aligned_merge produced on a B200 (generated by
+    tests/golden/make_reference_pin.py from oracle/_ref).  The CPU oracle must give the
+    same streams and the same merged tensors, NaN canonicalisation included."""
+    import json
+    import os
+    import torch
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_pin.json")
+    with open(path) as f:
+        pin = json.load(f)
+    torch.manual_seed(0)
+    w = (torch.randn(4096, 4096, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    cases = {"precision": w.view(torch.int16).numpy().view(np.uint16).reshape(-1),
+             "all_patterns": np.arange(65536, dtype=np.uint16)}
+    assert hex(O.crc32(cases["precision"])) == pin["input_crc32"]
+    for key, bits in cases.items():
+        for s in (0, 1, 3, 7):
+            want = pin[key][str(s)]
+            e, f = O.split(bits, s)
+            assert hex(O.crc32(e)) == want["exp_crc32"], (key, s)
+            assert hex(O.crc32(f)) == want["frac_crc32"], (key, s)
+            rt = O.merge(e, f, s, canonical_nan=True)
+            assert hex(O.crc32(rt)) == want["roundtrip_crc32"], (key, s)
+            if "roundtrip_identical_patterns" in want:
+                assert int((rt == bits).sum()) == want["roundtrip_identical_patterns"]
