@@ -220,6 +220,9 @@ typedef struct nz_decompress_item {
   uint32_t max_unit_words;   /* from nz_container_bytes, 0 = worst case    */
   uint32_t flags;            /* NZ_ITEM_* bits, 0 = none                   */
   void *out_bf16;            /* bf16[n], 16-byte aligned                   */
+  uint64_t operand_cols;     /* 0, or the row length of a matrix stored in
+                                operand order (nz_compress_bf16_operand);
+                                the output is row-major either way          */
 } nz_decompress_item;
 
 /* nz_decompress_bf16 for several tensors of the same precision and
@@ -285,6 +288,63 @@ int nz_linear_vec_bf16(const void *container, uint64_t container_bytes,
                        int canonical_nan, uint64_t in_features, const void *x_f32,
                        const void *bias_bf16, void *y_bf16, void *scratch,
                        uint64_t scratch_bytes, void *status, void *stream);
+
+/* ---- operand order and the fused linear ----------------------------------- */
+
+/* A [rows, cols] weight matrix can be stored in "operand order": the codec is
+ * applied to a permutation of the matrix in which every 256-element block of
+ * the stream is a 4-row x 64-column patch (stream element
+ * ((g * cols/64 + kb) * 4 + r) * 64 + c  is matrix element (4g + r, 64kb + c)),
+ * so that what the decoder produces per step is a piece of a tensor-core
+ * operand tile.  Requirements: rows % 4 == 0, cols % 64 == 0 and lane_symbols / 8
+ * divides cols / 64 (a unit never straddles a row group).  The stored bytes are
+ * what nz_compress_bf16 produces for the permuted tensor; the reference never
+ * exposes its stored bytes (cuda/high_level.cu:35-43), only what write / read
+ * return, which is unchanged. */
+
+/* lane_symbols to use for a matrix with `cols` columns at `precision`: the
+ * admissible value closest to nz_default_lane_symbols, or 0 when the matrix
+ * cannot be stored in operand order. */
+uint32_t nz_operand_lane_symbols(uint64_t cols, int precision);
+
+/* nz_compress_bf16 for a row-major [rows, cols] matrix, stored in operand order.
+ * Scratch of nz_compress_operand_scratch_bytes bytes.
+ * Reference: Manager::_write_to_cache, cuda/high_level.cu:71-130. */
+uint64_t nz_compress_operand_scratch_bytes(uint64_t rows, uint64_t cols, uint32_t lane_symbols);
+int nz_compress_bf16_operand(const void *in_bf16, uint64_t rows, uint64_t cols, int precision,
+                             uint32_t lane_symbols, void *frac_out, void *container,
+                             uint64_t container_cap, void *scratch, uint64_t scratch_bytes,
+                             void *stream);
+
+/* nz_decompress_bf16 for a matrix stored in operand order; out_bf16 receives the
+ * row-major [rows, cols] matrix.
+ * Reference: Manager::_decompress_and_merge, cuda/high_level.cu:164-206. */
+int nz_decompress_bf16_operand(const void *container, uint64_t container_bytes,
+                               const void *frac_in, uint64_t rows, uint64_t cols, int precision,
+                               uint32_t lane_symbols, uint32_t max_unit_words, int canonical_nan,
+                               void *out_bf16, void *status, void *stream);
+
+/* y[m_tokens, rows] = x[m_tokens, cols] * W^T (+ bias) for a weight W[rows, cols]
+ * stored in operand order: the decoder writes the bf16 weight tiles into shared
+ * memory in the tensor cores' operand layout and tcgen05.mma consumes them there
+ * (fp32 accumulation in tensor memory, one rounding to bf16 at the end), so the
+ * decoded weight never travels through global memory.  x and y are row-major
+ * bf16 (x 16-byte aligned), bias is bf16[rows] or NULL.  When a row of W spans
+ * several units (cols / 64 > lane_symbols / 8) each column segment is summed on
+ * its own into `workspace` (nz_linear_workspace_bytes, 16-byte aligned, fp32) and
+ * a second kernel adds the segments in a fixed order, so results are
+ * reproducible run to run.  Inputs of more than 256 rows are processed 256 at a
+ * time, decoding the weight once per pass.  No host sync.  Faults found while
+ * decoding are reported in `status` as for nz_decompress_bf16.
+ * Reference: Manager::linear / linear_without_bias = full decompress into a new
+ * tensor, then a library GEMM (cuda/high_level.cu:252-263). */
+uint64_t nz_linear_workspace_bytes(uint64_t rows, uint64_t cols, uint32_t lane_symbols,
+                                   uint64_t m_tokens);
+int nz_linear_bf16(const void *container, uint64_t container_bytes, const void *frac_in,
+                   uint64_t rows, uint64_t cols, int precision, uint32_t lane_symbols,
+                   uint32_t max_unit_words, int canonical_nan, const void *x_bf16,
+                   uint64_t m_tokens, const void *bias_bf16, void *y_bf16, void *workspace,
+                   uint64_t workspace_bytes, void *status, void *stream);
 
 #ifdef __cplusplus
 }

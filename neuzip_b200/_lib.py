@@ -58,7 +58,8 @@ SIGNATURES = {
 class DecompressItem(ctypes.Structure):
     """struct nz_decompress_item"""
     _fields_ = [("container", _vp), ("container_bytes", _u64), ("frac_in", _vp), ("n", _u64),
-                ("max_unit_words", _u32), ("flags", _u32), ("out_bf16", _vp)]
+                ("max_unit_words", _u32), ("flags", _u32), ("out_bf16", _vp),
+                ("operand_cols", _u64)]
 
 
 _f32 = ctypes.c_float
@@ -74,6 +75,17 @@ SIGNATURES["nz_linear_vec_bf16"] = (
     _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp])
 SIGNATURES["nz_decompress_bf16_batch"] = (
     _int, [ctypes.POINTER(DecompressItem), _u32, _int, _u32, _int, _vp, _vp])
+
+SIGNATURES["nz_operand_lane_symbols"] = (_u32, [_u64, _int])
+SIGNATURES["nz_compress_operand_scratch_bytes"] = (_u64, [_u64, _u64, _u32])
+SIGNATURES["nz_compress_bf16_operand"] = (
+    _int, [_vp, _u64, _u64, _int, _u32, _vp, _vp, _u64, _vp, _u64, _vp])
+SIGNATURES["nz_decompress_bf16_operand"] = (
+    _int, [_vp, _u64, _vp, _u64, _u64, _int, _u32, _u32, _int, _vp, _vp, _vp])
+SIGNATURES["nz_linear_workspace_bytes"] = (_u64, [_u64, _u64, _u32, _u64])
+SIGNATURES["nz_linear_bf16"] = (
+    _int, [_vp, _u64, _vp, _u64, _u64, _int, _u32, _u32, _int, _vp, _u64, _vp, _vp, _vp, _u64, _vp,
+           _vp])
 
 _lock = threading.Lock()
 _lib = None

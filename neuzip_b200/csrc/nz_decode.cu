@@ -1107,6 +1107,22 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
+// A [rows, cols] matrix stored in operand order, decoded to row-major.
+int decode_operand(const void *container, uint64_t container_bytes, const void *frac, uint64_t rows,
+                   uint64_t cols, int precision, uint32_t S, uint32_t max_unit_words, int canon,
+                   void *out_bf16, void *status, cudaStream_t st) {
+  HostItem it;
+  memset(&it, 0, sizeof(it));
+  it.container = container;
+  it.container_bytes = container_bytes;
+  it.frac = frac;
+  it.n = rows * cols;
+  it.max_unit_words = max_unit_words;
+  it.out_bf16 = out_bf16;
+  it.tile_cols = (uint32_t)cols;
+  return decode_many(&it, 1, precision, S, canon, true, status, st);
+}
+
 }  // namespace nz
 
 static int check_decode_args(const char *who, const void *container, uint64_t n, uint32_t S) {
@@ -1198,6 +1214,16 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
       host[i].in = host[i].seg = 0;
       host[i].flags = it.flags;
       host[i].tile_cols = 0;
+      if (it.operand_cols) {
+        const uint64_t c = it.operand_cols;
+        if (c % 64 || it.n % (4 * c) || (c / 64) % (lane_symbols / 8) || c >= (1ull << 31)) {
+          nz::set_error("nz_decompress_bf16_batch: item %u: %llu elements in rows of %llu are not "
+                        "in operand order for lane_symbols %u", base + i,
+                        (unsigned long long)it.n, (unsigned long long)c, lane_symbols);
+          return NZ_E_ARG;
+        }
+        host[i].tile_cols = (uint32_t)c;
+      }
     }
     int rc = nz::decode_many(host, m, precision, lane_symbols, canonical_nan, true, status,
                              (cudaStream_t)stream);

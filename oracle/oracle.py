@@ -354,3 +354,39 @@ def ref_lib() -> Optional[ctypes.CDLL]:
             fn.restype = ctypes.c_int
         _ref_lib = L
     return _ref_lib
+
+
+# --------------------------------------------------------------------------
+# Operand order: a [rows, cols] matrix whose stream blocks of 256 elements are
+# 4-row x 64-column patches (stream element ((g*cols/64 + kb)*4 + r)*64 + c is matrix
+# element (4g + r, 64kb + c)).  The codec is applied to the permuted tensor.
+
+def to_operand_order(bits: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    assert rows % 4 == 0 and cols % 64 == 0 and bits.size == rows * cols
+    return np.ascontiguousarray(
+        bits.reshape(rows // 4, 4, cols // 64, 64).transpose(0, 2, 1, 3)).reshape(-1)
+
+
+def from_operand_order(stream: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    assert rows % 4 == 0 and cols % 64 == 0 and stream.size == rows * cols
+    return np.ascontiguousarray(
+        stream.reshape(rows // 4, cols // 64, 4, 64).transpose(0, 2, 1, 3)).reshape(-1)
+
+
+def operand_lane_symbols(cols: int, s: int) -> int:
+    """The unit length (in lane symbols) for a matrix of `cols` columns in operand
+    order: lane_symbols / 8 is the divisor of cols / 64 closest in ratio to the default,
+    within a factor of two of it and between 16 and 128; 0 when there is none."""
+    if cols <= 0 or cols % 64:
+        return 0
+    spr, want = cols // 64, default_lane_symbols(s) // 8
+    best, best_cost = 0, 0.0
+    for beta in range(16, min(128, spr) + 1):
+        if spr % beta:
+            continue
+        ratio = beta / want if beta > want else want / beta
+        if ratio > 2.0:
+            continue
+        if not best or ratio < best_cost:
+            best, best_cost = beta, ratio
+    return best * 8

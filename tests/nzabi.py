@@ -142,3 +142,52 @@ def decompress_units(cont, frac, n, s, S, units, max_words=0, canon=False, fill=
 def dev_u8(a):
     """numpy uint8 -> 16-byte aligned cuda tensor."""
     return torch.from_numpy(np.ascontiguousarray(a, dtype=np.uint8).copy()).cuda()
+
+
+def compress_operand(x_bf16, rows, cols, s, S):
+    """[rows, cols] bf16 (cuda) -> (container, fractions, max unit words), operand order."""
+    L = lib()
+    n = rows * cols
+    cap = int(L.nz_container_bound(n, S))
+    fb = int(L.nz_frac_bytes(n, s))
+    raw_c, cont = guarded(cap)
+    raw_f, frac = guarded(fb)
+    sb = int(L.nz_compress_operand_scratch_bytes(rows, cols, S))
+    scratch = torch.empty(sb, dtype=torch.uint8, device="cuda")
+    _lib.check(L.nz_compress_bf16_operand(x_bf16.data_ptr(), rows, cols, s, S, frac.data_ptr(),
+                                          cont.data_ptr(), cap, scratch.data_ptr(), sb, stream()))
+    total, mw = ctypes.c_uint64(0), ctypes.c_uint32(0)
+    _lib.check(L.nz_container_bytes(cont.data_ptr(), total, mw, stream()))
+    assert guards_intact(raw_c, cap) and guards_intact(raw_f, fb)
+    return cont[: total.value].clone(), frac.clone(), int(mw.value)
+
+
+def decompress_operand(cont, frac, rows, cols, s, S, max_words=0, canon=False):
+    L = lib()
+    n = rows * cols
+    raw_o, out = guarded(2 * n, torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.nz_decompress_bf16_operand(cont.data_ptr(), cont.numel(), frac.data_ptr(), rows,
+                                            cols, s, S, max_words, int(canon), out.data_ptr(),
+                                            status.data_ptr(), stream()))
+    torch.cuda.synchronize()
+    assert guards_intact(raw_o, 2 * n)
+    return out, int(status.item())
+
+
+def linear(cont, frac, rows, cols, s, S, x, bias=None, max_words=0, canon=False):
+    """y = x W^T (+ bias) through nz_linear_bf16; x is [m, cols] bf16 (cuda).  Returns
+    (y [m, rows] bf16, status)."""
+    L = lib()
+    m = x.shape[0]
+    raw_y, y = guarded(2 * m * rows, torch.bfloat16)
+    wb = int(L.nz_linear_workspace_bytes(rows, cols, S, m))
+    ws = torch.empty(wb, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.nz_linear_bf16(cont.data_ptr(), cont.numel(), frac.data_ptr(), rows, cols, s, S,
+                                max_words, int(canon), x.data_ptr(), m,
+                                0 if bias is None else bias.data_ptr(), y.data_ptr(),
+                                ws.data_ptr(), wb, status.data_ptr(), stream()))
+    torch.cuda.synchronize()
+    assert guards_intact(raw_y, 2 * m * rows)
+    return y.view(m, rows), int(status.item())

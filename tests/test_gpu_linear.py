@@ -1,0 +1,180 @@
+"""Operand order and the fused decode -> tcgen05 GEMM (nz_linear_bf16), through the C ABI.
+
+Integer work (operand-order containers, fractions, decoded tensors) is compared bit
+for bit with the CPU oracle applied to the permuted tensor.  The GEMM is floating
+point: products are exact in fp32, sums are fp32 in a different order from a library
+GEMM, and the result is rounded once to bf16 -- so it is compared with an fp32
+restatement (decoded weight, fp32 matmul) within 2^-7 relative (one bf16 rounding
+step of the result, 2^-8, plus the same again for the restatement's own rounding)
+plus an absolute term for cancellation, 2^-7 of the largest |x|.|w| row sum.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests import nzabi as A
+
+pytestmark = pytest.mark.gpu
+
+
+def weights(shape, seed, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+def check_linear(y, x, w_dec, bias):
+    ref = x.float() @ w_dec.float().t()
+    mag = x.float().abs() @ w_dec.float().abs().t()
+    if bias is not None:
+        ref = ref + bias.float()
+        mag = mag + bias.float().abs()
+    err = (y.float() - ref).abs()
+    bound = 2.0 ** -7 * ref.abs() + 2.0 ** -7 * 2.0 ** -8 * mag + 1e-30
+    # the second term: fp32 accumulation error is far below it; it covers results that
+    # cancel to near zero, where one bf16 step of the partial sums dominates
+    bad = err > bound
+    assert not bool(bad.any()), (float(err.max()), int(bad.sum()), tuple(y.shape))
+
+
+@pytest.mark.parametrize("s", (7, 3, 1, 0))
+@pytest.mark.parametrize("rows,cols", ((128, 1024), (8, 4096), (260, 2048), (64, 11008)))
+def test_operand_order_container_equals_oracle_of_the_permuted_tensor(s, rows, cols):
+    L = A.lib()
+    S = int(L.nz_operand_lane_symbols(cols, s))
+    assert S == O.operand_lane_symbols(cols, s)
+    if S == 0:                      # no unit length near the default divides the row: pick one
+        S = 128
+    assert (cols // 64) % (S // 8) == 0
+    w = weights((rows, cols), rows + cols + s).cuda()
+    bits = A.to_bits(w)
+    cont, frac, mw = A.compress_operand(w, rows, cols, s, S)
+    stream = O.to_operand_order(bits, rows, cols)
+    c_ref, f_ref = O.compress_bf16(stream, s, S)
+    assert np.array_equal(cont.cpu().numpy(), c_ref)
+    assert np.array_equal(frac.cpu().numpy(), f_ref)
+    out, status = A.decompress_operand(cont, frac, rows, cols, s, S, mw, canon=True)
+    assert status == 0
+    ref = O.from_operand_order(O.decompress_bf16(c_ref, f_ref, bits.size, s, canonical_nan=True),
+                               rows, cols)
+    assert np.array_equal(A.to_bits(out), ref)
+    if s == 7:
+        assert np.array_equal(ref, bits)
+
+
+def test_operand_order_with_raw_units_and_all_patterns():
+    """Exponent bytes that do not compress (every pattern once) are stored raw; the
+    operand-order decode must place them as well."""
+    rows, cols, s = 16, 4096, 7
+    S = int(A.lib().nz_operand_lane_symbols(cols, s))
+    bits = np.arange(65536, dtype=np.uint16)
+    rng = np.random.default_rng(3)
+    rng.shuffle(bits)
+    w = A.from_bits(bits)
+    cont, frac, mw = A.compress_operand(w, rows, cols, s, S)
+    hdr = O.parse_header(cont.cpu().numpy())
+    assert hdr["n_raw_units"] > 0
+    out, status = A.decompress_operand(cont, frac, rows, cols, s, S, mw, canon=False)
+    assert status == 0
+    assert np.array_equal(A.to_bits(out), bits)
+
+
+def test_batched_decode_mixes_operand_order_and_stream_order_items():
+    from neuzip_b200 import _lib
+    L = A.lib()
+    s, rows, cols = 7, 256, 2048
+    S = int(L.nz_operand_lane_symbols(cols, s))
+    assert S == int(L.nz_default_lane_symbols(s))
+    w1, w2 = weights((rows, cols), 1).cuda(), weights((rows, cols), 2).cuda()
+    c1, f1, m1 = A.compress_operand(w1, rows, cols, s, S)
+    c2, f2, m2 = A.compress(w2.view(-1), s, S)
+    outs = [torch.empty(rows * cols, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    items = (_lib.DecompressItem * 2)()
+    for k, (c, f, mw, oc) in enumerate(((c1, f1, m1, cols), (c2, f2, m2, 0))):
+        items[k].container, items[k].container_bytes = c.data_ptr(), c.numel()
+        items[k].frac_in, items[k].n = f.data_ptr(), rows * cols
+        items[k].max_unit_words, items[k].flags = mw, 0
+        items[k].out_bf16, items[k].operand_cols = outs[k].data_ptr(), oc
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.nz_decompress_bf16_batch(items, 2, s, S, 1, status.data_ptr(), A.stream()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(outs[0].view(torch.int16), w1.view(-1).view(torch.int16))
+    assert torch.equal(outs[1].view(torch.int16), w2.view(-1).view(torch.int16))
+
+
+LINEAR_SHAPES = ((128, 1024), (256, 2048), (512, 4096), (136, 2048), (384, 11008))
+
+
+@pytest.mark.parametrize("rows,cols", LINEAR_SHAPES)
+@pytest.mark.parametrize("m", (1, 16, 100, 128))
+def test_fused_linear_lossless_matches_fp32_restatement(rows, cols, m):
+    s = 7
+    S = int(A.lib().nz_operand_lane_symbols(cols, s))
+    w = weights((rows, cols), 10 + rows).cuda()
+    cont, frac, mw = A.compress_operand(w, rows, cols, s, S)
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, cols, generator=g, dtype=torch.float32).to(torch.bfloat16).cuda()
+    y, status = A.linear(cont, frac, rows, cols, s, S, x, None, mw)
+    assert status == 0
+    check_linear(y, x, w, None)
+
+
+@pytest.mark.parametrize("s", (3, 1, 0))
+def test_fused_linear_lossy_precisions_with_bias(s):
+    rows, cols, m = 256, 4096, 48
+    S = 256          # shorter than the size-optimal unit of the lossy precisions: fits next to the tiles
+    w = weights((rows, cols), 77 + s).cuda()
+    cont, frac, mw = A.compress_operand(w, rows, cols, s, S)
+    w_dec, status = A.decompress_operand(cont, frac, rows, cols, s, S, mw, canon=True)
+    assert status == 0
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(m, cols, generator=g, dtype=torch.float32).to(torch.bfloat16).cuda()
+    bias = torch.randn(rows, generator=g, dtype=torch.float32).to(torch.bfloat16).cuda()
+    y, status = A.linear(cont, frac, rows, cols, s, S, x, bias, mw, canon=True)
+    assert status == 0
+    check_linear(y, x, w_dec.view(rows, cols), bias)
+
+
+@pytest.mark.parametrize("m", (256, 300, 512))
+def test_fused_linear_many_tokens_take_several_passes(m):
+    rows, cols, s = 256, 2048, 7
+    S = int(A.lib().nz_operand_lane_symbols(cols, s))
+    w = weights((rows, cols), 5).cuda()
+    cont, frac, mw = A.compress_operand(w, rows, cols, s, S)
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, cols, generator=g, dtype=torch.float32).to(torch.bfloat16).cuda()
+    bias = torch.randn(rows, generator=g, dtype=torch.float32).to(torch.bfloat16).cuda()
+    y, status = A.linear(cont, frac, rows, cols, s, S, x, bias, mw)
+    assert status == 0
+    check_linear(y, x, w, bias)
+
+
+def test_fused_linear_is_reproducible_and_exact_on_integers():
+    """Small integers: every product and sum is exact in fp32 and the result is exactly
+    representable, so the fused kernel must reproduce the integer GEMM exactly."""
+    rows, cols, s, m = 128, 2048, 7, 32
+    S = int(A.lib().nz_operand_lane_symbols(cols, s))
+    g = torch.Generator().manual_seed(9)
+    w = torch.randint(-1, 2, (rows, cols), generator=g).to(torch.bfloat16).cuda()
+    x = torch.randint(-1, 2, (m, cols), generator=g).to(torch.bfloat16).cuda()
+    cont, frac, mw = A.compress_operand(w, rows, cols, s, S)
+    y1, st1 = A.linear(cont, frac, rows, cols, s, S, x, None, mw)
+    y2, st2 = A.linear(cont, frac, rows, cols, s, S, x, None, mw)
+    assert st1 == 0 and st2 == 0
+    ref = (x.double() @ w.double().t())
+    assert float(ref.abs().max()) < 256          # representable in bf16 exactly
+    assert torch.equal(y1.double(), ref)
+    assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
+
+
+def test_fused_linear_rejects_what_it_cannot_do():
+    from neuzip_b200 import _lib
+    L = A.lib()
+    assert L.nz_operand_lane_symbols(100, 7) == 0          # columns not a multiple of 64
+    assert L.nz_operand_lane_symbols(512, 7) == 0          # rows of 8 blocks: units would be too short
+    x = torch.zeros(16, 2048, dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    rc = L.nz_linear_bf16(c.data_ptr(), c.numel(), c.data_ptr(), 130, 2048, 7, 256, 0, 0,
+                          x.data_ptr(), 16, 0, x.data_ptr(), 0, 0, 0, A.stream())
+    assert rc == _lib.NZ_E_ARG                             # rows not a multiple of 4
