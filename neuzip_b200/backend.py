@@ -43,6 +43,7 @@ class _Entry:
     fractions: torch.Tensor   # uint8, packed sign+mantissa stream
     normalizers: Optional[torch.Tensor] = None   # uint8, one byte per group (normalizer_size > 0)
     stamp: int = 0            # number of the library operation that wrote these bytes
+    operand_cols: int = 0     # > 0: a [numel / operand_cols, operand_cols] matrix in operand order
 
 
 # Every operation that any backend of this process enqueues gets a number.  A decode
@@ -105,6 +106,7 @@ class CodecBackend:
 
     precision: int = 7
     normalizer_size: int = 0
+    supports_operand_order = True      # write() takes operand=
 
     def __init__(self, algorithm: Algorithm = Algorithm.ans, chunk_size: int = 1 << 16) -> None:
         if not isinstance(algorithm, Algorithm):
@@ -126,6 +128,14 @@ class CodecBackend:
         self._vec_ver = -1
         self._vec_x: Optional[torch.Tensor] = None
         self._vec_scratch: Dict[tuple, torch.Tensor] = {}
+        # 2-D weights written with operand=True are stored in operand order when their shape
+        # allows it (the stream's 256-element blocks are 4 x 64 patches of the matrix), which
+        # is what lets `linear` decode straight into tensor-core operand tiles
+        self.operand_order = True
+        # `linear` with at most this many input rows runs the fused decode -> tcgen05 GEMM
+        # (nz_linear_bf16) on operand-order weights; 0 = always decode, then library GEMM
+        self.fused_linear_max_rows = 0
+        self._lin_ws: Optional[torch.Tensor] = None
 
     # -- helpers ---------------------------------------------------------
     def _ensure_device(self) -> None:
@@ -152,15 +162,50 @@ class CodecBackend:
             raise _lib.NeuzipError("decode reported: " + _lib.describe_status(word))
 
     # -- the six methods of the extension class ----------------------------
-    def write(self, name: str, tensor: torch.Tensor) -> None:
-        """cuda/high_level.cu:132-162 (+ _write_to_cache :71-130)."""
+    def _operand_geometry(self, tensor: torch.Tensor):
+        """(cols, lane_symbols) for a matrix that can be stored in operand order, else None."""
+        if tensor.dim() != 2 or self.normalizer_size:
+            return None          # group scales follow the flat element index
+        rows, cols = int(tensor.shape[0]), int(tensor.shape[1])
+        if rows % 4 or cols % 64:
+            return None
+        S = int(self._lib.nz_operand_lane_symbols(cols, self.precision))
+        return (cols, S) if S else None
+
+    def write(self, name: str, tensor: torch.Tensor, operand: Optional[bool] = None) -> None:
+        """cuda/high_level.cu:132-162 (+ _write_to_cache :71-130).  `operand=True` asks for
+        operand order (a Linear weight); None keeps the layout the handle already has."""
         _require_bf16(tensor)
         self._ensure_device()
         flat = _as_flat_bf16_cuda(tensor)
         n = flat.numel()
         L, S = self._lib, self.lane_symbols
-        self._cache.pop(name, None)
+        previous = self._cache.pop(name, None)
+        if operand is None:
+            operand = previous is not None and previous.operand_cols > 0
+        geometry = self._operand_geometry(tensor) if (operand and self.operand_order) else None
+        if (geometry is None and operand and previous is not None and previous.operand_cols
+                and tensor.dim() != 2 and n % previous.operand_cols == 0):
+            # an update of an operand-order weight that arrives flattened
+            geometry = self._operand_geometry(tensor.reshape(-1, previous.operand_cols))
         st = _stream()
+        if geometry is not None:
+            cols, S = geometry
+            rows = n // cols
+            frac = torch.empty(int(L.nz_frac_bytes(n, self.precision)), dtype=torch.uint8, device="cuda")
+            cap = int(L.nz_container_bound(n, S))
+            staging = torch.empty(cap, dtype=torch.uint8, device="cuda")
+            scratch = self._scratch_for(int(L.nz_compress_operand_scratch_bytes(rows, cols, S)))
+            _lib.check(L.nz_compress_bf16_operand(_ptr(flat), rows, cols, self.precision, S,
+                                                  _ptr(frac), _ptr(staging), cap, _ptr(scratch),
+                                                  scratch.numel(), st))
+            total = _lib._u64(0)
+            max_words = _lib._u32(0)
+            _lib.check(L.nz_container_bytes(_ptr(staging), total, max_words, st))
+            container = staging[: total.value].clone()
+            self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac,
+                                       None, _next_op(), cols)
+            return
         normalizers = None
         if self.normalizer_size:
             # per-group scaling first (cuda/kernels.cuh:94-118); the scaled copy is what gets split
@@ -196,6 +241,13 @@ class CodecBackend:
     def read_into(self, name: str, out: torch.Tensor) -> None:
         entry = self._cache[name]
         _next_op()
+        if entry.operand_cols:
+            _lib.check(self._lib.nz_decompress_bf16_operand(
+                _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions),
+                entry.numel // entry.operand_cols, entry.operand_cols, self.precision,
+                entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan), _ptr(out),
+                _ptr(self._status), _stream()))
+            return
         _lib.check(self._lib.nz_decompress_bf16(
             _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
             self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
@@ -218,8 +270,9 @@ class CodecBackend:
         k = rows.numel()
         if k == 0:
             return torch.empty(0, row_len, dtype=torch.bfloat16, device="cuda")
-        if entry.normalizers is not None:
-            # group scales follow the flat element index: decode everything, then pick
+        if entry.normalizers is not None or entry.operand_cols:
+            # group scales follow the flat element index, and a matrix in operand order
+            # interleaves four rows per block: decode everything, then pick
             return self.read(name).view(-1, row_len)[rows]
         U = 32 * entry.lane_symbols
         per_row = 1 if U % row_len == 0 else (row_len // U if row_len % U == 0
@@ -271,6 +324,7 @@ class CodecBackend:
                 items[k].max_unit_words = e.max_unit_words
                 items[k].flags = flags
                 items[k].out_bf16 = _ptr(outs[i])
+                items[k].operand_cols = e.operand_cols
             _lib.check(self._lib.nz_decompress_bf16_batch(
                 items, len(idx), self.precision, S, int(self.canonical_nan), _ptr(self._status),
                 _stream()))
@@ -309,6 +363,7 @@ class CodecBackend:
                 items[k].max_unit_words = e.max_unit_words
                 items[k].flags = flags
                 items[k].out_bf16 = _ptr(out)
+                items[k].operand_cols = e.operand_cols
             blocks.append(items)
         # the entries keep their tensors alive as long as the batch refers to them
         batch.entries, batch.blocks, batch.lane_symbols = entries, blocks, S.pop()
@@ -340,7 +395,9 @@ class CodecBackend:
     def linear(self, name: str, input: torch.Tensor, shape: Sequence[int],
                bias: torch.Tensor) -> torch.Tensor:
         """cuda/high_level.cu:252-257."""
-        fused = self._linear_vec(name, input, shape, bias)
+        fused = self._linear_fused(name, input, shape, bias)
+        if fused is None:
+            fused = self._linear_vec(name, input, shape, bias)
         if fused is not None:
             return fused
         weight = self.read(name).view(*shape)
@@ -349,11 +406,60 @@ class CodecBackend:
     def linear_without_bias(self, name: str, input: torch.Tensor,
                             shape: Sequence[int]) -> torch.Tensor:
         """cuda/high_level.cu:259-263."""
-        fused = self._linear_vec(name, input, shape, None)
+        fused = self._linear_fused(name, input, shape, None)
+        if fused is None:
+            fused = self._linear_vec(name, input, shape, None)
         if fused is not None:
             return fused
         weight = self.read(name).view(*shape)
         return torch.matmul(input, weight.t())
+
+    def _linear_fused(self, name: str, input: torch.Tensor, shape: Sequence[int],
+                      bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """`input @ W^T (+ bias)` with the weight decoded straight into tensor-core operand
+        tiles (``nz_linear_bf16``): no bf16 copy of the weight is written or read back.
+        Returns None when the call does not qualify (weight not in operand order, input not
+        contiguous bf16 on the GPU, more input rows than `fused_linear_max_rows`).  fp32
+        accumulation and one rounding to bf16, like the library GEMM; the order of the sums
+        differs, so the last bit may."""
+        limit = self.fused_linear_max_rows
+        if not limit:
+            return None
+        entry = self._cache.get(name)
+        if entry is None or not entry.operand_cols or len(shape) != 2:
+            return None
+        out_f, in_f = int(shape[0]), int(shape[1])
+        if in_f != entry.operand_cols or out_f * in_f != entry.numel:
+            return None
+        if (input.dtype != torch.bfloat16 or not input.is_cuda or input.dim() < 1
+                or input.shape[-1] != in_f):
+            return None
+        m = input.numel() // in_f
+        if m == 0 or m > limit:
+            return None
+        if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_cuda
+                                 or bias.numel() != out_f):
+            return None
+        x = input.detach().reshape(m, in_f)
+        if not x.is_contiguous() or x.data_ptr() % 16:
+            x = x.contiguous()
+            if x.data_ptr() % 16:
+                return None
+        L = self._lib
+        y = torch.empty(input.shape[:-1] + (out_f,), dtype=torch.bfloat16, device="cuda")
+        need = int(L.nz_linear_workspace_bytes(out_f, in_f, entry.lane_symbols, m))
+        if self._lin_ws is None or self._lin_ws.numel() < need:
+            self._lin_ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        _next_op()
+        rc = L.nz_linear_bf16(
+            _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), out_f, in_f,
+            self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
+            _ptr(x), m, _ptr(bias.contiguous() if bias is not None else None), _ptr(y),
+            _ptr(self._lin_ws), self._lin_ws.numel(), _ptr(self._status), _stream())
+        if rc == _lib.NZ_E_CAPACITY:
+            return None          # units too long to sit next to the operand tiles: decode instead
+        _lib.check(rc)
+        return y
 
     def _linear_vec(self, name: str, input: torch.Tensor, shape: Sequence[int],
                     bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -365,7 +471,8 @@ class CodecBackend:
         if not self.fused_vector_linear:
             return None
         entry = self._cache.get(name)
-        if entry is None or entry.normalizers is not None or len(shape) != 2:
+        if (entry is None or entry.normalizers is not None or entry.operand_cols
+                or len(shape) != 2):
             return None
         out_f, in_f = int(shape[0]), int(shape[1])
         if (input.dtype != torch.bfloat16 or not input.is_cuda or input.numel() != in_f
@@ -417,7 +524,8 @@ class CodecBackend:
                 "lane_symbols": e.lane_symbols, "max_unit_words": e.max_unit_words,
                 "container": e.container.cpu(), "fractions": e.fractions.cpu(),
                 "normalizer_size": self.normalizer_size,
-                "normalizers": None if e.normalizers is None else e.normalizers.cpu()}
+                "normalizers": None if e.normalizers is None else e.normalizers.cpu(),
+                "operand_cols": e.operand_cols}
 
     def import_entry(self, name: str, blob: dict) -> None:
         """Inverse of `export_entry`: the compressed bytes go straight to the GPU,
@@ -437,7 +545,7 @@ class CodecBackend:
             normalizers = normalizers.to(device="cuda", dtype=torch.uint8).contiguous()
         self._cache[name] = _Entry(n, torch.bfloat16, int(blob["lane_symbols"]),
                                    int(blob["max_unit_words"]), container, fractions, normalizers,
-                                   _next_op())
+                                   _next_op(), int(blob.get("operand_cols", 0)))
 
     # -- extras -----------------------------------------------------------
     def erase(self, name: str) -> None:

@@ -72,12 +72,19 @@ class Manager:
             self._be = factory(algorithm.value, chunk_size)
         self.meta_dict: Dict[str, torch.Size] = {}
 
-    def write(self, tensor: torch.Tensor, handle: Optional[str] = None) -> str:
-        """Compress ``tensor`` and return its handle; an existing handle is replaced."""
+    def write(self, tensor: torch.Tensor, handle: Optional[str] = None,
+              operand: Optional[bool] = None) -> str:
+        """Compress ``tensor`` and return its handle; an existing handle is replaced.
+        ``operand=True`` (not in the reference) marks a 2-D weight that will be the matrix
+        of `linear`: the backend may then store it in the order the fused GEMM wants; what
+        `read` returns is the same either way."""
         if handle is None:
             handle = str(len(self.meta_dict))
         self.meta_dict[handle] = tensor.shape
-        self._be.write(handle, tensor)
+        if operand is None or not getattr(self._be, "supports_operand_order", False):
+            self._be.write(handle, tensor)
+        else:
+            self._be.write(handle, tensor, operand=operand)
         return handle
 
     def read(self, handle: str) -> torch.Tensor:
@@ -133,6 +140,14 @@ class Manager:
         the library GEMM but a different order of the sums."""
         if hasattr(self._be, "fused_vector_linear"):
             self._be.fused_vector_linear = bool(enabled)
+
+    def fuse_linear(self, max_rows: int = 256) -> None:
+        """Let `linear` with at most `max_rows` input rows (tokens) decode the weight
+        straight into tensor-core operand tiles instead of decompressing it first
+        (0 switches it off).  Same fp32 accumulation as the library GEMM, different order
+        of the sums."""
+        if hasattr(self._be, "fused_linear_max_rows"):
+            self._be.fused_linear_max_rows = int(max_rows)
 
     def export_entry(self, handle: str) -> dict:
         """Stored bytes + metadata of a handle (for checkpoints)."""

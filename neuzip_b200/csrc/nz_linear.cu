@@ -15,9 +15,9 @@
 // length).  16 decoder warps walk 2 units each (the 32 row groups of the tile),
 // one block per step; a lane's 8 decoded elements are one 16-byte chunk of the
 // tile, stored where the 128-byte-swizzled K-major layout of the tensor-core
-// operand wants it.  One more warp feeds the tensor cores: it fetches the
-// matching 64-column slab of x with a tiled bulk tensor copy (TMA, no multicast)
-// and, when both the weight tile and the x slab of a step are complete, issues
+// operand wants it.  Two more warps feed the tensor cores: one thread fetches the
+// matching 64-column slab of x with a tiled bulk tensor copy (TMA, no multicast);
+// another, when both the weight tile and the x slab of a step are complete, issues
 // four tcgen05.mma (128 x N x 16, bf16 x bf16 -> fp32) that accumulate in tensor
 // memory.  Tiles and slabs cycle through a small ring guarded by mbarriers:
 //   full[s]   16 arrivals: every decoder warp has written its rows of tile s
@@ -32,6 +32,7 @@
 // CTA-wide abort flag that all other waits watch, and the CTA leaves through the
 // common exit, which frees its tensor memory.
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -41,7 +42,7 @@
 namespace nz {
 
 constexpr int kLinDecWarps = 16;                    // 2 units each: 32 row groups = 128 rows
-constexpr int kLinWarps = kLinDecWarps + 1;         // + the TMA / MMA warp
+constexpr int kLinWarps = kLinDecWarps + 2;         // + the tensor-core warp and the TMA warp
 constexpr int kLinThreads = kLinWarps * 32;
 constexpr uint32_t kTileRows = 128;
 constexpr uint32_t kTileBytes = kTileRows * 128;    // 128 rows x 64 bf16
@@ -184,7 +185,7 @@ __device__ __forceinline__ void chain_symbols(LinChain &ch, const LutView &lv, u
   }
 }
 
-template <int S, bool CANON, int ROW>
+template <int S, bool CANON, int ROW, bool BOTH_CODED>
 __device__ __forceinline__ bool linear_decode_loop(LinChain (&ch)[2], const LutView &lv,
                                                    uint32_t n_blocks, uint32_t stages,
                                                    uint32_t tiles0, uint32_t bar_full0,
@@ -200,6 +201,7 @@ __device__ __forceinline__ bool linear_decode_loop(LinChain (&ch)[2], const LutV
       fr[c][k] = (ch[c].kind != kUnitSkip && (uint32_t)k < n_blocks)
                      ? load_frac<S>(ch[c].frac + k * kFracStride) : 0;
   uint32_t stage = 0, phase = 0;
+#pragma unroll 1
   for (uint32_t b0 = 0; b0 < n_blocks; b0 += kAhead) {
 #pragma unroll
     for (int k = 0; k < kAhead; ++k) {
@@ -212,18 +214,38 @@ __device__ __forceinline__ bool linear_decode_loop(LinChain (&ch)[2], const LutV
         if (ch[c].kind != kUnitSkip && b + kAhead < n_blocks)
           fr[c][k] = load_frac<S>(ch[c].frac + (kAhead + k) * kFracStride);
       }
+      uint32_t w[2][4];
+      if (BOTH_CODED) {
+        // the two chains' steps alternate: each hides the other's table and multiply latency
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          uint32_t e0[2], e1[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) e0[c] = decode_step<ROW>(ch[c].st, lv);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) e1[c] = decode_step<ROW>(ch[c].st, lv);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) w[c][t] = merge_word<S, CANON>(e0[c], e1[c], bits[c], t);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          if (ch[c].kind == kUnitSkip) continue;
+          uint32_t ent[8];
+          chain_symbols<ROW>(ch[c], lv, ent);
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            w[c][t] = merge_word<S, CANON>(ent[2 * t], ent[2 * t + 1], bits[c], t);
+        }
+      }
       // the tensor cores must be done with the tile this step overwrites
       if (b >= stages && !wait_phase_warp(bar_empty0 + 8 * stage, phase ^ 1, abort_flag)) return false;
       const uint32_t tile = tiles0 + stage * kTileBytes;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        if (ch[c].kind == kUnitSkip) continue;
-        uint32_t ent[8], w[4];
-        chain_symbols<ROW>(ch[c], lv, ent);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) w[t] = merge_word<S, CANON>(ent[2 * t], ent[2 * t + 1], bits[c], t);
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tile + ch[c].dst), "r"(w[0]),
-                     "r"(w[1]), "r"(w[2]), "r"(w[3])
+        if (!BOTH_CODED && ch[c].kind == kUnitSkip) continue;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(tile + ch[c].dst),
+                     "r"(w[c][0]), "r"(w[c][1]), "r"(w[c][2]), "r"(w[c][3])
                      : "memory");
       }
       // make this lane's stores visible to the tensor cores' (asynchronous proxy) reads,
@@ -304,12 +326,16 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
   const uint32_t xs_a = tiles_a + p.stages * kTileBytes;     // 16 KB tiles keep this 1024-aligned
   const uint32_t n_blocks = p.S / 8;
   const bool is_dec = warp < (uint32_t)kLinDecWarps;
+  const bool is_mma = warp == (uint32_t)kLinDecWarps;
 
+  // a dependent launch (the kernel that adds up the column segments) may be set up now; it
+  // waits for this grid to complete before it reads anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- barriers and tensor memory
   if (threadIdx.x == 0) *abort_flag = 0;
   if (is_dec) {
     if (lane == 0) mbar_init(misc_a + kBarWarp + 8 * warp, 1);
-  } else {
+  } else if (is_mma) {
     if (lane == 0) {
       for (uint32_t s = 0; s < p.stages; ++s) {
         mbar_init(misc_a + kBarFull + 8 * s, kLinDecWarps);
@@ -399,16 +425,20 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
       // the operand only ever reaches the same row of the result, which is not stored
       // for rows outside the matrix and is flagged in the status word otherwise.
       const uint32_t bar_full0 = misc_a + kBarFull, bar_empty0 = misc_a + kBarEmpty;
+      const bool both = ch[0].kind == kUnitCoded && ch[1].kind == kUnitCoded;
       bool fine;
-      if (canon)
-        fine = linear_decode_loop<S, true, 0>(ch, lv, n_blocks, p.stages, tiles_a, bar_full0,
-                                              bar_empty0, lane, abort_flag);
+#define NZ_LIN_LOOP(CANON, ROW, BOTH)                                                          \
+  linear_decode_loop<S, CANON, ROW, BOTH>(ch, lv, n_blocks, p.stages, tiles_a, bar_full0,      \
+                                          bar_empty0, lane, abort_flag)
+      if (!both)
+        fine = canon ? NZ_LIN_LOOP(true, 0, false) : NZ_LIN_LOOP(false, 0, false);
+      else if (canon)
+        fine = NZ_LIN_LOOP(true, 0, true);
       else if (row_shift == 7)
-        fine = linear_decode_loop<S, false, 7>(ch, lv, n_blocks, p.stages, tiles_a, bar_full0,
-                                               bar_empty0, lane, abort_flag);
+        fine = NZ_LIN_LOOP(false, 7, true);
       else
-        fine = linear_decode_loop<S, false, 0>(ch, lv, n_blocks, p.stages, tiles_a, bar_full0,
-                                               bar_empty0, lane, abort_flag);
+        fine = NZ_LIN_LOOP(false, 0, true);
+#undef NZ_LIN_LOOP
       if (!fine) {
         if (lane == 0) raise(a.status, NZ_STATUS_TIMEOUT);
         *abort_flag = 1;
@@ -450,20 +480,13 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
         }
       }
     }
-  } else if (lane == 0) {
-    // ------------------------------------------------------- TMA + tensor-core thread
-    if (ok) {
+  } else if (is_mma) {
+    // ---------------------------------------------------------- tensor-core thread
+    if (ok && lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.n_pad >> 3) << 17) |
                              ((kTileRows >> 4) << 24);     // fp32 accumulate, bf16 x bf16, K-major
-      const int32_t k_first = (int32_t)(seg * n_blocks * 64);
-      const uint32_t pre = p.stages < n_blocks ? p.stages : n_blocks;
-      for (uint32_t s = 0; s < pre; ++s) {
-        mbar_expect_tx(misc_a + kBarXFull + 8 * s, xslab_bytes);
-        tma_load_2d(xs_a + s * xslab_bytes, &x_map, k_first + (int32_t)(s * 64), (int32_t)p.tok0,
-                    misc_a + kBarXFull + 8 * s);
-      }
       uint32_t stage = 0, phase = 0;
-      for (uint32_t b = 0; b < n_blocks && ok; ++b) {
+      for (uint32_t b = 0; b < n_blocks; ++b) {
         ok = wait_phase(misc_a + kBarFull + 8 * stage, phase, abort_flag) &&
              wait_phase(misc_a + kBarXFull + 8 * stage, phase, abort_flag);
         if (!ok) break;
@@ -473,16 +496,8 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k)      // 4 x 16 columns; 32 bytes = 2 descriptor units each
           mma_bf16_ss(tmem, ad + 2 * k, bd + 2 * k, idesc, (b | k) != 0);
+        // arrives when these MMAs are complete: tile and slab `stage` are free again
         mma_commit(misc_a + kBarEmpty + 8 * stage);
-        if (b + p.stages < n_blocks) {
-          // the slab is free once those MMAs have completed; then fetch its next use
-          ok = wait_phase(misc_a + kBarEmpty + 8 * stage, phase, abort_flag);
-          if (!ok) break;
-          mbar_expect_tx(misc_a + kBarXFull + 8 * stage, xslab_bytes);
-          tma_load_2d(xs_a + stage * xslab_bytes, &x_map,
-                      k_first + (int32_t)((b + p.stages) * 64), (int32_t)p.tok0,
-                      misc_a + kBarXFull + 8 * stage);
-        }
         if (++stage == p.stages) {
           stage = 0;
           phase ^= 1;
@@ -495,13 +510,34 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
         *abort_flag = 1;
       }
     }
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ TMA thread
+    // the x slab of step b: columns [seg * S / 8 + b] * 64 .. + 63 of the launch's tokens
+    if (ok) {
+      const int32_t k_first = (int32_t)(seg * n_blocks * 64);
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t b = 0; b < n_blocks; ++b) {
+        if (b >= p.stages && !wait_phase(misc_a + kBarEmpty + 8 * stage, phase ^ 1, abort_flag)) {
+          raise(a.status, NZ_STATUS_TIMEOUT);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(misc_a + kBarXFull + 8 * stage, xslab_bytes);
+        tma_load_2d(xs_a + stage * xslab_bytes, &x_map, k_first + (int32_t)(b * 64), (int32_t)p.tok0,
+                    misc_a + kBarXFull + 8 * stage);
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
   }
 
   // ---- common exit: everybody is done with tensor memory, then it is freed
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (!is_dec) {
+  if (is_mma) {
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(p.tmem_cols)
@@ -514,6 +550,9 @@ __global__ void linear_finish_kernel(const float *__restrict__ partial, uint32_t
                                      uint64_t plane, uint32_t rows,
                                      const uint16_t *__restrict__ bias, uint16_t *__restrict__ y) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // launched with programmatic stream serialisation: wait for the kernel that wrote the
+  // partial sums (a no-op for an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (i >= plane) return;
   float sum = 0.f;
   for (uint32_t s = 0; s < segs; ++s) sum += partial[(uint64_t)s * plane + i];
@@ -563,10 +602,12 @@ static bool linear_geometry(uint32_t S, uint32_t max_unit_words, uint32_t n_pad,
   const uint32_t fixed = 1024 /* alignment slack */ + 1024 /* misc */ +
                          2 * kLinDecWarps * g.slot_bytes + guard + 1024 /* tile alignment */;
   const uint32_t per_stage = kTileBytes + n_pad * 128u;
-  // prefer the conflict-free table (2^12 slots x 8 copies = 128 KB is never needed: lossless
-  // containers carry 9-bit tables, which reach 32 copies with lut_shift 4), then stages
-  for (uint32_t sh = 4; sh >= 2; --sh) {
-    for (uint32_t st = 3; st >= 2; --st) {
+  // Ring depth first (decoder warps that run ahead of the slowest one need somewhere to
+  // write), then table copies (fewer shared-memory bank conflicts per lookup).
+  const char *force = getenv("NZ_LINEAR_GEOMETRY");      // "<lut_shift>,<stages>": tuning aid
+  if (force) {
+    unsigned sh = 0, st = 0;
+    if (sscanf(force, "%u,%u", &sh, &st) == 2 && sh >= 2 && sh <= 4 && st >= 2 && st <= kLinMaxStages) {
       const uint64_t need = (uint64_t)fixed + (4096u << sh) + (uint64_t)st * per_stage;
       if (need <= kMaxDynamicSmem) {
         g.lut_shift = sh;
@@ -574,6 +615,16 @@ static bool linear_geometry(uint32_t S, uint32_t max_unit_words, uint32_t n_pad,
         g.smem_bytes = (uint32_t)need;
         return true;
       }
+    }
+  }
+  static const uint32_t order[][2] = {{4, 3}, {3, 3}, {4, 2}, {3, 2}, {2, 3}, {2, 2}};
+  for (const auto &o : order) {
+    const uint64_t need = (uint64_t)fixed + (4096u << o[0]) + (uint64_t)o[1] * per_stage;
+    if (need <= kMaxDynamicSmem) {
+      g.lut_shift = o[0];
+      g.stages = o[1];
+      g.smem_bytes = (uint32_t)need;
+      return true;
     }
   }
   return false;
@@ -744,11 +795,20 @@ extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, c
       set_error("nz_linear_bf16: output too large for one call");
       return NZ_E_ARG;
     }
-    linear_finish_kernel<<<(unsigned)blocks, 256, 0, st>>>((const float *)workspace, segs, plane,
-                                                           (uint32_t)rows,
-                                                           (const uint16_t *)bias_bf16,
-                                                           (uint16_t *)y_bf16);
-    NZ_LAUNCH_CHECK("linear_finish_kernel");
+    // the launch itself may overlap the tail of the kernel before it; the kernel waits
+    // (griddepcontrol.wait) before it reads the partial sums
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NZ_CUDA_TRY(cudaLaunchKernelEx(&cfg, linear_finish_kernel, (const float *)workspace, segs, plane,
+                                   (uint32_t)rows, (const uint16_t *)bias_bf16,
+                                   (uint16_t *)y_bf16));
   }
   return NZ_OK;
 }

@@ -10,7 +10,7 @@ class Linear(torch.nn.Module):
         super().__init__()
         self.manager = manager
         self.in_features, self.out_features = linear.in_features, linear.out_features
-        self._p = Parameter(manager, linear.weight.data)
+        self._p = Parameter(manager, linear.weight.data, operand=True)
         if linear.bias is None:
             self.register_parameter("bias", None)
         else:

@@ -8,13 +8,14 @@ class Parameter(torch.nn.Parameter):
     real weight gradient is collected in ``_gradient`` by the autograd function,
     ``.grad`` only ever holds a zero-size placeholder."""
 
-    def __new__(cls, manager, data, requires_grad=True):
+    def __new__(cls, manager, data, requires_grad=True, operand=None):
         placeholder = torch.zeros(0, dtype=data.dtype, device=data.device)
         self = super().__new__(cls, placeholder, requires_grad)
         self._manager = manager
         self._shape = data.shape
         self._gradient = None
-        self._handle = manager.write(data)
+        # operand=True: this tensor is the weight of a Linear (not in the reference's signature)
+        self._handle = manager.write(data) if operand is None else manager.write(data, operand=operand)
         self._staged = None        # view of a shared decode buffer (neuzip_b200.layerwise)
         self._stage_tag = None     # (stage, block number): the view is valid while they agree
         return self

@@ -178,3 +178,85 @@ def test_fused_linear_rejects_what_it_cannot_do():
     rc = L.nz_linear_bf16(c.data_ptr(), c.numel(), c.data_ptr(), 130, 2048, 7, 256, 0, 0,
                           x.data_ptr(), 16, 0, x.data_ptr(), 0, 0, 0, A.stream())
     assert rc == _lib.NZ_E_ARG                             # rows not a multiple of 4
+
+
+# ------------------------------------------------------------- through the Manager
+import neuzip  # noqa: E402
+
+
+def test_manager_stores_linear_weights_in_operand_order_and_reads_them_back():
+    m = neuzip.Manager(precision=7)
+    w = weights((256, 2048), 21).cuda()
+    h = m.write(w, operand=True)
+    e = m._be.entry(h)
+    assert e.operand_cols == 2048 and e.lane_symbols == 256
+    assert torch.equal(m.read(h).view(torch.int16), w.view(torch.int16))
+    # the stored bytes are the oracle's for the permuted tensor
+    stream = O.to_operand_order(A.to_bits(w), 256, 2048)
+    c_ref, f_ref = O.compress_bf16(stream, 7, 256)
+    assert np.array_equal(e.container.cpu().numpy(), c_ref)
+    assert np.array_equal(e.fractions.cpu().numpy(), f_ref)
+    # a shape that cannot be in operand order falls back to stream order
+    h2 = m.write(weights((10, 100), 22).cuda(), operand=True)
+    assert m._be.entry(h2).operand_cols == 0
+    # an update under the same handle keeps the layout; so does a checkpoint round trip
+    w2 = weights((256, 2048), 23).cuda()
+    m.write(w2, h)
+    assert m._be.entry(h).operand_cols == 2048
+    blob = m.export_entry(h)
+    m2 = neuzip.Manager(precision=7)
+    h3 = m2.import_entry(blob)
+    assert m2._be.entry(h3).operand_cols == 2048
+    assert torch.equal(m2.read(h3).view(torch.int16), w2.view(torch.int16))
+    # batched reads mix layouts
+    a, b = m.read_many([h, h2])
+    assert torch.equal(a.view(torch.int16), w2.view(torch.int16))
+    rows = m.read_rows(h, torch.tensor([3, 200, 7], device="cuda"))
+    assert torch.equal(rows.view(torch.int16), w2[[3, 200, 7]].view(torch.int16))
+    m.check()
+    m2.check()
+
+
+@pytest.mark.parametrize("with_bias", (False, True))
+def test_manager_linear_takes_the_fused_path_when_enabled(with_bias):
+    m = neuzip.Manager(precision=7)
+    w = weights((384, 2048), 31).cuda()
+    h = m.write(w, operand=True)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2, 5, 2048, generator=g).to(torch.bfloat16).cuda()
+    bias = torch.randn(384, generator=g).to(torch.bfloat16).cuda() if with_bias else None
+    plain = m.linear(h, x, bias)                       # decode, then library GEMM
+    m.fuse_linear(256)
+    fused = m.linear(h, x, bias)
+    assert fused.shape == plain.shape == (2, 5, 384)
+    check_linear(fused.reshape(10, 384), x.reshape(10, 2048), w, bias)
+    assert (fused.float() - plain.float()).abs().max().item() <= 2.0 ** -6 * plain.float().abs().max().item()
+    # more rows than the limit: back to decode + GEMM, bit-identical to the plain path
+    m.fuse_linear(4)
+    assert torch.equal(m.linear(h, x, bias), plain)
+    m.check()
+
+
+def test_converted_llama_with_fused_linear_matches_dense_logits_and_tokens():
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.LlamaConfig(vocab_size=512, hidden_size=1024, intermediate_size=2048,
+                                   num_hidden_layers=2, num_attention_heads=8,
+                                   num_key_value_heads=8, max_position_embeddings=128)
+    torch.manual_seed(0)
+    model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+    ids = torch.randint(0, 512, (1, 16), device="cuda")
+    with torch.no_grad():
+        ref_logits = model(ids).logits
+        ref_tokens = model.generate(ids, max_new_tokens=8, do_sample=False)
+    m = neuzip.Manager()
+    m.convert(model)
+    m.fuse_linear(256)
+    linears = [mod for mod in model.modules() if isinstance(mod, neuzip.nn.Linear)]
+    assert len(linears) == 14
+    assert all(m._be.entry(mod._p._handle).operand_cols == mod.in_features for mod in linears)
+    with torch.no_grad():
+        logits = model(ids).logits                     # prefill: 16 rows per Linear
+        tokens = model.generate(ids, max_new_tokens=8, do_sample=False)   # then one row at a time
+    m.check()
+    assert (logits.float() - ref_logits.float()).abs().max().item() <= 1e-2
+    assert torch.equal(tokens, ref_tokens)
