@@ -70,8 +70,8 @@ uint64_t nz_container_bound(uint64_t n, uint32_t lane_symbols);
 /* Bytes of device scratch nz_encode_exponents needs. */
 uint64_t nz_encode_scratch_bytes(uint64_t n, uint32_t lane_symbols);
 
-/* Bytes of device scratch nz_compress_bf16 needs (the encode scratch plus the
- * intermediate exponent stream). */
+/* Bytes of device scratch nz_compress_bf16 needs (tables and one slot per coded
+ * unit; the exponent stream is never written to memory). */
 uint64_t nz_compress_scratch_bytes(uint64_t n, uint32_t lane_symbols);
 
 /* ---- split / merge ------------------------------------------------------ */
@@ -174,8 +174,11 @@ int nz_decode_exponents(const void *container, uint64_t container_bytes,
 /* ---- whole-tensor paths -------------------------------------------------- */
 
 /* split + histogram + table + encode in one call: bf16[N] -> fractions +
- * container.  Buffers as for nz_split_bf16 / nz_encode_exponents, scratch of
- * nz_compress_scratch_bytes bytes.
+ * container, byte for byte what nz_split_bf16 followed by nz_encode_exponents
+ * give (with 9-bit probabilities at precision 7).  Two sweeps over the input: a
+ * histogram of the exponent bytes, then a kernel that writes the fractions and
+ * codes the exponents without storing them.  Buffers as for nz_split_bf16 /
+ * nz_encode_exponents, scratch of nz_compress_scratch_bytes bytes.
  * Reference: Manager::_write_to_cache, cuda/high_level.cu:71-130. */
 int nz_compress_bf16(const void *in_bf16, uint64_t n, int precision,
                      uint32_t lane_symbols, void *frac_out, void *container,

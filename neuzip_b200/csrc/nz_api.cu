@@ -35,11 +35,10 @@ int sm_count() {
   return cached;
 }
 
-int split_bf16(const void *in, uint64_t n, int precision, void *exp_out, void *frac_out,
-               cudaStream_t st);
-int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container,
-                     uint64_t container_cap, void *scratch, uint64_t scratch_bytes,
-                     cudaStream_t st, uint32_t low_prob_bits);
+int compress_bf16_fused(const void *in, uint64_t n, int precision, uint32_t LS, uint32_t cols,
+                        void *frac_out, void *container, uint64_t container_cap, void *scratch,
+                        uint64_t scratch_bytes, cudaStream_t st);
+uint64_t compress_fused_scratch_bytes(uint64_t n, uint32_t LS);
 
 }  // namespace nz
 
@@ -78,9 +77,8 @@ extern "C" uint32_t nz_default_lane_symbols(int precision) {
 }
 
 extern "C" uint64_t nz_compress_scratch_bytes(uint64_t n, uint32_t lane_symbols) {
-  const uint64_t enc = nz_encode_scratch_bytes(n, lane_symbols);
-  if (enc == 0) return 0;
-  return enc + nz::align16(n) + 16;
+  if (!nz::valid_lane_symbols(lane_symbols)) return 0;
+  return nz::compress_fused_scratch_bytes(n, lane_symbols);
 }
 
 extern "C" int nz_compress_bf16(const void *in_bf16, uint64_t n, int precision,
@@ -110,23 +108,12 @@ extern "C" int nz_compress_bf16(const void *in_bf16, uint64_t n, int precision,
                   "fractions 8-byte aligned");
     return NZ_E_ARG;
   }
-  const uint64_t enc = nz_encode_scratch_bytes(n, lane_symbols);
-  if (scratch_bytes < enc + nz::align16(n) + 16) {
+  const uint64_t need = nz::compress_fused_scratch_bytes(n, lane_symbols);
+  if (scratch_bytes < need) {
     nz::set_error("nz_compress_bf16: scratch of %llu bytes is smaller than the %llu required",
-                  (unsigned long long)scratch_bytes,
-                  (unsigned long long)(enc + nz::align16(n) + 16));
+                  (unsigned long long)scratch_bytes, (unsigned long long)need);
     return NZ_E_CAPACITY;
   }
-  cudaStream_t st = (cudaStream_t)stream;
-  uint8_t *exp_buf = (uint8_t *)scratch + nz::align16(enc);
-  if (n) {
-    int rc = nz::split_bf16(in_bf16, n, precision, exp_buf, frac_out, st);
-    if (rc) return rc;
-  }
-  // Lossless tensors keep 8 fraction bits per element, so the exponent stream is
-  // a quarter of what is stored: 9-bit probabilities cost 0.2 % of the stored
-  // size there and let the decoder keep one table copy per shared-memory bank.
-  const uint32_t low_pb = precision == 7 ? nz::kMinProbBits : nz::kDefaultLowProbBits;
-  return nz::encode_exponents(exp_buf, n, lane_symbols, container, container_cap, scratch, enc, st,
-                              low_pb);
+  return nz::compress_bf16_fused(in_bf16, n, precision, lane_symbols, 0, frac_out, container,
+                                 container_cap, scratch, scratch_bytes, (cudaStream_t)stream);
 }

@@ -591,6 +591,592 @@ int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container
   return NZ_OK;
 }
 
+
+// ===========================================================================
+// Whole-tensor compressor: bf16 in, fractions + container out, with no exponent
+// stream in global memory.
+//
+// Replaces split + nvcomp compress + right-sizing of the reference's write path
+// (cuda/high_level.cu:81-124) in two sweeps over the bf16 input:
+//   1. bf16_histogram_kernel  counts the exponent bytes (after the rounding of the
+//      lossy precisions, exactly as the split computes them);
+//   2. bf16_encode_kernel     reads the input again (largely from L2 for tensors of
+//      the usual size), writes the packed fractions and rANS-codes the exponents.
+//      A warp codes two units side by side (two independent chains per lane);
+//      each lane's 16-bit words go into its slice of a shared-memory cell, the
+//      cell is then squeezed into the unit's final layout and written with
+//      coalesced stores into the unit's slot of the scratch area.
+// scan_kernel then fixes the offsets and place_units_kernel copies every slot to
+// its place in the payload.  The input may be a matrix to be stored in operand
+// order: the element a lane handles is then found through operand_index().
+// The results are byte-identical to split + nz_encode_exponents.
+//
+// A lane's slice holds `cap_s` words (4 bits per symbol on average; real weights
+// need about 2.6).  A unit in which some lane needs more is coded again, words
+// placed straight into the slot in global memory: slower, same bytes.
+constexpr int kFusedWarps = 8;
+constexpr int kFusedChains = 2;
+
+template <int S>
+__device__ __forceinline__ uint32_t exp_of(uint32_t val) {
+  const uint32_t mag = val & 0x7FFFu;
+  uint32_t keep = mag >> (7 - S);
+  if (S < 7) keep += (mag >> (6 - S)) & 1u;
+  return (keep >> S) & 0xFFu;
+}
+
+// The 8 elements of a 16-byte load, two per 32-bit word, split with half-word
+// arithmetic: exponent bytes (lo: elements 0-3, hi: 4-7) and the S+1 bytes of packed
+// fields in memory order (f0: first four bytes, f1: the rest at precision 7).
+template <int S>
+__device__ __forceinline__ void split8(const uint32_t (&w)[4], uint32_t &lo, uint32_t &hi,
+                                       uint32_t &f0, uint32_t &f1) {
+  constexpr uint32_t kOnes = 0x00010001u;
+  constexpr uint32_t kKeep = ((1u << (8 + S)) - 1u) * kOnes;
+  uint32_t ex[4], fd[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t m = w[j] & 0x7FFF7FFFu;
+    uint32_t k = (m >> (7 - S)) & kKeep;
+    if (S < 7) k = (k + ((m >> (6 - S)) & kOnes)) & kKeep;   // the carry stays inside its half
+    ex[j] = (k >> S) & 0x00FF00FFu;
+    fd[j] = ((w[j] >> (15 - S)) & ((1u << S) * kOnes)) | (k & (((1u << S) - 1u) * kOnes));
+  }
+  lo = __byte_perm(ex[0], ex[1], 0x6420);
+  hi = __byte_perm(ex[2], ex[3], 0x6420);
+  f1 = 0;
+  if (S == 7) {
+    f0 = __byte_perm(fd[0], fd[1], 0x6420);
+    f1 = __byte_perm(fd[2], fd[3], 0x6420);
+  } else if (S == 3) {
+    uint32_t b[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b[j] = ((fd[j] << 4) | (fd[j] >> 16)) & 0xFFu;
+    f0 = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+  } else if (S == 1) {
+    uint32_t nib[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) nib[j] = ((fd[j] & 3u) << 2) | ((fd[j] >> 16) & 3u);
+    f0 = ((nib[0] << 4) | nib[1]) | (((nib[2] << 4) | nib[3]) << 8);
+  } else {
+    uint32_t pr[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pr[j] = ((fd[j] & 1u) << 1) | ((fd[j] >> 16) & 1u);
+    f0 = (pr[0] << 6) | (pr[1] << 4) | (pr[2] << 2) | pr[3];
+  }
+}
+
+template <int S>
+__device__ __forceinline__ void store_fields(uint8_t *dst, uint32_t f0, uint32_t f1) {
+  if (S == 7) *reinterpret_cast<uint2 *>(dst) = make_uint2(f0, f1);
+  else if (S == 3) *reinterpret_cast<uint32_t *>(dst) = f0;
+  else if (S == 1) *reinterpret_cast<uint16_t *>(dst) = (uint16_t)f0;
+  else *dst = (uint8_t)f0;
+}
+
+template <int S>
+__global__ void __launch_bounds__(kHistThreads)
+bf16_histogram_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t *__restrict__ hist) {
+  __shared__ uint32_t sh[kHistWarps][256];
+  for (int i = threadIdx.x; i < kHistWarps * 256; i += kHistThreads) (&sh[0][0])[i] = 0;
+  __syncthreads();
+  uint32_t *mine = sh[threadIdx.x >> 5];
+  const uint64_t n_vec = n / 8;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint4 *v = reinterpret_cast<const uint4 *>(in);
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    const uint4 q = __ldg(v + i);          // read again by the encode kernel: keep it in L2
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t lo, hi, f0, f1;
+    split8<S>(w, lo, hi, f0, f1);
+    // runs of equal exponents are common: count them locally
+    const uint32_t quad[2] = {lo, hi};
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t b0 = quad[k] & 0xFF, b1 = (quad[k] >> 8) & 0xFF, b2 = (quad[k] >> 16) & 0xFF,
+                     b3 = quad[k] >> 24;
+      if (b0 == b1 && b1 == b2 && b2 == b3) {
+        atomicAdd(&mine[b0], 4u);
+      } else {
+        atomicAdd(&mine[b0], 1u);
+        atomicAdd(&mine[b1], 1u);
+        atomicAdd(&mine[b2], 1u);
+        atomicAdd(&mine[b3], 1u);
+      }
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (uint64_t i = n_vec * 8; i < n; ++i) atomicAdd(&mine[exp_of<S>(in[i])], 1u);
+  __syncthreads();
+  for (int b = threadIdx.x; b < 256; b += kHistThreads) {
+    uint32_t t = 0;
+#pragma unroll
+    for (int w = 0; w < kHistWarps; ++w) t += sh[w][b];
+    if (t) atomicAdd(&hist[b], t);
+  }
+}
+
+// Matrix element behind stream element e (see the operand order in the decoder).
+__device__ __forceinline__ uint64_t source_index(uint64_t e, uint32_t cols) {
+  if (!cols) return e;
+  const uint64_t block = e >> 8;
+  const uint32_t w = (uint32_t)e & 255u;
+  const uint32_t spr = cols >> 6;
+  const uint64_t g = block / spr;
+  const uint32_t kb = (uint32_t)(block - g * spr);
+  return (4 * g + (w >> 6)) * cols + kb * 64u + (w & 63u);
+}
+
+// The 8 stream elements from e0 (a multiple of 8) as exponent bytes (lo: elements
+// 0-3, hi: 4-7, first element in the low byte) and packed fields; elements past n
+// give the pad symbol and zero fields.  `store` writes the (S+1) bytes of fields
+// (or as many as hold elements that exist).
+template <int S>
+__device__ __forceinline__ void load_group(const uint16_t *__restrict__ in, uint64_t e0, uint64_t n,
+                                           uint32_t cols, uint32_t pad, uint8_t *__restrict__ frac_out,
+                                           bool store, uint32_t &lo, uint32_t &hi) {
+  constexpr int FB = S + 1;
+  uint32_t val[8];
+  const uint32_t valid = e0 + 8 <= n ? 8u : (e0 < n ? (uint32_t)(n - e0) : 0u);
+  if (valid == 8) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4 *>(in + source_index(e0, cols)));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      val[2 * k] = w[k] & 0xFFFFu;
+      val[2 * k + 1] = w[k] >> 16;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) val[k] = (uint32_t)k < valid ? in[source_index(e0 + k, cols)] : 0u;
+  }
+  uint64_t packed = 0;        // first element in the top bits
+  lo = hi = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    uint32_t ex;
+    uint32_t field;
+    {
+      const uint32_t sign = (val[k] >> 15) & 1u;
+      const uint32_t mag = val[k] & 0x7FFFu;
+      uint32_t keep = mag >> (7 - S);
+      if (S < 7) keep += (mag >> (6 - S)) & 1u;
+      keep &= (1u << (8 + S)) - 1u;
+      ex = keep >> S;
+      field = (sign << S) | (keep & ((1u << S) - 1u));
+    }
+    if ((uint32_t)k >= valid) {
+      ex = pad;
+      field = 0;
+    }
+    packed = (packed << FB) | field;
+    if (k < 4) lo |= ex << (8 * k); else hi |= ex << (8 * (k - 4));
+  }
+  if (store && valid) {
+    uint8_t *dst = frac_out + e0 * FB / 8;
+    if (valid == 8) {
+      if (S == 7) {
+        const uint32_t a = (uint32_t)(packed >> 32), b = (uint32_t)packed;
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(__byte_perm(a, 0, 0x0123), __byte_perm(b, 0, 0x0123));
+      } else if (S == 3) {
+        *reinterpret_cast<uint32_t *>(dst) = __byte_perm((uint32_t)packed, 0, 0x0123);
+      } else if (S == 1) {
+        *reinterpret_cast<uint16_t *>(dst) = (uint16_t)__byte_perm((uint32_t)packed, 0, 0x3301);
+      } else {
+        *dst = (uint8_t)packed;
+      }
+    } else {
+      const uint32_t bytes = (valid * FB + 7) / 8;
+      for (uint32_t b = 0; b < bytes; ++b) dst[b] = (uint8_t)(packed >> (8 * (FB - 1 - b)));
+    }
+  }
+}
+
+// encode_step with the word going to shared memory (16-bit places from `slice`).
+__device__ __forceinline__ void encode_step_sh(uint32_t &x, int32_t &idx, uint32_t src, uint32_t sel,
+                                               uint32_t tab_addr, uint32_t slice, uint32_t pow_m) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 s, a, xm, rc, nf, cm, q, r0, r1, j;\n\t"
+      ".reg .pred p, g;\n\t"
+      "prmt.b32 s, %2, 0, %3;\n\t"
+      "mad.lo.u32 a, s, 16, %4;\n\t"
+      "ld.shared.v4.u32 {xm, rc, nf, cm}, [a];\n\t"
+      "setp.ge.u32 p, %0, xm;\n\t"
+      "max.s32 j, %1, 1;\n\t"
+      "@p mad.lo.u32 j, j, 2, %5;\n\t"
+      "@p st.shared.u16 [j], %0;\n\t"
+      "@p shr.u32 %0, %0, 16;\n\t"
+      "@p sub.s32 %1, %1, 1;\n\t"
+      "mul.hi.u32 q, %0, rc;\n\t"
+      "mad.lo.u32 r0, q, nf, %0;\n\t"
+      "add.u32 r1, r0, nf;\n\t"
+      "setp.ge.s32 g, r1, 0;\n\t"
+      "@g add.u32 q, q, 1;\n\t"
+      "@g mov.b32 r0, r1;\n\t"
+      "add.u32 r0, r0, cm;\n\t"
+      "mad.lo.u32 %0, q, %6, r0;\n\t"
+      "}"
+      : "+r"(x), "+r"(idx)
+      : "r"(src), "r"(sel), "r"(tab_addr), "r"(slice), "r"(pow_m)
+      : "memory");
+}
+
+// Second coding of a unit whose words did not fit the shared-memory slices: the
+// lengths are known from the first attempt, so every word goes straight to its
+// final place in the slot (global memory).
+template <int S>
+__device__ __noinline__ void encode_unit_in_place(const uint16_t *__restrict__ in, uint64_t n,
+                                                  uint32_t LS, uint32_t cols, uint64_t first,
+                                                  uint32_t pad, uint32_t tab_addr, uint32_t pow_m,
+                                                  uint16_t *slot, uint32_t offset, uint32_t words,
+                                                  uint32_t padded, uint32_t lane) {
+  // the lane's stream occupies slot[offset .. offset + padded); words are emitted
+  // backwards from offset + words - 1, the state ends up in the first two places
+  uint16_t *mine = slot + offset;
+  int32_t idx = (int32_t)words - 1;
+  uint32_t x = kStateLow;
+  for (int32_t blk = (int32_t)(LS / 8) - 1; blk >= 0; --blk) {
+    uint32_t lo, hi;
+    load_group<S>(in, first + (uint64_t)blk * 256 + lane * 8, n, cols, pad, nullptr, false, lo, hi);
+#pragma unroll
+    for (int t = 7; t >= 0; --t)
+      encode_step(x, idx, t < 4 ? lo : hi, 0x4440u | (uint32_t)(t & 3), tab_addr, mine, pow_m);
+  }
+  mine[0] = (uint16_t)(x & 0xFFFFu);
+  mine[1] = (uint16_t)(x >> 16);
+  for (uint32_t k = words; k < padded; ++k) mine[k] = 0;
+}
+
+template <int S>
+__global__ void __launch_bounds__(kFusedWarps * 32)
+bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uint32_t n_units,
+                   uint32_t cols, const uint32_t *__restrict__ enc_tab_g,
+                   const uint32_t *__restrict__ misc, uint32_t cap_s,
+                   uint8_t *__restrict__ frac_out, uint32_t *__restrict__ unit_words,
+                   uint8_t *__restrict__ slots, uint32_t slot_stride) {
+  extern __shared__ __align__(16) uint8_t enc_smem[];
+  uint4 *tab = reinterpret_cast<uint4 *>(enc_smem);
+  const uint32_t pb = misc[1];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    const uint32_t e = enc_tab_g[i];
+    const uint32_t fr = e & 0xFFFFu;
+    const uint32_t rc = fr > 1 ? (uint32_t)((1ull << 32) / fr) : 0xFFFFFFFFu;
+    tab[i] = make_uint4(fr << (32 - pb), rc, 0u - fr, e >> 16);
+  }
+  __syncthreads();
+  const uint32_t pad = misc[0];
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t lenq = len_quantum(LS);
+  const uint32_t cap = lane_cap_words(LS);
+  const uint64_t U = 32ull * LS;
+  const uint32_t tab_addr = (uint32_t)__cvta_generic_to_shared(tab);
+  const uint32_t pow_m = 1u << pb;
+  // a chain's cell: 16 words of lane lengths, then 32 slices of cap_s words one word apart
+  const uint32_t sstride = cap_s + 1;
+  const uint32_t cell_words = (16 + 32 * sstride + 7) & ~7u;
+  uint16_t *cell0 = reinterpret_cast<uint16_t *>(enc_smem + 4096) +
+                    (uint64_t)(warp * kFusedChains) * cell_words;
+  const uint32_t n_warps = blockDim.x >> 5;
+  const uint32_t n_blocks = LS / 8;
+  const uint32_t groups = (n_units + kFusedChains - 1) / kFusedChains;
+  for (uint32_t gq = blockIdx.x * n_warps + warp; gq < groups; gq += gridDim.x * n_warps) {
+    uint32_t u[kFusedChains];
+    uint64_t first[kFusedChains];
+    bool live[kFusedChains];
+    uint32_t x[kFusedChains], slice[kFusedChains];
+    int32_t idx[kFusedChains];
+#pragma unroll
+    for (int c = 0; c < kFusedChains; ++c) {
+      u[c] = gq * kFusedChains + c;
+      live[c] = u[c] < n_units;
+      first[c] = (uint64_t)u[c] * U;
+      x[c] = kStateLow;
+      idx[c] = (int32_t)cap_s - 1;
+      slice[c] = (uint32_t)__cvta_generic_to_shared(cell0 + c * cell_words + 16 + lane * sstride);
+    }
+    // Whole units walk two pointers down, block by block (in operand order a unit's
+    // blocks are 64 elements apart in the lane's row; otherwise 256); only the tensor's
+    // last unit can be ragged and takes the guarded loads.
+    bool whole = true;
+    const uint16_t *src[kFusedChains];
+    uint8_t *fdst[kFusedChains];
+#pragma unroll
+    for (int c = 0; c < kFusedChains; ++c) {
+      if (live[c] && first[c] + U > n) whole = false;
+      const uint64_t e_last = first[c] + (uint64_t)(n_blocks - 1) * 256 + lane * 8;
+      src[c] = in + (live[c] && first[c] + U <= n ? source_index(e_last, cols) : 0);
+      fdst[c] = frac_out + (live[c] ? e_last * (S + 1) / 8 : 0);
+    }
+    const uint32_t step = cols ? 64u : 256u;
+    if (whole) {
+      for (int32_t blk = (int32_t)n_blocks - 1; blk >= 0; --blk) {
+        uint32_t lo[kFusedChains], hi[kFusedChains];
+#pragma unroll
+        for (int c = 0; c < kFusedChains; ++c) {
+          lo[c] = hi[c] = 0;
+          if (live[c]) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4 *>(src[c]));
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            uint32_t f0, f1;
+            split8<S>(w, lo[c], hi[c], f0, f1);
+            store_fields<S>(fdst[c], f0, f1);
+            src[c] -= step;
+            fdst[c] -= 32 * (S + 1);
+          }
+        }
+#pragma unroll
+        for (int t = 7; t >= 0; --t) {
+#pragma unroll
+          for (int c = 0; c < kFusedChains; ++c)
+            encode_step_sh(x[c], idx[c], t < 4 ? lo[c] : hi[c], 0x4440u | (uint32_t)(t & 3),
+                           tab_addr, slice[c], pow_m);
+        }
+      }
+    } else {
+      for (int32_t blk = (int32_t)n_blocks - 1; blk >= 0; --blk) {
+        uint32_t lo[kFusedChains], hi[kFusedChains];
+#pragma unroll
+        for (int c = 0; c < kFusedChains; ++c) {
+          lo[c] = hi[c] = 0;
+          if (live[c])
+            load_group<S>(in, first[c] + (uint64_t)blk * 256 + lane * 8, n, cols, pad, frac_out,
+                          true, lo[c], hi[c]);
+        }
+#pragma unroll
+        for (int t = 7; t >= 0; --t) {
+#pragma unroll
+          for (int c = 0; c < kFusedChains; ++c)
+            encode_step_sh(x[c], idx[c], t < 4 ? lo[c] : hi[c], 0x4440u | (uint32_t)(t & 3),
+                           tab_addr, slice[c], pow_m);
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kFusedChains; ++c) {
+      if (!live[c]) continue;             // same verdict in every lane
+      uint16_t *cell = cell0 + c * cell_words;
+      const uint64_t count = (n - first[c] < U) ? (n - first[c]) : U;
+      const uint32_t emitted = (uint32_t)((int32_t)cap_s - 1 - idx[c]);
+      const uint32_t words = emitted + 2;
+      const uint32_t q = (words + lenq - 1) / lenq;
+      const uint32_t padded = q * lenq;
+      uint32_t incl = padded;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (lane >= (uint32_t)o) incl += v;
+      }
+      const uint32_t total = 16u + __shfl_sync(0xFFFFFFFFu, incl, 31);
+      const uint64_t raw_words = (count + 1) / 2;
+      const bool too_long = __any_sync(0xFFFFFFFFu, words > cap);       // the format's own limit
+      const bool raw = too_long || total >= raw_words;
+      if (lane == 0) unit_words[u[c]] = raw ? ((uint32_t)raw_words | kRawFlag) : total;
+      if (raw) continue;                  // placed from the input by place_units_kernel
+      uint16_t *slot = reinterpret_cast<uint16_t *>(slots + (uint64_t)u[c] * slot_stride);
+      if (__any_sync(0xFFFFFFFFu, words > cap_s)) {
+        // did not fit the slices: code it again, straight into the slot
+        reinterpret_cast<uint8_t *>(slot)[lane] = (uint8_t)q;
+        encode_unit_in_place<S>(in, n, LS, cols, first[c], pad, tab_addr, pow_m, slot,
+                                16 + incl - padded, words, padded, lane);
+        continue;
+      }
+      // state in front of the emitted words, then squeeze the 32 streams together
+      uint16_t *mine = cell + 16 + lane * sstride;
+      mine[cap_s - emitted - 2] = (uint16_t)(x[c] & 0xFFFFu);
+      mine[cap_s - emitted - 1] = (uint16_t)(x[c] >> 16);
+      __syncwarp();
+      reinterpret_cast<uint8_t *>(cell)[lane] = (uint8_t)q;
+      uint32_t p = 16;
+      for (uint32_t j = 0; j < 32; ++j) {
+        const uint32_t wj = __shfl_sync(0xFFFFFFFFu, words, j);
+        const uint32_t pj = __shfl_sync(0xFFFFFFFFu, padded, j);
+        const uint32_t from = 16 + j * sstride + cap_s - wj;
+        for (uint32_t k0 = 0; k0 < pj; k0 += 32) {
+          const uint32_t k = k0 + lane;
+          const uint16_t v = (k < wj) ? cell[from + k] : (uint16_t)0;
+          __syncwarp();
+          if (k < pj) cell[p + k] = v;
+          __syncwarp();
+        }
+        p += pj;
+      }
+      // p == total; the cell and the slot are 16-byte aligned
+      const uint4 *c4 = reinterpret_cast<const uint4 *>(cell);
+      uint4 *d4 = reinterpret_cast<uint4 *>(slot);
+      for (uint32_t k = lane; k < (total + 7) / 8; k += 32) d4[k] = c4[k];
+      __syncwarp();
+    }
+  }
+}
+
+// Every unit to its place in the payload: coded units from their slots, raw units
+// (exponent bytes as they are) from the input.
+template <int S>
+__global__ void __launch_bounds__(128)
+place_units_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uint32_t n_units,
+                   uint32_t cols, const uint8_t *__restrict__ slots, uint32_t slot_stride,
+                   uint8_t *__restrict__ container) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t U = 32ull * LS;
+  const uint32_t *offsets = reinterpret_cast<const uint32_t *>(container + kOffsetsOffset);
+  uint16_t *payload = reinterpret_cast<uint16_t *>(container + payload_offset(n_units));
+  for (uint32_t u = blockIdx.x * 4 + (threadIdx.x >> 5); u < n_units; u += gridDim.x * 4) {
+    const uint32_t off = offsets[u];
+    const uint32_t w0 = off & ~kRawFlag;
+    uint16_t *dst = payload + w0;
+    if (off & kRawFlag) {
+      const uint64_t first = (uint64_t)u * U;
+      const uint64_t count = (n - first < U) ? (n - first) : U;
+      uint8_t *d8 = reinterpret_cast<uint8_t *>(dst);
+      for (uint64_t i = lane; i < count; i += 32)
+        d8[i] = (uint8_t)exp_of<S>(in[source_index(first + i, cols)]);
+      if ((count & 1) && lane == 0) d8[count] = 0;
+      continue;
+    }
+    const uint32_t words = (offsets[u + 1] & ~kRawFlag) - w0;
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(slots + (uint64_t)u * slot_stride);
+    if ((w0 & 1) == 0) {
+      uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+      for (uint32_t k = lane; k < words / 2; k += 32) d32[k] = src[k];
+      if ((words & 1) && lane == 0)
+        dst[words - 1] = reinterpret_cast<const uint16_t *>(src)[words - 1];
+    } else {
+      // the destination starts on an odd word: one 16-bit store, then 32-bit stores of
+      // source words shifted by half a word
+      if (lane == 0) dst[0] = reinterpret_cast<const uint16_t *>(src)[0];
+      uint32_t *d32 = reinterpret_cast<uint32_t *>(dst + 1);
+      const uint32_t pairs = (words - 1) / 2;
+      for (uint32_t k = lane; k < pairs; k += 32)
+        d32[k] = __funnelshift_r(src[k], src[k + 1], 16);
+      if (((words - 1) & 1) && lane == 0)
+        dst[words - 1] = reinterpret_cast<const uint16_t *>(src)[words - 1];
+    }
+  }
+}
+
+struct FusedLayout {
+  uint64_t unit_words, slots, total;
+  uint32_t slot_stride, cap_s;
+};
+
+__host__ __device__ inline FusedLayout fused_layout(uint64_t n, uint32_t LS) {
+  const uint64_t nu = unit_count(n, LS);
+  const uint32_t cap = lane_cap_words(LS);
+  FusedLayout L;
+  L.unit_words = kScratchUnits;
+  // a slot holds a coded unit of any admissible length (one word past the end may be read
+  // by the half-word-shifted copy)
+  L.slot_stride = (uint32_t)align16((16ull + 32ull * cap) * 2 + 4);
+  L.slots = align16(L.unit_words + 4 * (nu + 1));
+  L.total = align16(L.slots + nu * (uint64_t)L.slot_stride) + 16;
+  uint32_t cs = LS / 4 + 2;              // 4 bits per symbol and the state
+  L.cap_s = cs < cap ? cs : cap;
+  return L;
+}
+
+template <int S>
+static int compress_fused(const void *in, uint64_t n, uint32_t LS, uint32_t cols, void *frac_out,
+                          void *container, uint64_t container_cap, void *scratch,
+                          uint64_t scratch_bytes, cudaStream_t st, uint32_t low_pb) {
+  const FusedLayout L = fused_layout(n, LS);
+  if (scratch_bytes < L.total) {
+    set_error("compress: scratch of %llu bytes is smaller than the %llu required",
+              (unsigned long long)scratch_bytes, (unsigned long long)L.total);
+    return NZ_E_CAPACITY;
+  }
+  if (container_cap < container_bound(n, LS)) {
+    set_error("compress: container capacity %llu is below the bound %llu",
+              (unsigned long long)container_cap, (unsigned long long)container_bound(n, LS));
+    return NZ_E_CAPACITY;
+  }
+  uint8_t *sc = (uint8_t *)scratch;
+  uint8_t *cont = (uint8_t *)container;
+  const uint32_t nu = (uint32_t)unit_count(n, LS);
+  NZ_CUDA_TRY(cudaMemsetAsync(sc + kScratchHist, 0, 1024, st));
+  if (n) {
+    uint64_t blocks = (n / 8 + kHistThreads - 1) / kHistThreads;
+    const uint64_t capb = (uint64_t)sm_count() * 8;
+    if (blocks > capb) blocks = capb;
+    if (blocks == 0) blocks = 1;
+    bf16_histogram_kernel<S><<<(unsigned)blocks, kHistThreads, 0, st>>>(
+        (const uint16_t *)in, n, (uint32_t *)(sc + kScratchHist));
+    NZ_LAUNCH_CHECK("bf16_histogram_kernel");
+  }
+  normalize_kernel<<<1, 256, 0, st>>>((const uint32_t *)(sc + kScratchHist),
+                                      (uint16_t *)(sc + kScratchFreq),
+                                      (uint32_t *)(sc + kScratchTab),
+                                      (uint32_t *)(sc + kScratchMisc),
+                                      (uint16_t *)(cont + kFreqOffset), low_pb);
+  NZ_LAUNCH_CHECK("normalize_kernel");
+  if (nu) {
+    const uint32_t cell_words = (16 + 32 * (L.cap_s + 1) + 7) & ~7u;
+    // up to 8 warps per block; long lane streams get fewer so that a block still fits
+    uint32_t warps = (kMaxDynamicSmem - 4096) / (kFusedChains * cell_words * 2);
+    if (warps > (uint32_t)kFusedWarps) warps = kFusedWarps;
+    if (warps == 0) warps = 1;
+    const uint32_t smem = 4096 + warps * kFusedChains * cell_words * 2;
+    auto kern = bf16_encode_kernel<S>;
+    {
+      static std::mutex mu;
+      static bool opted[kMaxDeviceOrdinals] = {};
+      int dev = 0;
+      NZ_CUDA_TRY(cudaGetDevice(&dev));
+      std::lock_guard<std::mutex> lock(mu);
+      if (dev < 0 || dev >= kMaxDeviceOrdinals || !opted[dev]) {
+        NZ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kMaxDynamicSmem));
+        if (dev >= 0 && dev < kMaxDeviceOrdinals) opted[dev] = true;
+      }
+    }
+    if (smem > kMaxDynamicSmem) {
+      set_error("compress: lane_symbols %u needs %u bytes of shared memory per block", LS, smem);
+      return NZ_E_ARG;
+    }
+    const uint32_t groups = (nu + kFusedChains - 1) / kFusedChains;
+    uint32_t blocks = (groups + warps - 1) / warps;
+    const uint32_t per_sm = kMaxDynamicSmem / (smem + 1024) ? kMaxDynamicSmem / (smem + 1024) : 1;
+    const uint32_t capb = (uint32_t)sm_count() * per_sm;
+    if (blocks > capb) blocks = capb;
+    kern<<<blocks, warps * 32, smem, st>>>(
+        (const uint16_t *)in, n, LS, nu, cols, (const uint32_t *)(sc + kScratchTab),
+        (const uint32_t *)(sc + kScratchMisc), L.cap_s, (uint8_t *)frac_out,
+        (uint32_t *)(sc + L.unit_words), sc + L.slots, L.slot_stride);
+    NZ_LAUNCH_CHECK("bf16_encode_kernel");
+  }
+  scan_kernel<<<1, 1024, 0, st>>>((const uint32_t *)(sc + L.unit_words), nu, n, LS,
+                                  (const uint32_t *)(sc + kScratchMisc), cont);
+  NZ_LAUNCH_CHECK("scan_kernel");
+  if (nu) {
+    uint32_t blocks = (nu + 3) / 4;
+    const uint32_t capb = (uint32_t)sm_count() * 16;
+    if (blocks > capb) blocks = capb;
+    place_units_kernel<S><<<blocks, 128, 0, st>>>((const uint16_t *)in, n, LS, nu, cols,
+                                                  sc + L.slots, L.slot_stride, cont);
+    NZ_LAUNCH_CHECK("place_units_kernel");
+  }
+  return NZ_OK;
+}
+
+uint64_t compress_fused_scratch_bytes(uint64_t n, uint32_t LS) { return fused_layout(n, LS).total; }
+
+// bf16[n] (a [n / cols, cols] matrix to be stored in operand order when cols != 0)
+// -> fractions + container.
+int compress_bf16_fused(const void *in, uint64_t n, int precision, uint32_t LS, uint32_t cols,
+                        void *frac_out, void *container, uint64_t container_cap, void *scratch,
+                        uint64_t scratch_bytes, cudaStream_t st) {
+  // Lossless tensors keep 8 fraction bits per element, so the exponent stream is
+  // a quarter of what is stored: 9-bit probabilities cost 0.2 % of the stored
+  // size there and let the decoder keep one table copy per shared-memory bank.
+  const uint32_t low_pb = precision == 7 ? kMinProbBits : kDefaultLowProbBits;
+  switch (precision) {
+    case 0: return compress_fused<0>(in, n, LS, cols, frac_out, container, container_cap, scratch, scratch_bytes, st, low_pb);
+    case 1: return compress_fused<1>(in, n, LS, cols, frac_out, container, container_cap, scratch, scratch_bytes, st, low_pb);
+    case 3: return compress_fused<3>(in, n, LS, cols, frac_out, container, container_cap, scratch, scratch_bytes, st, low_pb);
+    default: return compress_fused<7>(in, n, LS, cols, frac_out, container, container_cap, scratch, scratch_bytes, st, low_pb);
+  }
+}
+
 }  // namespace nz
 
 static int check_encode_args(const char *who, uint64_t n, uint32_t S) {

@@ -474,3 +474,25 @@ def test_unit_gather_with_raw_units_bad_numbers_and_empty_list():
     assert (got[1] == 0x1234).all()
     out, status = A.decompress_units(cont, frac, n, 7, S, [], mw)
     assert status == 0 and out.numel() == 0
+
+
+@pytest.mark.parametrize("s", PRECISIONS)
+@pytest.mark.parametrize("span", (48, 64, 120, 250))
+def test_compress_wide_exponent_alphabets_match_oracle(s, span):
+    """Exponents spread evenly over `span` values need 5.6 to 8 bits per symbol: lane
+    streams longer than the coder's shared-memory slices (units coded a second time,
+    straight into their slots), and from 8 bits on units stored raw.  Ragged size."""
+    n = 3 * 8192 + 1234
+    rng = np.random.default_rng(span + s)
+    exp = rng.integers(2, 2 + span, size=n, dtype=np.uint16)
+    rest = rng.integers(0, 256, size=n, dtype=np.uint16)
+    bits = ((rest & 0x80) << 8) | (exp << 7) | (rest & 0x7F)
+    x = A.from_bits(bits)
+    for S in (O.default_lane_symbols(s), 64, 1024):
+        cont, frac, mw = A.compress(x, s, S)
+        c_ref, f_ref = O.compress_bf16(bits, s, S)
+        assert np.array_equal(frac.cpu().numpy(), f_ref), (s, span, S)
+        assert np.array_equal(cont.cpu().numpy(), c_ref), (s, span, S)
+        out, status = A.decompress(cont, frac, n, s, S, mw, canon=True)
+        assert status == 0
+        assert np.array_equal(A.to_bits(out), O.decompress_bf16(c_ref, f_ref, n, s, canonical_nan=True))
