@@ -44,6 +44,11 @@ class _Entry:
     normalizers: Optional[torch.Tensor] = None   # uint8, one byte per group (normalizer_size > 0)
     stamp: int = 0            # number of the library operation that wrote these bytes
     operand_cols: int = 0     # > 0: a [numel / operand_cols, operand_cols] matrix in operand order
+    # While a write is still in flight the container sits in its worst-case-sized buffer;
+    # `pending` = (pinned copy of the header, event after that copy).  Once the event has
+    # completed the entry is settled: right-sized container, real max_unit_words.
+    pending: Optional[tuple] = None
+    version: int = 0          # bumped when the container tensor is replaced
 
 
 # Every operation that any backend of this process enqueues gets a number.  A decode
@@ -65,12 +70,13 @@ def _stable_flag(entries, op: int) -> int:
 
 class _Batch:
     """Argument blocks of a batched decode, rebuilt when an entry is replaced."""
-    __slots__ = ("names", "outs", "entries", "blocks", "lane_symbols")
+    __slots__ = ("names", "outs", "entries", "versions", "blocks", "lane_symbols")
 
     def __init__(self, names, outs) -> None:
         self.names = list(names)
         self.outs = list(outs)
         self.entries = []
+        self.versions = []
         self.blocks = None
         self.lane_symbols = 0
 
@@ -136,6 +142,8 @@ class CodecBackend:
         # (nz_linear_bf16) on operand-order weights; 0 = always decode, then library GEMM
         self.fused_linear_max_rows = 0
         self._lin_ws: Optional[torch.Tensor] = None
+        # True: `write` waits for the compressed size like the reference does
+        self.sync_writes = False
 
     # -- helpers ---------------------------------------------------------
     def _ensure_device(self) -> None:
@@ -199,12 +207,8 @@ class CodecBackend:
             _lib.check(L.nz_compress_bf16_operand(_ptr(flat), rows, cols, self.precision, S,
                                                   _ptr(frac), _ptr(staging), cap, _ptr(scratch),
                                                   scratch.numel(), st))
-            total = _lib._u64(0)
-            max_words = _lib._u32(0)
-            _lib.check(L.nz_container_bytes(_ptr(staging), total, max_words, st))
-            container = staging[: total.value].clone()
-            self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac,
-                                       None, _next_op(), cols)
+            self._cache[name] = self._finish_write(
+                _Entry(n, tensor.dtype, S, 0, staging, frac, None, _next_op(), cols))
             return
         normalizers = None
         if self.normalizer_size:
@@ -222,16 +226,51 @@ class CodecBackend:
         scratch = self._scratch_for(scratch_bytes)
         _lib.check(L.nz_compress_bf16(_ptr(flat), n, self.precision, S, _ptr(frac), _ptr(staging),
                                       cap, _ptr(scratch), scratch.numel(), st))
-        total = _lib._u64(0)
-        max_words = _lib._u32(0)
-        _lib.check(L.nz_container_bytes(_ptr(staging), total, max_words, st))
-        container = staging[: total.value].clone()
-        self._cache[name] = _Entry(n, tensor.dtype, S, int(max_words.value), container, frac,
-                                   normalizers, _next_op())
+        self._cache[name] = self._finish_write(
+            _Entry(n, tensor.dtype, S, 0, staging, frac, normalizers, _next_op()))
+
+    # -- settling a write without stalling the host ----------------------------
+    def _finish_write(self, entry: _Entry) -> _Entry:
+        """The reference reads the compressed size back right after compressing, which
+        blocks the host (cuda/high_level.cu:114-115).  Here the 64-byte container header
+        is copied to pinned memory asynchronously; the entry is usable at once (decoding
+        from the worst-case-sized buffer) and is right-sized the first time it is touched
+        after that copy has completed.  `sync_writes = True` restores the blocking form."""
+        header = torch.empty(64, dtype=torch.uint8).pin_memory()
+        header.copy_(entry.container[:64], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        entry.pending = (header, event)
+        if self.sync_writes:
+            self._settle(entry, block=True)
+        return entry
+
+    def _settle(self, entry: _Entry, block: bool) -> None:
+        if entry.pending is None:
+            return
+        header, event = entry.pending
+        if block:
+            event.synchronize()
+        elif not event.query():
+            return
+        words = header.view(torch.int32)
+        if int(words[0]) != 0x31525A4E:
+            raise _lib.NeuzipError("write produced no NZR1 container")
+        total = int(header.view(torch.int64)[6])
+        entry.max_unit_words = int(words[15])
+        entry.container = entry.container[:total].clone()     # enqueued after the write
+        entry.pending = None
+        entry.version += 1
+
+    def _get(self, name: str) -> Optional[_Entry]:
+        entry = self._cache.get(name)
+        if entry is not None and entry.pending is not None:
+            self._settle(entry, block=False)
+        return entry
 
     def read(self, name: str) -> torch.Tensor:
         """cuda/high_level.cu:223-250 (+ _decompress_and_merge :164-206); no host sync."""
-        entry = self._cache.get(name)
+        entry = self._get(name)
         if entry is None:
             raise RuntimeError("Data not found")
         out = torch.empty(entry.numel, dtype=torch.bfloat16, device="cuda")
@@ -239,7 +278,9 @@ class CodecBackend:
         return out
 
     def read_into(self, name: str, out: torch.Tensor) -> None:
-        entry = self._cache[name]
+        entry = self._get(name)
+        if entry is None:
+            raise RuntimeError("Data not found")
         _next_op()
         if entry.operand_cols:
             _lib.check(self._lib.nz_decompress_bf16_operand(
@@ -261,7 +302,7 @@ class CodecBackend:
         nothing synchronises with the host.  Row numbers outside the table raise at
         the next ``check()``.  The reference decompresses the whole
         table for every lookup (neuzip/nn/embedding.py:30-39)."""
-        entry = self._cache.get(name)
+        entry = self._get(name)
         if entry is None:
             raise RuntimeError("Data not found")
         if row_len <= 0 or entry.numel % row_len:
@@ -303,7 +344,7 @@ class CodecBackend:
         small matrices share the GPU instead of each leaving most SMs idle."""
         entries = []
         for name in names:
-            entry = self._cache.get(name)
+            entry = self._get(name)
             if entry is None:
                 raise RuntimeError("Data not found")
             entries.append(entry)
@@ -345,6 +386,8 @@ class CodecBackend:
 
     def _bind_batch(self, batch: _Batch) -> None:
         entries = [self._cache[n] for n in batch.names]
+        for e in entries:
+            self._settle(e, block=False)
         S = {e.lane_symbols for e in entries}
         if len(S) != 1:
             raise ValueError("a batch must share one lane_symbols value")
@@ -367,11 +410,14 @@ class CodecBackend:
             blocks.append(items)
         # the entries keep their tensors alive as long as the batch refers to them
         batch.entries, batch.blocks, batch.lane_symbols = entries, blocks, S.pop()
+        batch.versions = [e.version for e in entries]
 
     def run_batch(self, batch: _Batch) -> None:
         cache = self._cache
-        for name, entry in zip(batch.names, batch.entries):
-            if cache.get(name) is not entry:       # written, imported or erased since
+        for name, entry, version in zip(batch.names, batch.entries, batch.versions):
+            # written, imported or erased since -- or its write has settled meanwhile
+            if (cache.get(name) is not entry or entry.version != version
+                    or (entry.pending is not None and entry.pending[1].query())):
                 self._bind_batch(batch)
                 break
         items = batch.blocks[1 if _stable_flag(batch.entries, _next_op()) else 0]
@@ -389,6 +435,7 @@ class CodecBackend:
         entry = self._cache.get(name)
         if entry is None:
             return 0
+        self._settle(entry, block=True)
         extra = 0 if entry.normalizers is None else entry.normalizers.numel()
         return entry.container.numel() + entry.fractions.numel() + extra
 
@@ -425,7 +472,7 @@ class CodecBackend:
         limit = self.fused_linear_max_rows
         if not limit:
             return None
-        entry = self._cache.get(name)
+        entry = self._get(name)
         if entry is None or not entry.operand_cols or len(shape) != 2:
             return None
         out_f, in_f = int(shape[0]), int(shape[1])
@@ -470,7 +517,7 @@ class CodecBackend:
         library GEMM, but the order of the sums differs, so the last bit may."""
         if not self.fused_vector_linear:
             return None
-        entry = self._cache.get(name)
+        entry = self._get(name)
         if (entry is None or entry.normalizers is not None or entry.operand_cols
                 or len(shape) != 2):
             return None
@@ -520,6 +567,7 @@ class CodecBackend:
         """The stored form of one tensor as CPU tensors plus the numbers needed to
         decode it; what `nn.Linear.get_extra_state` puts into a state_dict."""
         e = self._cache[name]
+        self._settle(e, block=True)
         return {"format": "NZR1", "precision": self.precision, "numel": e.numel,
                 "lane_symbols": e.lane_symbols, "max_unit_words": e.max_unit_words,
                 "container": e.container.cpu(), "fractions": e.fractions.cpu(),
@@ -552,7 +600,9 @@ class CodecBackend:
         self._cache.pop(name, None)
 
     def entry(self, name: str) -> _Entry:
-        return self._cache[name]
+        entry = self._cache[name]
+        self._settle(entry, block=True)
+        return entry
 
     def names(self):
         return list(self._cache)

@@ -910,20 +910,25 @@ bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
     }
     const uint32_t step = cols ? 64u : 256u;
     if (whole) {
+      // the next block's 16 bytes are requested before the current block's 8 symbols are
+      // coded, so the load latency hides behind them
+      uint4 nxt[kFusedChains];
+#pragma unroll
+      for (int c = 0; c < kFusedChains; ++c) {
+        nxt[c] = make_uint4(0, 0, 0, 0);
+        if (live[c]) nxt[c] = __ldg(reinterpret_cast<const uint4 *>(src[c]));
+      }
       for (int32_t blk = (int32_t)n_blocks - 1; blk >= 0; --blk) {
         uint32_t lo[kFusedChains], hi[kFusedChains];
 #pragma unroll
         for (int c = 0; c < kFusedChains; ++c) {
-          lo[c] = hi[c] = 0;
-          if (live[c]) {
-            const uint4 q = __ldg(reinterpret_cast<const uint4 *>(src[c]));
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-            uint32_t f0, f1;
-            split8<S>(w, lo[c], hi[c], f0, f1);
-            store_fields<S>(fdst[c], f0, f1);
-            src[c] -= step;
-            fdst[c] -= 32 * (S + 1);
-          }
+          const uint32_t w[4] = {nxt[c].x, nxt[c].y, nxt[c].z, nxt[c].w};
+          src[c] -= step;
+          if (live[c] && blk > 0) nxt[c] = __ldg(reinterpret_cast<const uint4 *>(src[c]));
+          uint32_t f0, f1;
+          split8<S>(w, lo[c], hi[c], f0, f1);
+          if (live[c]) store_fields<S>(fdst[c], f0, f1);
+          fdst[c] -= 32 * (S + 1);
         }
 #pragma unroll
         for (int t = 7; t >= 0; --t) {
@@ -1037,8 +1042,22 @@ place_units_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
     const uint32_t words = (offsets[u + 1] & ~kRawFlag) - w0;
     const uint32_t *src = reinterpret_cast<const uint32_t *>(slots + (uint64_t)u * slot_stride);
     if ((w0 & 1) == 0) {
+      // four independent loads in flight per lane: the copy is latency-bound otherwise
       uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
-      for (uint32_t k = lane; k < words / 2; k += 32) d32[k] = src[k];
+      const uint32_t n32 = words / 2;
+      for (uint32_t k0 = 0; k0 < n32; k0 += 128) {
+        uint32_t v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t k = k0 + 32 * i + lane;
+          v[i] = k < n32 ? __ldcs(src + k) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t k = k0 + 32 * i + lane;
+          if (k < n32) d32[k] = v[i];
+        }
+      }
       if ((words & 1) && lane == 0)
         dst[words - 1] = reinterpret_cast<const uint16_t *>(src)[words - 1];
     } else {
@@ -1047,8 +1066,20 @@ place_units_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
       if (lane == 0) dst[0] = reinterpret_cast<const uint16_t *>(src)[0];
       uint32_t *d32 = reinterpret_cast<uint32_t *>(dst + 1);
       const uint32_t pairs = (words - 1) / 2;
-      for (uint32_t k = lane; k < pairs; k += 32)
-        d32[k] = __funnelshift_r(src[k], src[k + 1], 16);
+      for (uint32_t k0 = 0; k0 < pairs; k0 += 128) {
+        uint32_t a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t k = k0 + 32 * i + lane;
+          a[i] = k < pairs ? __ldcs(src + k) : 0u;
+          b[i] = k < pairs ? __ldcs(src + k + 1) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t k = k0 + 32 * i + lane;
+          if (k < pairs) d32[k] = __funnelshift_r(a[i], b[i], 16);
+        }
+      }
       if (((words - 1) & 1) && lane == 0)
         dst[words - 1] = reinterpret_cast<const uint16_t *>(src)[words - 1];
     }
