@@ -281,18 +281,21 @@ class CodecBackend:
         entry = self._get(name)
         if entry is None:
             raise RuntimeError("Data not found")
-        _next_op()
-        if entry.operand_cols:
-            _lib.check(self._lib.nz_decompress_bf16_operand(
-                _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions),
-                entry.numel // entry.operand_cols, entry.operand_cols, self.precision,
-                entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan), _ptr(out),
-                _ptr(self._status), _stream()))
-            return
-        _lib.check(self._lib.nz_decompress_bf16(
-            _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
-            self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
-            _ptr(out), _ptr(self._status), _stream()))
+        # a batch of one: the batched entry point carries the per-item promise that the
+        # compressed bytes are not fresh, which lets this launch set up while the previous
+        # kernel of the stream drains
+        item = (_lib.DecompressItem * 1)()
+        item[0].container = _ptr(entry.container)
+        item[0].container_bytes = entry.container.numel()
+        item[0].frac_in = _ptr(entry.fractions)
+        item[0].n = entry.numel
+        item[0].max_unit_words = entry.max_unit_words
+        item[0].flags = _stable_flag([entry], _next_op())
+        item[0].out_bf16 = _ptr(out)
+        item[0].operand_cols = entry.operand_cols
+        _lib.check(self._lib.nz_decompress_bf16_batch(
+            item, 1, self.precision, entry.lane_symbols, int(self.canonical_nan),
+            _ptr(self._status), _stream()))
         self._denormalize(entry, out)
 
     def read_rows(self, name: str, rows: torch.Tensor, row_len: int) -> torch.Tensor:

@@ -101,9 +101,20 @@ class Manager:
             return self._be.linear_without_bias(handle, inputs, shape)
         return self._be.linear(handle, inputs, shape, bias)
 
-    def convert(self, module: torch.nn.Module) -> torch.nn.Module:
+    def convert(self, module: torch.nn.Module, tp_rank: Optional[int] = None,
+                tp_world: Optional[int] = None, tp_plan=None, tp_group=None) -> torch.nn.Module:
+        """neuzip/binding.py:105-106.  With ``tp_rank`` / ``tp_world`` (not in the
+        reference) the Linears named in ``tp_plan`` (default: the Llama projections, see
+        neuzip_b200.sharding) keep only this rank's block, row-parallel ones all-reduce
+        their output over ``tp_group``; attention code that derives the head count from
+        the projection width (Hugging Face Llama does) then runs tensor-parallel as is."""
         from .utils import _convert
-        return _convert(self, module)
+        tp = None
+        if tp_world is not None and tp_world > 1:
+            if tp_rank is None or not 0 <= tp_rank < tp_world:
+                raise ValueError("tp_rank must be in [0, tp_world)")
+            tp = (tp_rank, tp_world, tp_plan, tp_group)
+        return _convert(self, module, tp=tp)
 
     def split(self, tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         exp, frac = self._be.split(tensor)

@@ -6,21 +6,45 @@ from .module import Parameter
 
 
 class Linear(torch.nn.Module):
-    def __init__(self, manager, linear: torch.nn.Linear) -> None:
+    def __init__(self, manager, linear: torch.nn.Linear, tp=None) -> None:
+        """`tp = (mode, rank, world_size, group)` (not in the reference) keeps only this
+        rank's block of the weight: rows for mode "column", columns for "row"; a
+        row-parallel Linear adds the ranks' partial outputs with one all-reduce."""
         super().__init__()
         self.manager = manager
-        self.in_features, self.out_features = linear.in_features, linear.out_features
-        self._p = Parameter(manager, linear.weight.data, operand=True)
-        if linear.bias is None:
+        weight, bias = linear.weight.data, (None if linear.bias is None else linear.bias.data)
+        self.reduce_group = None
+        self.reduce_output = False
+        if tp is not None:
+            from ..sharding import shard_linear_weight
+            mode, rank, world, group = tp
+            weight, bias = shard_linear_weight(weight, bias, mode, rank, world)
+            self.reduce_output = mode == "row" and world > 1
+            self.reduce_group = group
+        self.out_features, self.in_features = int(weight.shape[0]), int(weight.shape[1])
+        self._p = Parameter(manager, weight, operand=True)
+        if bias is None:
             self.register_parameter("bias", None)
         else:
-            self.bias = torch.nn.Parameter(linear.bias.data)
+            self.bias = torch.nn.Parameter(bias)
 
     @property
     def weight(self) -> Parameter:
         return self._p
 
     def forward(self, x):
+        y = self._forward_local(x)
+        if self.reduce_output:
+            # partial sums of a row-parallel Linear: one all-reduce over the ranks
+            import torch.distributed as dist
+            if torch.is_grad_enabled() and y.requires_grad:
+                from torch.distributed.nn.functional import all_reduce
+                y = all_reduce(y, group=self.reduce_group)
+            else:
+                dist.all_reduce(y, group=self.reduce_group)
+        return y
+
+    def _forward_local(self, x):
         if not torch.is_grad_enabled():
             staged = self._p.staged()
             if staged is not None:          # decoded ahead for the whole block: a plain linear

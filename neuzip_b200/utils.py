@@ -48,10 +48,15 @@ def _unroll_convert(manager, module):
     return module
 
 
-def _convert(manager, module, prefix=""):
+def _convert(manager, module, prefix="", tp=None):
     """Recursively replace ``nn.Linear`` (and HF ``Conv1D``) children by compressed
     Linears; any child whose name contains ``lm_head`` is left alone and not
-    descended into (neuzip/utils.py:57-68)."""
+    descended into (neuzip/utils.py:57-68).
+
+    ``tp = (rank, world_size, plan, group)`` (not in the reference) makes every Linear
+    whose name is in the plan keep only this rank's block (neuzip_b200.sharding);
+    Linears that the plan does not name are converted whole on every rank."""
+    from .sharding import tp_mode
     convertible = (torch.nn.Linear,) + ((_hf_conv1d_type(),) if _hf_conv1d_type() else ())
     for name, child in list(module.named_children()):
         full_name = f"{prefix}.{name}" if prefix else name
@@ -59,8 +64,13 @@ def _convert(manager, module, prefix=""):
             continue
         if isinstance(child, convertible):
             logger.debug("Converting %s: %s", full_name, child)
-            setattr(module, name, Linear(manager, child))
+            shard = None
+            if tp is not None and tp[1] > 1:
+                mode = tp_mode(name, tp[2])
+                if mode is not None:
+                    shard = (mode, tp[0], tp[1], tp[3])
+            setattr(module, name, Linear(manager, child, tp=shard))
             _delete_module(child)
         else:
-            _convert(manager, child, full_name)
+            _convert(manager, child, full_name, tp)
     return module
