@@ -1,24 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the NeuZip decompress hot path on B200.
 
-Workload ("config 2" of the baseline): a stack of 32 Llama-7B-shaped layer sets
-(4x 4096x4096, 2x 11008x4096, 1x 4096x11008 per layer = 224 bf16 matrices,
-6 476 005 376 elements, 12.95 GB), values N(0, 0.02).  The data are synthetic:
-each matrix is drawn on the GPU from a generator seeded 1000 + 7*layer + j
-(+ 100000*rank), which stands in for the real checkpoints the reference's
-scripts load.
+Headline workload ("config 2" of the baseline list): a stack of 32 Llama-7B-shaped
+layer sets (4x 4096x4096, 2x 11008x4096, 1x 4096x11008 per layer = 224 bf16 matrices,
+6 476 005 376 elements, 12.95 GB), values N(0, 0.02).  The data are synthetic and stand
+in for the checkpoints the reference's scripts load: layer set 0 of rank 0 is drawn
+from the CPU generator seeded 1000 + 7*layer + j and its compressed form is compared
+(CRC-32) with the committed fixture tests/golden/config2_layer0.json; the other layer
+sets are drawn on the GPU from generators with the same seeds (+ 100000 * rank).
 
-A step = one lossless (precision 7) decompress pass over the rank's whole
-stack: 224 calls of nz_decompress_bf16 through the C ABI, compressed inputs
-resident in HBM, every call a different matrix (the pass reads 8.6 GB and writes
-13 GB, far more than the 126 MB L2, so no flush is needed between iterations).
-`value` counts decoded bytes out + compressed bytes in, per second, over all
-ranks (weak scaling: every rank owns a full stack; there is no collective in
-the data path).
+A step = one lossless (precision 7) decompress pass over the rank's stack: 32 calls of
+nz_decompress_bf16_batch through the C ABI, one per layer set (one kernel launch for the
+seven matrices of a layer), compressed inputs resident in HBM, every call a different
+layer set (a pass reads 8.6 GB and writes 13 GB, far more than the 126 MB L2, so no
+flush is needed).  `value` counts decoded bytes out + compressed bytes in, per second,
+over all ranks (weak scaling: every rank owns a full stack; `--shard layers` splits one
+stack over the ranks instead; there is no collective in the data path either way).
 
-Also reported: the lossy sweep (precision 3/1/0), compress throughput, the
-roofline of the decode kernel, a CPU baseline (the OpenMP oracle on a bounded
-sample) and an end-to-end figure with host buffers on both sides.
+Sub-objects of the JSON line: `config1` (one 4096x4096 matrix, one call), the same stack
+with one call per matrix, the lossy sweep with compress throughput, `linear_fused` (the
+fused decode -> tcgen05 GEMM against decode + library GEMM), the roofline of the decode
+kernel, a CPU baseline (the OpenMP oracle on a bounded sample), the end-to-end figure
+with host buffers on both sides and its H2D-only / D2H-only parts, and `model`: tokens/s
+of shortened Llama-shaped models, dense vs compressed (decode, eager and CUDA-graphed;
+AdamW training).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 """
@@ -31,6 +36,7 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -55,11 +61,18 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="layer sets in the stack (32 = config 2)")
+    ap.add_argument("--shard", default="weak", choices=["weak", "layers"],
+                    help="weak: every rank owns a full stack; layers: one stack, layer set l on "
+                         "rank l mod N")
     ap.add_argument("--e2e-layers", type=int, default=2,
                     help="layer sets held in pinned host memory for the end-to-end leg")
+    ap.add_argument("--model-layers", type=int, default=8,
+                    help="transformer layers of the shortened models of the `model` legs")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-linear", action="store_true")
+    ap.add_argument("--no-model", action="store_true")
     return ap.parse_args()
 
 
@@ -74,7 +87,7 @@ def measured_peak():
 
 # --------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -94,9 +107,11 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
-            return
+            return self
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
+        time.sleep(0.25)
+        return self
 
     def _pump(self):
         for line in self.proc.stdout:
@@ -105,6 +120,7 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -126,6 +142,33 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    return vis.split(",")[local_rank] if vis else local_rank
+
+
+def bind_to_gpu_numa(local_rank):
+    """Restrict this process to the CPUs NVML names as local to its GPU, so that the
+    pinned buffers allocated afterwards (first touch) and the copy threads sit on the
+    GPU's NUMA node.  Reads settings only.  Returns a description for the report."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        idx = int(gpu_index(local_rank))
+        handle = pynvml.nvmlDeviceGetHandleByIndex(idx)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = [64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1]
+        allowed = sorted(set(cpus) & os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return {"gpu": idx, "cpus": f"{allowed[0]}-{allowed[-1]}" if allowed else None,
+                "n_cpus": len(allowed)}
+    except Exception as exc:       # no NVML: stay where we are
+        return {"gpu": None, "cpus": None, "n_cpus": len(os.sched_getaffinity(0)),
+                "note": f"not bound ({type(exc).__name__})"}
 
 
 # ------------------------------------------------------------------- workload
@@ -151,8 +194,14 @@ class Stack:
         return sum(n for _, _, n, _, _ in self.items)
 
 
-def build_stacks(L, torch, layers, precisions, rank):
-    """Generate every matrix once, compress it at each precision, drop the original."""
+def crc(t):
+    return zlib.crc32(t.cpu().numpy().tobytes())
+
+
+def build_stacks(L, torch, layer_ids, precisions, rank):
+    """Generate every matrix once, compress it at each precision, drop the original.
+    Layer set 0 of rank 0 comes from the CPU generator and is checked against the
+    committed fixture (input, container and fraction CRC-32s at precision 7)."""
     from neuzip_b200 import _lib
     stacks = {s: Stack(s) for s in precisions}
     st = torch.cuda.current_stream().cuda_stream
@@ -165,6 +214,10 @@ def build_stacks(L, torch, layers, precisions, rank):
     staging = torch.empty(cap_max, dtype=torch.uint8, device="cuda")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gen = torch.Generator(device="cuda")
+    fixture = None
+    if rank == 0 and 0 in layer_ids:
+        with open(os.path.join(ROOT, "tests", "golden", "config2_layer0.json")) as f:
+            fixture = json.load(f)
     # untimed warm-up of the compress pipeline (kernel loading) at every precision
     warm = torch.zeros(1 << 20, dtype=torch.bfloat16, device="cuda")
     for s in precisions:
@@ -175,11 +228,18 @@ def build_stacks(L, torch, layers, precisions, rank):
                                       scratch.numel(), st))
     torch.cuda.synchronize()
     del warm
-    for layer in range(layers):
+    checked = 0
+    for layer in layer_ids:
         for j, shape in enumerate(LAYER_SHAPES):
-            gen.manual_seed(1000 + 7 * layer + j + 100000 * rank)
-            w = (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * 0.02
-                 ).to(torch.bfloat16).view(-1)
+            pinned = fixture is not None and layer == 0
+            if pinned:
+                g = torch.Generator().manual_seed(1000 + 7 * layer + j)
+                w = (torch.randn(shape, generator=g, dtype=torch.float32) * 0.02
+                     ).to(torch.bfloat16).cuda().view(-1)
+            else:
+                gen.manual_seed(1000 + 7 * layer + j + 100000 * rank)
+                w = (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * 0.02
+                     ).to(torch.bfloat16).view(-1)
             n = w.numel()
             for s in precisions:
                 S = int(L.nz_default_lane_symbols(s))
@@ -193,48 +253,48 @@ def build_stacks(L, torch, layers, precisions, rank):
                 _lib.check(L.nz_container_bytes(staging.data_ptr(), total, mw, st))
                 stacks[s].compress_ms += e0.elapsed_time(e1)
                 stacks[s].in_bytes += 2 * n
-                stacks[s].items.append((staging[: total.value].clone(), frac, n, S, int(mw.value)))
+                cont = staging[: total.value].clone()
+                stacks[s].items.append((cont, frac, n, S, int(mw.value)))
+                if pinned and s == 7:
+                    want = fixture["matrices"][j]
+                    assert hex(crc(w.view(torch.int16))) == want["input_crc32"], "workload drifted"
+                    assert cont.numel() == want["container_bytes"], "container size differs from fixture"
+                    assert hex(crc(cont)) == want["container_crc32"], "container differs from fixture"
+                    assert hex(crc(frac)) == want["frac_crc32"], "fractions differ from fixture"
+                    checked += 1
             del w
-    return stacks
+    return stacks, checked
 
 
-def decompress_pass(L, stack, outs, status, st):
-    s = stack.precision
-    k = 0
-    for c, f, n, S, mw in stack.items:
-        rc = L.nz_decompress_bf16(c.data_ptr(), c.numel(), f.data_ptr(), n, s, S, mw, 1,
-                                  outs[k].data_ptr(), status.data_ptr(), st)
-        if rc:
-            from neuzip_b200 import _lib
-            _lib.check(rc)
-        k = (k + 1) % len(outs)
-
-
-def make_batches(stack, outs_per_layer):
-    """One nz_decompress_item array per layer set (7 matrices)."""
+def make_batches(stack, outs_per_layer, single=False):
+    """nz_decompress_item arrays: one per layer set (7 matrices), or one per matrix."""
     from neuzip_b200 import _lib
     per_layer = len(LAYER_SHAPES)
     batches = []
     for base in range(0, len(stack.items), per_layer):
         chunk = stack.items[base:base + per_layer]
-        arr = (_lib.DecompressItem * len(chunk))()
-        for k, (c, f, n, S, mw) in enumerate(chunk):
-            arr[k].container = c.data_ptr()
-            arr[k].container_bytes = c.numel()
-            arr[k].frac_in = f.data_ptr()
-            arr[k].n = n
-            arr[k].max_unit_words = mw
-            # the stack was compressed (and the device synchronised) before any timed pass
-            arr[k].flags = _lib.NZ_ITEM_INPUTS_STABLE
-            arr[k].out_bf16 = outs_per_layer[(base // per_layer) % len(outs_per_layer)][k].data_ptr()
-        batches.append((arr, len(chunk), chunk[0][3]))
+        outs = outs_per_layer[(base // per_layer) % len(outs_per_layer)]
+        groups = [[k] for k in range(len(chunk))] if single else [list(range(len(chunk)))]
+        for group in groups:
+            arr = (_lib.DecompressItem * len(group))()
+            for i, k in enumerate(group):
+                c, f, n, S, mw = chunk[k]
+                arr[i].container = c.data_ptr()
+                arr[i].container_bytes = c.numel()
+                arr[i].frac_in = f.data_ptr()
+                arr[i].n = n
+                arr[i].max_unit_words = mw
+                # the stack was compressed (and the device synchronised) before any timed pass
+                arr[i].flags = _lib.NZ_ITEM_INPUTS_STABLE
+                arr[i].out_bf16 = outs[k].data_ptr()
+                arr[i].operand_cols = 0
+            batches.append((arr, len(group), chunk[0][3]))
     return batches
 
 
-def decompress_pass_batched(L, stack, batches, status, st):
-    s = stack.precision
+def decompress_pass(L, precision, batches, status, st):
     for arr, count, S in batches:
-        rc = L.nz_decompress_bf16_batch(arr, count, s, S, 1, status.data_ptr(), st)
+        rc = L.nz_decompress_bf16_batch(arr, count, precision, S, 1, status.data_ptr(), st)
         if rc:
             from neuzip_b200 import _lib
             _lib.check(rc)
@@ -260,12 +320,174 @@ def timed_passes(torch, dist, fn, steps, warmup, world):
     return ms
 
 
+def event_time_us(torch, fn, iters=20, warm=5):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+# --------------------------------------------------------------- config 1 leg
+def config1_leg(L, torch, peak, index):
+    """Configuration 1: the seed-0 4096x4096 matrix, lossless, one call per decode.  The
+    container is checked against the committed fixture; eight copies of the compressed
+    matrix and of the output are used in turn (445 MB, larger than L2)."""
+    from neuzip_b200 import _lib
+    with open(os.path.join(ROOT, "tests", "golden", "config1.json")) as f:
+        golden = json.load(f)["precision"]["7"]
+    torch.manual_seed(0)
+    w = (torch.randn(4096, 4096, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    wd = w.cuda().view(-1)
+    n, s = wd.numel(), 7
+    S = int(L.nz_default_lane_symbols(s))
+    st = torch.cuda.current_stream().cuda_stream
+    cap = int(L.nz_container_bound(n, S))
+    staging = torch.empty(cap, dtype=torch.uint8, device="cuda")
+    frac = torch.empty(int(L.nz_frac_bytes(n, s)), dtype=torch.uint8, device="cuda")
+    scratch = torch.empty(int(L.nz_compress_scratch_bytes(n, S)), dtype=torch.uint8, device="cuda")
+
+    def compress():
+        _lib.check(L.nz_compress_bf16(wd.data_ptr(), n, s, S, frac.data_ptr(), staging.data_ptr(), cap,
+                                      scratch.data_ptr(), scratch.numel(), st))
+    compress()
+    total, mw = ctypes.c_uint64(0), ctypes.c_uint32(0)
+    _lib.check(L.nz_container_bytes(staging.data_ptr(), total, mw, st))
+    cont = staging[: total.value].clone()
+    assert hex(crc(cont)) == golden["container_crc32"], "config 1 container differs from fixture"
+    assert hex(crc(frac)) == golden["frac_crc32"], "config 1 fractions differ from fixture"
+    copies = 8
+    conts = [cont.clone() for _ in range(copies)]
+    fracs = [frac.clone() for _ in range(copies)]
+    outs = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for _ in range(copies)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    it = [0]
+
+    def decode():
+        k = it[0] % copies
+        it[0] += 1
+        rc = L.nz_decompress_bf16(conts[k].data_ptr(), conts[k].numel(), fracs[k].data_ptr(), n, s, S,
+                                  mw.value, 1, outs[k].data_ptr(), status.data_ptr(), st)
+        if rc:
+            _lib.check(rc)
+    sampler = ClockSampler(index).start()
+    us = event_time_us(torch, decode, iters=40, warm=8)
+    us_compress = event_time_us(torch, compress, iters=10, warm=2)
+    clocks = sampler.stop()
+    assert int(status.item()) == 0
+    assert torch.equal(outs[0].view(torch.int16), wd.view(torch.int16)), "config 1 is not bit exact"
+    nbytes = 2 * n + cont.numel() + frac.numel()
+    gbs = nbytes / us / 1e3
+    return {"workload": "config 1: one 4096x4096 matrix, CPU seed 0, N(0,0.02), lossless; one "
+                        "nz_decompress_bf16 call per decode, 8 copies in turn (larger than L2)",
+            "decompress_us": round(us, 2), "decompress_gbs": round(gbs, 1),
+            "frac_of_hbm": round(gbs / peak, 4), "bytes_per_call": nbytes,
+            "compress_us": round(us_compress, 1),
+            "compress_gbs": round(nbytes / us_compress / 1e3, 1),
+            "ratio": round((cont.numel() + frac.numel()) / (2 * n), 5),
+            "stored_over_entropy_bound": round((cont.numel() + frac.numel()) / golden["ideal_bytes"], 4),
+            "bit_exact": True, "fixture": "tests/golden/config1.json", "clocks": clocks}
+
+
+# ------------------------------------------------------------ fused linear leg
+def linear_leg(L, torch, index):
+    """y = x W^T on a compressed weight: the fused decode -> tcgen05 GEMM (nz_linear_bf16, weight
+    in operand order) against decode (nz_decompress_bf16, stream order) + torch.matmul
+    (cuBLAS), both eager through the same stream, four copies of each weight in turn."""
+    from neuzip_b200 import _lib
+    st = torch.cuda.current_stream().cuda_stream
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cases = []
+    sampler = ClockSampler(index).start()
+    for rows, cols in ((4096, 11008), (4096, 4096), (11008, 4096)):
+        s, n = 7, rows * cols
+        S_op = int(L.nz_operand_lane_symbols(cols, s))
+        S_fl = int(L.nz_default_lane_symbols(s))
+        copies = 4
+        ops, flats = [], []
+        gen = torch.Generator(device="cuda")
+        scratch = torch.empty(int(L.nz_compress_scratch_bytes(n, S_fl)), dtype=torch.uint8, device="cuda")
+        for k in range(copies):
+            gen.manual_seed(50 + k)
+            w = (torch.randn(rows, cols, generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+            for S, operand, dst in ((S_op, True, ops), (S_fl, False, flats)):
+                cap = int(L.nz_container_bound(n, S))
+                staging = torch.empty(cap, dtype=torch.uint8, device="cuda")
+                frac = torch.empty(int(L.nz_frac_bytes(n, s)), dtype=torch.uint8, device="cuda")
+                if operand:
+                    _lib.check(L.nz_compress_bf16_operand(w.data_ptr(), rows, cols, s, S, frac.data_ptr(),
+                                                          staging.data_ptr(), cap, scratch.data_ptr(),
+                                                          scratch.numel(), st))
+                else:
+                    _lib.check(L.nz_compress_bf16(w.data_ptr(), n, s, S, frac.data_ptr(),
+                                                  staging.data_ptr(), cap, scratch.data_ptr(),
+                                                  scratch.numel(), st))
+                total, mw = ctypes.c_uint64(0), ctypes.c_uint32(0)
+                _lib.check(L.nz_container_bytes(staging.data_ptr(), total, mw, st))
+                dst.append((staging[: total.value].clone(), frac, int(mw.value)))
+            last_w = w
+        out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        for m in (16, 128):
+            x = torch.randn(m, cols, device="cuda").to(torch.bfloat16)
+            y = torch.empty(m, rows, dtype=torch.bfloat16, device="cuda")
+            y2 = torch.empty(m, rows, dtype=torch.bfloat16, device="cuda")
+            wb = int(L.nz_linear_workspace_bytes(rows, cols, S_op, m))
+            ws = torch.empty(wb, dtype=torch.uint8, device="cuda")
+            it = [0]
+
+            def fused():
+                c, f, mw = ops[it[0] % copies]
+                it[0] += 1
+                rc = L.nz_linear_bf16(c.data_ptr(), c.numel(), f.data_ptr(), rows, cols, s, S_op, mw, 0,
+                                      x.data_ptr(), m, 0, y.data_ptr(), ws.data_ptr(), wb,
+                                      status.data_ptr(), st)
+                if rc:
+                    _lib.check(rc)
+
+            def decode_gemm():
+                c, f, mw = flats[it[0] % copies]
+                it[0] += 1
+                L.nz_decompress_bf16(c.data_ptr(), c.numel(), f.data_ptr(), n, s, S_fl, mw, 0,
+                                     out.data_ptr(), status.data_ptr(), st)
+                torch.matmul(x, out.view(rows, cols).t(), out=y2)
+            t_fused = event_time_us(torch, fused)
+            t_plain = event_time_us(torch, decode_gemm)
+            # both paths ended on the last copy: same weight, results agree to bf16 rounding
+            it[0] = copies - 1
+            fused()
+            it[0] = copies - 1
+            decode_gemm()
+            torch.cuda.synchronize()
+            err = (y.float() - y2.float()).abs().max().item()
+            scale = y2.float().abs().max().item()
+            assert err <= 2.0 ** -6 * scale, "fused linear disagrees with decode + GEMM"
+            c, f, _ = ops[0]
+            cases.append({"out": rows, "in": cols, "m": m, "fused_us": round(t_fused, 1),
+                          "decode_plus_gemm_us": round(t_plain, 1),
+                          "speedup": round(t_plain / t_fused, 3),
+                          "compressed_bytes": c.numel() + f.numel(),
+                          "max_abs_diff_over_max": err / scale})
+        del ops, flats, last_w
+    clocks = sampler.stop()
+    assert int(status.item()) == 0
+    return {"what": "y = x W^T, lossless weight; fused = nz_linear_bf16 (decoder warps write "
+                    "128x64 operand tiles, tcgen05.mma accumulates in tensor memory, the decoded weight "
+                    "never reaches HBM); baseline = nz_decompress_bf16 + torch.matmul (cuBLAS)",
+            "cases": cases, "clocks": clocks}
+
+
 # ------------------------------------------------------------------ e2e leg
 def e2e_leg(L, torch, stack, n_layers_host, total_layers, steps, warmup):
     """Host buffers on both sides: pinned compressed bytes -> H2D -> decode kernel
     -> D2H of the bf16 result into pinned memory, three streams pipelined.  The
     pinned set holds `n_layers_host` layer sets and is walked total_layers /
-    n_layers_host times per step, so a step moves as many bytes as a device step."""
+    n_layers_host times per step, so a step moves as many bytes as a device step.
+    Also times the two copy directions on their own (same buffers, no kernel)."""
     per_layer = len(LAYER_SHAPES)
     items = stack.items[: n_layers_host * per_layer]
     reps = max(1, total_layers // max(1, n_layers_host))
@@ -293,45 +515,65 @@ def e2e_leg(L, torch, stack, n_layers_host, total_layers, steps, warmup):
     h2d = sum(hc.numel() + hf.numel() for hc, hf, _, _, _ in host_in) * reps
     d2h = sum(2 * n for _, _, n, _, _ in host_in) * reps
 
-    def one_step():
+    def one_step(copy_in=True, kernel=True, copy_out=True):
         i = 0
         for _ in range(reps):
             for hc, hf, n, S, mw in host_in:
                 k = i % depth
-                with torch.cuda.stream(s_in):
-                    s_in.wait_event(ev_k[k])        # kernel that last read this slot is done
-                    dev_c[k][: hc.numel()].copy_(hc, non_blocking=True)
-                    dev_f[k][: hf.numel()].copy_(hf, non_blocking=True)
-                    ev_in[k].record(s_in)
-                with torch.cuda.stream(s_k):
-                    s_k.wait_event(ev_in[k])
-                    s_k.wait_event(ev_out[k])       # previous result left the slot
-                    L.nz_decompress_bf16(dev_c[k].data_ptr(), hc.numel(), dev_f[k].data_ptr(), n, s,
-                                         S, mw, 1, dev_o[k].data_ptr(), status.data_ptr(),
-                                         s_k.cuda_stream)
-                    ev_k[k].record(s_k)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_k[k])
-                    host_o[k][:n].copy_(dev_o[k][:n], non_blocking=True)
-                    ev_out[k].record(s_out)
+                if copy_in:
+                    with torch.cuda.stream(s_in):
+                        s_in.wait_event(ev_k[k])        # kernel that last read this slot is done
+                        dev_c[k][: hc.numel()].copy_(hc, non_blocking=True)
+                        dev_f[k][: hf.numel()].copy_(hf, non_blocking=True)
+                        ev_in[k].record(s_in)
+                if kernel:
+                    with torch.cuda.stream(s_k):
+                        s_k.wait_event(ev_in[k])
+                        s_k.wait_event(ev_out[k])       # previous result left the slot
+                        L.nz_decompress_bf16(dev_c[k].data_ptr(), hc.numel(), dev_f[k].data_ptr(), n, s,
+                                             S, mw, 1, dev_o[k].data_ptr(), status.data_ptr(),
+                                             s_k.cuda_stream)
+                        ev_k[k].record(s_k)
+                if copy_out:
+                    with torch.cuda.stream(s_out):
+                        s_out.wait_event(ev_k[k])
+                        host_o[k][:n].copy_(dev_o[k][:n], non_blocking=True)
+                        ev_out[k].record(s_out)
                 i += 1
+        return i
 
-    for _ in range(warmup):
-        one_step()
-    torch.cuda.synchronize()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record(s_in)
-    for _ in range(steps):
-        one_step()
-    s_out.wait_stream(s_in)
-    s_out.wait_stream(s_k)
-    t1.record(s_out)
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1) / steps
+    def timed(**kw):
+        for _ in range(warmup):
+            one_step(**kw)
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record(s_in)
+        s_k.wait_stream(s_in)
+        s_out.wait_stream(s_in)
+        for _ in range(steps):
+            calls = one_step(**kw)
+        s_out.wait_stream(s_in)
+        s_out.wait_stream(s_k)
+        t1.record(s_out)
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / steps, calls
+
+    ms, calls = timed()
     assert int(status.item()) == 0
-    # the last result really is the matrix: compare with a device decode
-    return ms, h2d, d2h, (h2d + d2h)
+    # the last result really is the last matrix: compare the host copy with a device decode
+    last = (calls - 1) % depth
+    hc, hf, n, S, mw = host_in[-1]
+    c, f, _, _, _ = items[-1]
+    check = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    L.nz_decompress_bf16(c.data_ptr(), c.numel(), f.data_ptr(), n, s, S, mw, 1, check.data_ptr(),
+                         status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(host_o[last][:n].view(torch.int16), check.cpu().view(torch.int16)), \
+        "end-to-end result differs from a device decode"
+    ms_in, _ = timed(kernel=False, copy_out=False)
+    ms_out, _ = timed(copy_in=False, kernel=False)
+    return {"ms": ms, "h2d": h2d, "d2h": d2h, "ms_h2d_only": ms_in, "ms_d2h_only": ms_out}
 
 
 # ------------------------------------------------------------- CPU baseline
@@ -378,7 +620,10 @@ def run_reference(args):
     """The reference has no CPU implementation of this path (every stage is a CUDA
     kernel or nvcomp device code) and its nvcomp build cannot be installed here, so
     this arm times the CPU oracle - the restatement of the same split / entropy /
-    merge semantics - on all host cores, on a bounded sample of the workload."""
+    merge semantics, pinned to outputs of the reference's own split / merge kernels - on
+    all host cores, on a bounded sample of the workload.  It is a one-host figure: under a
+    multi-rank launch rank 0 alone runs it and the line says n_gpus 1, whatever --gpus is,
+    so that it does not grow with the number of ranks."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -408,7 +653,8 @@ def run_reference(args):
     cores = omp_threads()
     sample = "1 of 32 layer sets (7 matrices, 202 375 168 elements) per step, lossless"
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1,
+        "requested_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
         "data": "synthetic", "gpu_launches": 0,
@@ -419,77 +665,99 @@ def run_reference(args):
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "reference nvcomp build unavailable (nvcomp not installed, no network); the reference "
-                "has no CPU path, so the CPU oracle port is timed with OpenMP on all host cores",
+                "has no CPU path, so the CPU oracle port is timed with OpenMP on the host cores of "
+                "one machine: the value does not depend on the number of GPUs",
     }))
+
+
+# --------------------------------------------------------------- model legs
+def model_legs(torch, n_layers, index):
+    """Tokens/s of shortened Llama-shaped models, dense vs compressed, on one GPU.
+    Shortened means fewer transformer layers than the configurations name (the JSON says
+    how many of how many); widths, heads and vocabulary are the configurations'."""
+    import bench_models as modelbench
+    sampler = ClockSampler(index).start()
+    out = {"decode_7b_shape": modelbench.decode_leg(n_layers=n_layers, full_layers=32),
+           "train_1p3b_shape": modelbench.train_leg(n_layers=max(2, n_layers * 24 // 32),
+                                                    full_layers=24)}
+    out["clocks"] = sampler.stop()
+    return out
 
 
 # ------------------------------------------------------------------ our arm
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from neuzip_b200 import _lib
+    from neuzip_b200 import _lib, sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
+    numa = bind_to_gpu_numa(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     L = _lib.load()                     # raises if the CUDA library is not built
     _lib.check(L.nz_device_check())
+    index = gpu_index(local_rank)
+    peak, peak_kind = measured_peak()
 
+    if args.shard == "layers":
+        layer_ids = sharding.layers_of_rank(args.layers, rank, world)
+        scaling = "strong"
+    else:
+        layer_ids = list(range(args.layers))
+        scaling = "weak"
     precisions = [7] if args.no_sweep else [7, 3, 1, 0]
-    stacks = build_stacks(L, torch, args.layers, precisions, rank)
+    stacks, pinned_checked = build_stacks(L, torch, layer_ids, precisions, rank)
     torch.cuda.synchronize()
     max_n = max(a * b for a, b in LAYER_SHAPES)
-    outs = [torch.empty(max_n, dtype=torch.bfloat16, device="cuda") for _ in range(4)]
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
-
-    # correctness gate inside the bench: the last matrix decodes bit-exactly
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(1000 + 7 * (args.layers - 1) + 6 + 100000 * rank)
-    ref = (torch.randn(LAYER_SHAPES[6], generator=gen, device="cuda", dtype=torch.float32) * 0.02
-           ).to(torch.bfloat16).view(-1)
-    c, f, n, S, mw = stacks[7].items[-1]
-    _lib.check(L.nz_decompress_bf16(c.data_ptr(), c.numel(), f.data_ptr(), n, 7, S, mw, 1,
-                                    outs[0].data_ptr(), status.data_ptr(), st))
-    torch.cuda.synchronize()
-    assert torch.equal(outs[0][:n].view(torch.int16), ref.view(torch.int16)), "lossless decode mismatch"
-    del ref
-
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
-                           os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
     main = stacks[7]
     # output buffers of two layer sets, used alternately (1.6 GB, larger than L2)
     layer_outs = [[torch.empty(a * b, dtype=torch.bfloat16, device="cuda") for a, b in LAYER_SHAPES]
                   for _ in range(2)]
     batches = {s: make_batches(stacks[s], layer_outs) for s in precisions}
-    ms = timed_passes(torch, dist,
-                      lambda: decompress_pass_batched(L, main, batches[7], status, st),
+    singles = make_batches(main, layer_outs, single=True)
+
+    # correctness gate inside the bench: the last layer set decodes bit-exactly
+    last_layer = layer_ids[-1]
+    gen = torch.Generator(device="cuda")
+    decompress_pass(L, 7, batches[7][-1:], status, st)
+    slot = ((len(layer_ids) - 1) % 2)
+    for j, shape in enumerate(LAYER_SHAPES):
+        if rank == 0 and last_layer == 0:
+            g = torch.Generator().manual_seed(1000 + j)
+            ref = (torch.randn(shape, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16).cuda()
+        else:
+            gen.manual_seed(1000 + 7 * last_layer + j + 100000 * rank)
+            ref = (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * 0.02
+                   ).to(torch.bfloat16)
+        assert torch.equal(layer_outs[slot][j].view(torch.int16), ref.view(-1).view(torch.int16)), \
+            "lossless decode mismatch"
+    del ref
+
+    sampler = ClockSampler(index)
+    if rank == 0:
+        sampler.start()
+    ms = timed_passes(torch, dist, lambda: decompress_pass(L, 7, batches[7], status, st),
                       args.steps, args.warmup, world)
     clocks = sampler.stop() if rank == 0 else None
     assert int(status.item()) == 0, "decode status word is not clean"
-    # the last layer set of the batched pass decoded bit-exactly as well
-    _lib.check(L.nz_decompress_bf16_batch(batches[7][-1][0], batches[7][-1][1], 7, batches[7][-1][2],
-                                          1, status.data_ptr(), st))
-    _lib.check(L.nz_decompress_bf16(c.data_ptr(), c.numel(), f.data_ptr(), n, 7, S, mw, 1,
-                                    outs[0].data_ptr(), status.data_ptr(), st))
-    torch.cuda.synchronize()
-    last = layer_outs[(args.layers - 1) % 2][6]
-    assert torch.equal(last.view(torch.int16), outs[0][:n].view(torch.int16)), "batched decode mismatch"
-    # one call per matrix, for comparison
-    ms_single = timed_passes(torch, dist, lambda: decompress_pass(L, main, outs, status, st),
+    # one call per matrix (the granularity of the reference's Manager.read), for comparison
+    ms_single = timed_passes(torch, dist, lambda: decompress_pass(L, 7, singles, status, st),
                              max(2, args.steps // 2), 3, world)
 
     bytes_pass = main.bytes_per_pass
-    value = world * bytes_pass / (ms * 1e-3) / 1e9
+    total_bytes = bytes_pass
+    if world > 1:
+        t = torch.tensor([bytes_pass], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)
+        total_bytes = float(t.item())
+    value = total_bytes / (ms * 1e-3) / 1e9
     per_gpu = bytes_pass / (ms * 1e-3) / 1e9
     launches_per_pass = len(batches[7])
-    peak, peak_kind = measured_peak()
 
     sweep = {}
     for s in precisions:
@@ -497,14 +765,13 @@ def run_ours(args):
         if s == 7:
             t = ms
         else:
-            t = timed_passes(torch, dist,
-                             lambda: decompress_pass_batched(L, stk, batches[s], status, st),
+            t = timed_passes(torch, dist, lambda: decompress_pass(L, s, batches[s], status, st),
                              max(2, args.steps // 2), 3, world)
         gbs = stk.bytes_per_pass / (t * 1e-3) / 1e9
         cgbs = (stk.in_bytes + stk.stored_bytes) / (stk.compress_ms * 1e-3) / 1e9
         sweep[f"precision_{s}"] = {
             "decompress_gbs_per_gpu": round(gbs, 1), "frac_of_hbm": round(gbs / peak, 4),
-            "compress_gbs_per_gpu": round(cgbs, 1),
+            "compress_gbs_per_gpu": round(cgbs, 1), "compress_frac_of_hbm": round(cgbs / peak, 4),
             "ratio": round(stk.stored_bytes / stk.in_bytes, 5),
             "bytes_per_elem": round(stk.bytes_per_pass / stk.elements, 4),
         }
@@ -512,23 +779,37 @@ def run_ours(args):
     e2e = None
     if not args.no_e2e:
         e_steps = max(2, min(args.steps, 3))
-        e_ms, h2d, d2h, _ = e2e_leg(L, torch, main, min(args.e2e_layers, args.layers), args.layers,
-                                    e_steps, 3)
+        n_host = max(1, min(args.e2e_layers, len(layer_ids)))
+        r = e2e_leg(L, torch, main, n_host, len(layer_ids), e_steps, 3)
+        rates = torch.tensor([r["ms"], r["ms_h2d_only"], r["ms_d2h_only"], float(r["h2d"]),
+                              float(r["d2h"])], device="cuda", dtype=torch.float64)
+        per_rank = [rates.clone() for _ in range(world)]
         if world > 1:
-            t = torch.tensor([e_ms], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms = float(t.item())
-        scale = args.layers / (max(1, args.layers // max(1, min(args.e2e_layers, args.layers)))
-                               * min(args.e2e_layers, args.layers))
-        e2e = {"value": world * (h2d + d2h) / (e_ms * 1e-3) / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e_ms,
-               "steps": e_steps,
+            dist.all_gather(per_rank, rates)
+        e_ms = max(float(p[0]) for p in per_rank)
+        h2d_total = sum(float(p[3]) for p in per_rank)
+        d2h_total = sum(float(p[4]) for p in per_rank)
+        e2e = {"value": (h2d_total + d2h_total) / (e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total),
+               "ms_per_step": e_ms, "steps": e_steps,
+               "per_rank": [{"rank": i,
+                             "e2e_gbs": round((float(p[3]) + float(p[4])) / float(p[0]) / 1e6, 1),
+                             "h2d_only_gbs": round(float(p[3]) / float(p[1]) / 1e6, 1),
+                             "d2h_only_gbs": round(float(p[4]) / float(p[2]) / 1e6, 1)}
+                            for i, p in enumerate(per_rank)],
+               "numa": numa,
                "how": "pinned host compressed bytes -> H2D -> nz_decompress_bf16 -> D2H of the bf16 "
-                      "result into pinned host memory, 3 streams; the pinned set of "
-                      f"{min(args.e2e_layers, args.layers)} layer sets is walked "
-                      f"{max(1, args.layers // max(1, min(args.e2e_layers, args.layers)))} times per step"}
-        del scale
+                      "result into pinned host memory, 3 streams, the last host result compared with "
+                      f"a device decode; the pinned set of {n_host} layer sets is walked "
+                      f"{max(1, len(layer_ids) // n_host)} times per step; h2d_only / d2h_only time "
+                      "the two copy directions alone on the same buffers; pinned memory is allocated "
+                      "after the process was bound to the CPUs NVML reports as local to its GPU"}
 
+    extras = {}
+    if rank == 0 and world == 1:
+        extras["config1"] = config1_leg(L, torch, peak, index)
+        if not args.no_linear:
+            extras["linear_fused"] = linear_leg(L, torch, index)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle import oracle as O
@@ -538,27 +819,34 @@ def run_ours(args):
         cpu = {"value": gbs, "unit": UNIT, "cores": omp_threads(), "kind": "port",
                "sample": f"one 4096x4096 and one 4096x11008 matrix (61 865 984 elements), lossless, "
                          f"{reps} passes in {secs:.1f} s with the OpenMP oracle"}
+    if rank == 0 and world == 1 and not args.no_model:
+        del stacks, batches, singles, main
+        torch.cuda.empty_cache()
+        extras["model"] = model_legs(torch, args.model_layers, index)
+        main = None
 
     if rank == 0:
+        n_items = len(layer_ids) * len(LAYER_SHAPES)
+        elements = sum(a * b for a, b in LAYER_SHAPES) * len(layer_ids)
         avg_launch_bytes = bytes_pass / launches_per_pass
-        traffic = None
-        if NCU_TRAFFIC_BYTES_45M:
-            traffic = NCU_TRAFFIC_BYTES_45M * (main.elements / launches_per_pass) / NCU_TRAFFIC_ELEMENTS
+        traffic = NCU_TRAFFIC_BYTES_45M * (elements / launches_per_pass) / NCU_TRAFFIC_ELEMENTS
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "gpu_launches": args.steps * launches_per_pass * world,
             "config": {
                 "workload": f"config 2: {args.layers} x Llama-7B layer sets "
-                            f"({len(main.items)} bf16 matrices, {main.elements} elements per GPU), "
+                            f"({n_items} bf16 matrices, {elements} elements on rank 0), "
                             "N(0,0.02) seeded per matrix, precision 7 (lossless), one "
                             "nz_decompress_bf16_batch call (= one kernel launch) per layer set of 7 "
                             "matrices",
                 "l2": "inputs larger than L2: a pass reads 8.6 GB and writes 13 GB, every call a "
-                      "different matrix",
-                "sharding": "every rank decodes its own full stack, no collective",
-                "ratio": round(main.stored_bytes / main.in_bytes, 5),
+                      "different layer set",
+                "sharding": ("every rank decodes its own full stack, no collective" if scaling == "weak"
+                             else "one stack, layer set l on rank l mod N, no collective"),
+                "pinned_to_fixture": f"{pinned_checked} matrices of layer set 0 (CPU-seeded) matched "
+                                     "tests/golden/config2_layer0.json",
             },
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": UNIT,
                          "frac": per_gpu / peak, "traffic": traffic, "peak_kind": peak_kind,
@@ -566,11 +854,13 @@ def run_ours(args):
                          "bytes_per_launch": avg_launch_bytes,
                          "avg_launch_us": ms * 1e3 / launches_per_pass},
             "clocks": clocks,
-            "one_call_per_matrix": {"value": world * bytes_pass / (ms_single * 1e-3) / 1e9,
-                                    "unit": UNIT, "ms_per_step": ms_single,
-                                    "launches_per_step": len(main.items)},
+            "one_call_per_matrix": {"value": total_bytes / (ms_single * 1e-3) / 1e9, "unit": UNIT,
+                                    "frac_of_hbm": round(bytes_pass / (ms_single * 1e-3) / 1e9 / peak, 4),
+                                    "ms_per_step": ms_single, "launches_per_step": len(singles)
+                                    if main is not None else n_items},
             "sweep": sweep,
         }
+        line.update(extras)
         if e2e:
             line["e2e"] = e2e
         if cpu:

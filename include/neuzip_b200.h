@@ -226,10 +226,13 @@ typedef struct nz_decompress_item {
   uint64_t operand_cols;     /* 0, or the row length of a matrix stored in
                                 operand order (nz_compress_bf16_operand);
                                 the output is row-major either way          */
+  uint32_t lane_symbols;     /* 0 = the call's lane_symbols; else this
+                                tensor's own (tensors of one call may differ) */
+  uint32_t reserved;         /* 0                                           */
 } nz_decompress_item;
 
-/* nz_decompress_bf16 for several tensors of the same precision and
- * lane_symbols (for instance the seven matrices of one transformer layer) in
+/* nz_decompress_bf16 for several tensors of the same precision (for instance the
+ * seven matrices of one transformer layer; an item may name its own lane_symbols) in
  * as few launches as possible: up to 8 tensors share a launch, each on a share
  * of the SMs proportional to its size, so small matrices do not leave most of
  * the GPU idle and the fixed cost of a launch is paid once.  `items` is a host

@@ -59,7 +59,7 @@ class DecompressItem(ctypes.Structure):
     """struct nz_decompress_item"""
     _fields_ = [("container", _vp), ("container_bytes", _u64), ("frac_in", _vp), ("n", _u64),
                 ("max_unit_words", _u32), ("flags", _u32), ("out_bf16", _vp),
-                ("operand_cols", _u64)]
+                ("operand_cols", _u64), ("lane_symbols", _u32), ("reserved", _u32)]
 
 
 _f32 = ctypes.c_float

@@ -262,6 +262,12 @@ class CodecBackend:
         entry.pending = None
         entry.version += 1
 
+    def settle_all(self) -> None:
+        """Wait for every write still in flight and right-size its container (for instance
+        before capturing decodes in a CUDA graph, where events must not be queried)."""
+        for entry in self._cache.values():
+            self._settle(entry, block=True)
+
     def _get(self, name: str) -> Optional[_Entry]:
         entry = self._cache.get(name)
         if entry is not None and entry.pending is not None:
@@ -293,6 +299,7 @@ class CodecBackend:
         item[0].flags = _stable_flag([entry], _next_op())
         item[0].out_bf16 = _ptr(out)
         item[0].operand_cols = entry.operand_cols
+        item[0].lane_symbols = entry.lane_symbols
         _lib.check(self._lib.nz_decompress_bf16_batch(
             item, 1, self.precision, entry.lane_symbols, int(self.canonical_nan),
             _ptr(self._status), _stream()))
@@ -352,26 +359,23 @@ class CodecBackend:
                 raise RuntimeError("Data not found")
             entries.append(entry)
         outs = [torch.empty(e.numel, dtype=torch.bfloat16, device="cuda") for e in entries]
-        # one batched call per lane_symbols value (a manager only ever has one)
-        by_s: Dict[int, List[int]] = {}
-        for i, e in enumerate(entries):
-            by_s.setdefault(e.lane_symbols, []).append(i)
-        for S, idx in by_s.items():
-            items = (_lib.DecompressItem * len(idx))()
-            flags = _stable_flag([entries[i] for i in idx], _next_op())
-            for k, i in enumerate(idx):
-                e = entries[i]
+        # one batched call; every item names its own lane_symbols
+        if entries:
+            items = (_lib.DecompressItem * len(entries))()
+            flags = _stable_flag(entries, _next_op())
+            for k, e in enumerate(entries):
                 items[k].container = _ptr(e.container)
                 items[k].container_bytes = e.container.numel()
                 items[k].frac_in = _ptr(e.fractions)
                 items[k].n = e.numel
                 items[k].max_unit_words = e.max_unit_words
                 items[k].flags = flags
-                items[k].out_bf16 = _ptr(outs[i])
+                items[k].out_bf16 = _ptr(outs[k])
                 items[k].operand_cols = e.operand_cols
+                items[k].lane_symbols = e.lane_symbols
             _lib.check(self._lib.nz_decompress_bf16_batch(
-                items, len(idx), self.precision, S, int(self.canonical_nan), _ptr(self._status),
-                _stream()))
+                items, len(entries), self.precision, entries[0].lane_symbols,
+                int(self.canonical_nan), _ptr(self._status), _stream()))
         for e, out in zip(entries, outs):
             self._denormalize(e, out)
         return outs
@@ -391,9 +395,6 @@ class CodecBackend:
         entries = [self._cache[n] for n in batch.names]
         for e in entries:
             self._settle(e, block=False)
-        S = {e.lane_symbols for e in entries}
-        if len(S) != 1:
-            raise ValueError("a batch must share one lane_symbols value")
         # two argument blocks: with and without the promise that the inputs are stable
         blocks = []
         for flags in (0, _lib.NZ_ITEM_INPUTS_STABLE):
@@ -410,9 +411,10 @@ class CodecBackend:
                 items[k].flags = flags
                 items[k].out_bf16 = _ptr(out)
                 items[k].operand_cols = e.operand_cols
+                items[k].lane_symbols = e.lane_symbols
             blocks.append(items)
         # the entries keep their tensors alive as long as the batch refers to them
-        batch.entries, batch.blocks, batch.lane_symbols = entries, blocks, S.pop()
+        batch.entries, batch.blocks, batch.lane_symbols = entries, blocks, entries[0].lane_symbols
         batch.versions = [e.version for e in entries]
 
     def run_batch(self, batch: _Batch) -> None:

@@ -63,6 +63,7 @@ struct BatchItem {
   uint32_t n_units;
   uint32_t cta_begin;     // first CTA of this tensor
   uint32_t tile_cols;     // operand order: row length (0 = stream order)
+  uint32_t S;             // lane symbols of this tensor
 };
 struct BatchArgs {
   BatchItem item[kMaxBatch];
@@ -672,7 +673,7 @@ decode_kernel(const BatchArgs batch) {
   a.container_bytes = batch.item[ti].container_bytes;
   a.frac = batch.item[ti].frac;
   a.n = batch.item[ti].n;
-  a.S = batch.S;
+  a.S = batch.item[ti].S;
   a.n_units = batch.item[ti].n_units;
   a.slot_bytes = batch.slot_bytes;
   a.lut_shift = batch.lut_shift;
@@ -861,11 +862,12 @@ struct HostItem {
   uint32_t in, seg;
   uint32_t flags;              // NZ_ITEM_* of the C interface
   uint32_t tile_cols;          // operand order: row length of the matrix (0 = stream order)
+  uint32_t S;                  // lane symbols of this tensor
 };
 
 // Units a launch decodes for an item.
-static inline uint64_t work_units(const HostItem &it, uint32_t S) {
-  return it.unit_list ? it.n_list : unit_count(it.n, S);
+static inline uint64_t work_units(const HostItem &it) {
+  return it.unit_list ? it.n_list : unit_count(it.n, it.S);
 }
 
 // Grid geometry of one launch over `count` tensors.  One CTA per SM.  Every
@@ -874,16 +876,22 @@ static inline uint64_t work_units(const HostItem &it, uint32_t S) {
 // same number of warps, every warp the same number of unit groups (within one).
 // The decode table gets what shared memory the slots and rings leave (more
 // copies = fewer bank conflicts), at most 128 KB.
-static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, uint32_t ring_bytes,
+static int decode_geometry(const HostItem *items, uint32_t count, uint32_t ring_bytes,
                            BatchArgs &b, uint32_t &warps, uint32_t &smem_bytes) {
-  const uint64_t U = 32ull * S;
+  // tensors of one launch may differ in lane symbols: slots and guard band are sized for
+  // the longest unit, and a tensor's share of the CTAs follows its symbols, not its units
+  uint32_t S = 0;
   uint64_t unit_bytes = 0, total_units = 0;
   for (uint32_t t = 0; t < count; ++t) {
+    const uint64_t U = 32ull * items[t].S;
     uint64_t ub = items[t].max_unit_words ? (uint64_t)items[t].max_unit_words * 2 : U;
     if (ub > U) ub = U;
     if (ub > unit_bytes) unit_bytes = ub;
-    total_units += work_units(items[t], S);
+    if (items[t].S > S) S = items[t].S;
+    total_units += work_units(items[t]) * items[t].S;
   }
+  const uint64_t U = 32ull * S;
+  b.S = S;
   if (unit_bytes < 160) unit_bytes = 160;
   b.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
   const uint32_t guard = ((S + 8) * 2 + 127) & ~127u;
@@ -902,14 +910,14 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, ui
   // (or fewer when there is not enough work to give every SM a group of units)
   const uint32_t sms = (uint32_t)sm_count();
   uint64_t total_groups = 0;
-  for (uint32_t t = 0; t < count; ++t) total_groups += (work_units(items[t], S) + kChains - 1) / kChains;
+  for (uint32_t t = 0; t < count; ++t) total_groups += (work_units(items[t]) + kChains - 1) / kChains;
   uint32_t n_ctas = sms;
   if (total_groups < n_ctas) n_ctas = (uint32_t)total_groups;
   if (n_ctas < count) n_ctas = count;
   uint32_t ctas[kMaxBatch], used = 0;
   for (uint32_t t = 0; t < count; ++t) {
-    const uint64_t nu = work_units(items[t], S);
-    uint64_t c = total_units ? (nu * n_ctas + total_units / 2) / total_units : 1;
+    const uint64_t nu = work_units(items[t]);
+    uint64_t c = total_units ? (nu * items[t].S * n_ctas + total_units / 2) / total_units : 1;
     const uint64_t groups = (nu + kChains - 1) / kChains;
     if (c > groups) c = groups;
     if (c < 1) c = 1;
@@ -918,7 +926,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, ui
   }
   // fix the rounding: take from / give to the tensor with the most / fewest groups per CTA
   auto load = [&](uint32_t t, uint32_t c) {
-    return (double)((work_units(items[t], S) + kChains - 1) / kChains) / (double)c;
+    return (double)((work_units(items[t]) + kChains - 1) / kChains) * items[t].S / (double)c;
   };
   while (used > n_ctas) {
     uint32_t best = kMaxBatch;
@@ -932,7 +940,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, ui
   while (used < n_ctas) {
     uint32_t best = kMaxBatch;
     for (uint32_t t = 0; t < count; ++t) {
-      const uint64_t groups = (work_units(items[t], S) + kChains - 1) / kChains;
+      const uint64_t groups = (work_units(items[t]) + kChains - 1) / kChains;
       if (ctas[t] < groups && (best == kMaxBatch || load(t, ctas[t]) > load(best, ctas[best])))
         best = t;
     }
@@ -943,7 +951,7 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t S, ui
   // warps per CTA: enough for the busiest CTA's groups, spread over whole rounds
   uint32_t max_groups = 1;
   for (uint32_t t = 0; t < count; ++t) {
-    const uint64_t groups = (work_units(items[t], S) + kChains - 1) / kChains;
+    const uint64_t groups = (work_units(items[t]) + kChains - 1) / kChains;
     const uint32_t per_cta = (uint32_t)((groups + ctas[t] - 1) / ctas[t]);
     if (per_cta > max_groups) max_groups = per_cta;
   }
@@ -1016,11 +1024,10 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
     memset(&b, 0, sizeof(b));
     uint32_t warps = 0, smem_bytes = 0;
     // the exponent-only kernel is the precision-7 instantiation
-    int rc = decode_geometry(live, n_live, S, ring_warp_bytes(merge ? precision : 7), b, warps,
+    int rc = decode_geometry(live, n_live, ring_warp_bytes(merge ? precision : 7), b, warps,
                              smem_bytes);
     if (rc) return rc;
     b.count = n_live;
-    b.S = S;
     b.canon = canon;
     b.status = (uint32_t *)status;
     for (uint32_t t = 0; t < n_live; ++t) {
@@ -1030,8 +1037,9 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
       b.item[t].n = live[t].n;
       b.item[t].out_bf16 = (uint16_t *)live[t].out_bf16;
       b.item[t].out_exp = (uint8_t *)live[t].out_exp;
-      b.item[t].n_units = (uint32_t)unit_count(live[t].n, S);
+      b.item[t].n_units = (uint32_t)unit_count(live[t].n, live[t].S);
       b.item[t].tile_cols = live[t].tile_cols;
+      b.item[t].S = live[t].S;
     }
     const bool gather = live[0].unit_list != nullptr;   // gather calls pass a single item
     b.unit_list = live[0].unit_list;
@@ -1071,13 +1079,15 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
   };
   for (uint32_t i = 0; i < count; ++i) {
     if (items[i].n == 0) continue;
-    const uint64_t nu = unit_count(items[i].n, S);
+    const uint64_t nu = unit_count(items[i].n, items[i].S ? items[i].S : S);
     if (items[i].container_bytes < payload_offset(nu)) {
       set_error("decode: container %u of %llu bytes is too short for %llu units", i,
                 (unsigned long long)items[i].container_bytes, (unsigned long long)nu);
       return NZ_E_FORMAT;
     }
-    live[n_live++] = items[i];
+    live[n_live] = items[i];
+    if (!live[n_live].S) live[n_live].S = S;
+    ++n_live;
     if (n_live == kMaxBatch) {
       int rc = flush();
       if (rc) return rc;
@@ -1104,6 +1114,7 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   it.in = it.seg = 0;
   it.flags = 0;
   it.tile_cols = 0;
+  it.S = 0;
   return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
@@ -1214,9 +1225,19 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
       host[i].in = host[i].seg = 0;
       host[i].flags = it.flags;
       host[i].tile_cols = 0;
+      host[i].S = 0;
+      if (it.lane_symbols) {
+        if (!nz::valid_lane_symbols(it.lane_symbols)) {
+          nz::set_error("nz_decompress_bf16_batch: item %u: lane_symbols must be a multiple of 8 "
+                        "in [8, %u] (got %u)", base + i, nz::kMaxLaneSymbols, it.lane_symbols);
+          return NZ_E_ARG;
+        }
+        host[i].S = it.lane_symbols;
+      }
       if (it.operand_cols) {
         const uint64_t c = it.operand_cols;
-        if (c % 64 || it.n % (4 * c) || (c / 64) % (lane_symbols / 8) || c >= (1ull << 31)) {
+        const uint32_t item_s = it.lane_symbols ? it.lane_symbols : lane_symbols;
+        if (c % 64 || it.n % (4 * c) || (c / 64) % (item_s / 8) || c >= (1ull << 31)) {
           nz::set_error("nz_decompress_bf16_batch: item %u: %llu elements in rows of %llu are not "
                         "in operand order for lane_symbols %u", base + i,
                         (unsigned long long)it.n, (unsigned long long)c, lane_symbols);
@@ -1269,6 +1290,7 @@ extern "C" int nz_decompress_bf16_units(const void *container, uint64_t containe
   it.in = it.seg = 0;
   it.flags = 0;
   it.tile_cols = 0;
+  it.S = 0;
   return nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                          (cudaStream_t)stream);
 }
@@ -1463,6 +1485,7 @@ extern "C" int nz_linear_vec_bf16(const void *container, uint64_t container_byte
   it.seg = nz::dot_segments(in_features, U);
   it.flags = 0;
   it.tile_cols = 0;
+  it.S = 0;
   rc = nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                        (cudaStream_t)stream);
   if (rc) return rc;

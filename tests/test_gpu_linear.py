@@ -260,3 +260,33 @@ def test_converted_llama_with_fused_linear_matches_dense_logits_and_tokens():
     m.check()
     assert (logits.float() - ref_logits.float()).abs().max().item() <= 1e-2
     assert torch.equal(tokens, ref_tokens)
+
+
+def test_batched_decode_of_tensors_with_different_lane_symbols():
+    """One launch, three tensors: operand order with units of 344 and of 256 lane
+    symbols, and a stream-order tensor with 64."""
+    from neuzip_b200 import _lib
+    L = A.lib()
+    s = 7
+    specs = [((64, 11008), 344, True), ((256, 2048), 256, True), ((100, 333), 64, False)]
+    ws, comps = [], []
+    for k, (shape, S, operand) in enumerate(specs):
+        w = weights(shape, 40 + k).cuda()
+        ws.append(w)
+        comps.append(A.compress_operand(w, shape[0], shape[1], s, S) if operand
+                     else A.compress(w.view(-1), s, S))
+    outs = [torch.empty(w.numel(), dtype=torch.bfloat16, device="cuda") for w in ws]
+    items = (_lib.DecompressItem * 3)()
+    for k, ((shape, S, operand), (c, f, mw)) in enumerate(zip(specs, comps)):
+        items[k].container, items[k].container_bytes = c.data_ptr(), c.numel()
+        items[k].frac_in, items[k].n = f.data_ptr(), ws[k].numel()
+        items[k].max_unit_words, items[k].flags = mw, 0
+        items[k].out_bf16 = outs[k].data_ptr()
+        items[k].operand_cols = shape[1] if operand else 0
+        items[k].lane_symbols = S
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.nz_decompress_bf16_batch(items, 3, s, 256, 1, status.data_ptr(), A.stream()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for w, o in zip(ws, outs):
+        assert torch.equal(o.view(torch.int16), w.view(-1).view(torch.int16))
