@@ -180,18 +180,21 @@ __host__ __device__ constexpr uint32_t ring_warp_bytes(int precision) {
 
 // Where the four words (8 bf16) that a lane produces per block and chain go.
 // StoreSink writes them to the output tensor.
-struct StoreSink {
+// ADV = elements between a lane's consecutive blocks: 256, or 64 in operand order (a
+// compile-time constant, so that the offsets fold into the store instructions).
+template <int ADV>
+struct StoreSinkT {
   uint16_t *out[kChains];
-  uint32_t adv;       // elements between a lane's consecutive blocks: 256, or 64 in operand order
   __device__ __forceinline__ void begin(int) {}
   __device__ __forceinline__ void put(int c, int k, const uint32_t (&w)[4]) {
-    __stcs(reinterpret_cast<uint4 *>(out[c] + k * adv), make_uint4(w[0], w[1], w[2], w[3]));
+    __stcs(reinterpret_cast<uint4 *>(out[c] + k * ADV), make_uint4(w[0], w[1], w[2], w[3]));
   }
   __device__ __forceinline__ void advance(int blocks) {
 #pragma unroll
-    for (int c = 0; c < kChains; ++c) out[c] += blocks * adv;
+    for (int c = 0; c < kChains; ++c) out[c] += blocks * ADV;
   }
 };
+using StoreSink = StoreSinkT<256>;
 
 // One lane's running dot product of a weight row with the input vector.  The
 // tensor is a row-major [out, in] matrix with `in` a multiple of 256, so the 256
@@ -545,10 +548,10 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
   }
 }
 
-__device__ __forceinline__ void init_sink(StoreSink &sk, int c, const DecodeArgs &a, uint32_t,
+template <int ADV>
+__device__ __forceinline__ void init_sink(StoreSinkT<ADV> &sk, int c, const DecodeArgs &a, uint32_t,
                                           uint64_t out_elem, uint32_t) {
   // out_elem is the lane's first element of the unit in stream order (a multiple of 8)
-  sk.adv = a.tile_cols ? 64u : 256u;
   sk.out[c] = a.out_bf16 ? a.out_bf16 + out_index(a, out_elem) : nullptr;
 }
 __device__ __forceinline__ void init_sink(DotSink &sk, int c, const DecodeArgs &a, uint32_t unit,
@@ -556,7 +559,8 @@ __device__ __forceinline__ void init_sink(DotSink &sk, int c, const DecodeArgs &
   sk.lane[c].start(a.gx, a.in, (uint64_t)unit * (32ull * a.S), a.partial + (uint64_t)unit * a.seg,
                    lane);
 }
-__device__ __forceinline__ void finish_sink(StoreSink &) {}
+template <int ADV>
+__device__ __forceinline__ void finish_sink(StoreSinkT<ADV> &) {}
 __device__ __forceinline__ void finish_sink(DotSink &sk) {
 #pragma unroll
   for (int c = 0; c < kChains; ++c) sk.lane[c].finish();
@@ -805,22 +809,33 @@ decode_kernel(const BatchArgs batch) {
         done = true;
         const uint8_t *fr[kChains];
         uint8_t *xb[kChains];
-        typename std::conditional<DOT, DotSink, StoreSink>::type sink;
+        auto run = [&](auto &sink) {
 #pragma unroll
-        for (int c = 0; c < kChains; ++c) {
-          const uint64_t e = (uint64_t)real[c] * U + lane * 8;                  // in the tensor
-          const uint64_t o = LIST ? (uint64_t)(u + c) * U + lane * 8 : e;       // in the output
-          fr[c] = MERGE ? a.frac + e * (S + 1) / 8 : nullptr;
-          xb[c] = MERGE ? nullptr : a.out_exp + o;
-          init_sink(sink, c, a, real[c], o, lane);
+          for (int c = 0; c < kChains; ++c) {
+            const uint64_t e = (uint64_t)real[c] * U + lane * 8;                  // in the tensor
+            const uint64_t o = LIST ? (uint64_t)(u + c) * U + lane * 8 : e;       // in the output
+            fr[c] = MERGE ? a.frac + e * (S + 1) / 8 : nullptr;
+            xb[c] = MERGE ? nullptr : a.out_exp + o;
+            init_sink(sink, c, a, real[c], o, lane);
+          }
+          if (canon)
+            decode_blocks_multi<S, MERGE, true, 0>(st, lv, a.S / 8, fr, sink, xb, ring);
+          else if (row_shift == kFastRow)
+            decode_blocks_multi<S, MERGE, false, kFastRow>(st, lv, a.S / 8, fr, sink, xb, ring);
+          else
+            decode_blocks_multi<S, MERGE, false, 0>(st, lv, a.S / 8, fr, sink, xb, ring);
+          finish_sink(sink);
+        };
+        if (DOT) {
+          typename std::conditional<DOT, DotSink, StoreSink>::type sink;
+          run(sink);
+        } else if (MODE == kModeTensor && MERGE && a.tile_cols) {
+          typename std::conditional<DOT, DotSink, StoreSinkT<64>>::type sink;     // operand order
+          run(sink);
+        } else {
+          typename std::conditional<DOT, DotSink, StoreSink>::type sink;
+          run(sink);
         }
-        if (canon)
-          decode_blocks_multi<S, MERGE, true, 0>(st, lv, a.S / 8, fr, sink, xb, ring);
-        else if (row_shift == kFastRow)
-          decode_blocks_multi<S, MERGE, false, kFastRow>(st, lv, a.S / 8, fr, sink, xb, ring);
-        else
-          decode_blocks_multi<S, MERGE, false, 0>(st, lv, a.S / 8, fr, sink, xb, ring);
-        finish_sink(sink);
         bool low = true;
 #pragma unroll
         for (int c = 0; c < kChains; ++c) low = low && st[c].x == kStateLow;
