@@ -206,6 +206,29 @@ int nz_adamw_bf16(void *weight_bf16, const void *grad_bf16, void *exp_avg,
                   float beta1, float beta2, float eps, float weight_decay,
                   uint32_t step, float grad_scale, void *stream);
 
+/* The whole read -> update -> write cycle of one compressed weight in one call,
+ * with the update fused into the decoder: the decode kernel applies the AdamW
+ * step (the formula of nz_adamw_bf16, moments in bf16) to the weights as it
+ * produces them, against the gradient and the moments at the same positions of
+ * their row-major tensors, and writes the updated weights once, into `scratch`;
+ * the compressor then codes them into frac_out / container_out (which may be
+ * the buffers a previous call produced, but not the inputs of this one; read
+ * the new container's size with nz_container_bytes).  operand_cols != 0 names
+ * the row length of a weight stored in operand order (kept).  Results are bit
+ * for bit those of nz_decompress_bf16 -> nz_adamw_bf16 -> nz_compress_bf16.
+ * Scratch of nz_adamw_compressed_scratch_bytes bytes, 16-byte aligned.
+ * Reference: compressed_lomo_hook (neuzip/__init__.py:25-35: param() ->
+ * add_ -> manager.write) and the loop at examples/training/train_clm.py:822-833. */
+uint64_t nz_adamw_compressed_scratch_bytes(uint64_t n, uint32_t lane_symbols);
+int nz_adamw_compressed_bf16(const void *container, uint64_t container_bytes, const void *frac_in,
+                             uint64_t n, uint64_t operand_cols, int precision,
+                             uint32_t lane_symbols, uint32_t max_unit_words, int canonical_nan,
+                             const void *grad_bf16, void *exp_avg_bf16, void *exp_avg_sq_bf16,
+                             float lr, float beta1, float beta2, float eps, float weight_decay,
+                             uint32_t step, float grad_scale, void *frac_out, void *container_out,
+                             uint64_t container_cap, void *scratch, uint64_t scratch_bytes,
+                             void *status, void *stream);
+
 /* Item flag: the container and the fractions were complete (written and
  * visible) before the kernel that precedes this call on the stream was
  * launched -- true for weights that were compressed earlier and are decoded

@@ -87,6 +87,11 @@ SIGNATURES["nz_linear_bf16"] = (
     _int, [_vp, _u64, _vp, _u64, _u64, _int, _u32, _u32, _int, _vp, _u64, _vp, _vp, _vp, _u64, _vp,
            _vp])
 
+SIGNATURES["nz_adamw_compressed_scratch_bytes"] = (_u64, [_u64, _u32])
+SIGNATURES["nz_adamw_compressed_bf16"] = (
+    _int, [_vp, _u64, _vp, _u64, _u64, _int, _u32, _u32, _int, _vp, _vp, _vp, _f32, _f32, _f32, _f32,
+           _f32, _u32, _f32, _vp, _vp, _u64, _vp, _u64, _vp, _vp])
+
 _lock = threading.Lock()
 _lib = None
 

@@ -229,6 +229,38 @@ class CodecBackend:
         self._cache[name] = self._finish_write(
             _Entry(n, tensor.dtype, S, 0, staging, frac, normalizers, _next_op()))
 
+    def adamw_update(self, name: str, grad: torch.Tensor, exp_avg: torch.Tensor,
+                     exp_avg_sq: torch.Tensor, lr: float, beta1: float, beta2: float, eps: float,
+                     weight_decay: float, step: int, grad_scale: float = 1.0) -> bool:
+        """The read -> AdamW -> write cycle of one stored weight as a single library call
+        (``nz_adamw_compressed_bf16``): the decode kernel applies the step while it produces
+        the weights, the compressor codes the result.  Bit for bit what `read`,
+        ``nz_adamw_bf16`` and `write` give.  Needs bf16 moments and a bf16 gradient shaped
+        like the weight; returns False (nothing done) when the call does not qualify."""
+        entry = self._get(name)
+        if entry is None:
+            raise RuntimeError("Data not found")
+        n = entry.numel
+        if (self.normalizer_size or entry.normalizers is not None or n % 8
+                or any(t.dtype != torch.bfloat16 or not t.is_cuda or t.numel() != n
+                       or not t.is_contiguous() or t.data_ptr() % 16
+                       for t in (grad, exp_avg, exp_avg_sq))):
+            return False
+        L, S = self._lib, entry.lane_symbols
+        frac = torch.empty_like(entry.fractions)
+        cap = int(L.nz_container_bound(n, S))
+        staging = torch.empty(cap, dtype=torch.uint8, device="cuda")
+        scratch = self._scratch_for(int(L.nz_adamw_compressed_scratch_bytes(n, S)))
+        _lib.check(L.nz_adamw_compressed_bf16(
+            _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), n,
+            entry.operand_cols, self.precision, S, entry.max_unit_words, int(self.canonical_nan),
+            _ptr(grad), _ptr(exp_avg), _ptr(exp_avg_sq), lr, beta1, beta2, eps, weight_decay, step,
+            grad_scale, _ptr(frac), _ptr(staging), cap, _ptr(scratch), scratch.numel(),
+            _ptr(self._status), _stream()))
+        self._cache[name] = self._finish_write(
+            _Entry(n, entry.dtype, S, 0, staging, frac, None, _next_op(), entry.operand_cols))
+        return True
+
     # -- settling a write without stalling the host ----------------------------
     def _finish_write(self, entry: _Entry) -> _Entry:
         """The reference reads the compressed size back right after compressing, which

@@ -77,4 +77,19 @@ int cuda_fail(cudaError_t err, const char *what);
 
 int sm_count();
 
+// AdamW step on one element, in fp32: the one formula shared by the stand-alone update
+// kernel and by the decoder's update mode, so that both give the same bits.
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale;
+};
+__device__ __forceinline__ float adamw_element(float w, float g, float &m, float &v,
+                                               const AdamArgs &a) {
+  const float grad = g * a.grad_scale;
+  m = a.beta1 * m + (1.0f - a.beta1) * grad;
+  v = a.beta2 * v + (1.0f - a.beta2) * grad * grad;
+  w *= 1.0f - a.lr * a.weight_decay;
+  w -= (a.lr / a.bias1) * m / (sqrtf(v / a.bias2) + a.eps);
+  return w;
+}
+
 }  // namespace nz

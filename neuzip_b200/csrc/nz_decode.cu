@@ -31,6 +31,7 @@
 // CTA's shared memory (a guard band behind the last slot absorbs run-away
 // pointers), output and fraction addresses never depend on coded data, and
 // the wait on the bulk copy is bounded.
+#include <cuda_bf16.h>
 #include <string.h>
 #include <mutex>
 #include <type_traits>
@@ -72,6 +73,9 @@ struct BatchArgs {
   const float *gx;             // matrix-vector launches (count == 1), see DecodeArgs
   float *partial;
   uint32_t in, seg;
+  const uint16_t *grad;        // update launches (count == 1): gradient, AdamW moments (bf16)
+  uint16_t *exp_avg, *exp_avg_sq;
+  AdamArgs adam;
   uint32_t inputs_stable;      // containers and fractions were complete before the previous kernel
   uint32_t count;
   uint32_t n_ctas;        // == gridDim.x
@@ -256,6 +260,64 @@ struct DotSink {
   DotLane lane[kChains];
   __device__ __forceinline__ void begin(int c) { lane[c].begin(); }
   __device__ __forceinline__ void put(int c, int, const uint32_t (&w)[4]) { lane[c].put(w); }
+  __device__ __forceinline__ void advance(int) {}
+};
+
+// Update launches: the four decoded words of a block (8 weights of one row) take an
+// AdamW step against the gradient and the moments at the same place of their (row-major)
+// tensors and go, rounded to bf16 once, to the output tensor; the moments are updated in
+// place.  Gradient and moments of a block are requested before its symbols are decoded.
+__device__ __forceinline__ void adamw_words(const uint32_t (&w)[4], const uint4 &gv, uint4 &mv,
+                                            uint4 &vv, const AdamArgs &a, uint4 &out) {
+  const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+  uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w}, ow[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    uint32_t res = 0, mres = 0, vres = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t sh = 16 * h;
+      float m = __bfloat162float(__ushort_as_bfloat16((unsigned short)(mw[k] >> sh)));
+      float v = __bfloat162float(__ushort_as_bfloat16((unsigned short)(vw[k] >> sh)));
+      const float x = adamw_element(
+          __bfloat162float(__ushort_as_bfloat16((unsigned short)(w[k] >> sh))),
+          __bfloat162float(__ushort_as_bfloat16((unsigned short)(gw[k] >> sh))), m, v, a);
+      res |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x)) << sh;
+      mres |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(m)) << sh;
+      vres |= (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v)) << sh;
+    }
+    ow[k] = res;
+    mw[k] = mres;
+    vw[k] = vres;
+  }
+  out = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  mv = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+  vv = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+}
+
+template <int ADV>
+struct UpdateSinkT {
+  uint16_t *out[kChains];
+  const uint16_t *g[kChains];
+  uint16_t *m[kChains], *v[kChains];
+  uint4 gv[kChains], mv[kChains], vv[kChains];
+  int blk[kChains];
+  AdamArgs adam;
+  __device__ __forceinline__ void begin(int c) {
+    const int o = blk[c] * ADV;
+    gv[c] = __ldcs(reinterpret_cast<const uint4 *>(g[c] + o));
+    mv[c] = __ldcs(reinterpret_cast<const uint4 *>(m[c] + o));
+    vv[c] = __ldcs(reinterpret_cast<const uint4 *>(v[c] + o));
+  }
+  __device__ __forceinline__ void put(int c, int, const uint32_t (&w)[4]) {
+    uint4 res;
+    adamw_words(w, gv[c], mv[c], vv[c], adam, res);
+    const int o = blk[c] * ADV;
+    __stcs(reinterpret_cast<uint4 *>(out[c] + o), res);
+    __stcs(reinterpret_cast<uint4 *>(m[c] + o), mv[c]);
+    __stcs(reinterpret_cast<uint4 *>(v[c] + o), vv[c]);
+    ++blk[c];
+  }
   __device__ __forceinline__ void advance(int) {}
 };
 
@@ -561,6 +623,39 @@ __device__ __forceinline__ void init_sink(DotSink &sk, int c, const DecodeArgs &
 }
 template <int ADV>
 __device__ __forceinline__ void finish_sink(StoreSinkT<ADV> &) {}
+template <int ADV>
+__device__ __forceinline__ void init_sink(UpdateSinkT<ADV> &sk, int c, const DecodeArgs &a, uint32_t,
+                                          uint64_t out_elem, uint32_t) {
+  const uint64_t o = out_index(a, out_elem);
+  sk.out[c] = a.out_bf16 + o;
+  sk.g[c] = a.grad + o;
+  sk.m[c] = a.exp_avg + o;
+  sk.v[c] = a.exp_avg_sq + o;
+  sk.blk[c] = 0;
+  sk.adam = a.adam;
+}
+template <int ADV>
+__device__ __forceinline__ void finish_sink(UpdateSinkT<ADV> &) {}
+
+// Update launches, units that do not take the fast path: the unit has just been decoded
+// into the output tensor the ordinary way; its elements take their step there.
+__device__ __forceinline__ void update_decoded_unit(const DecodeArgs &a, uint32_t u, uint32_t lane) {
+  if (u >= a.n_units) return;
+  const uint64_t U = 32ull * a.S;
+  const uint64_t first = (uint64_t)u * U;
+  const uint64_t count = (a.n - first < U) ? (a.n - first) : U;
+  __syncwarp();
+  for (uint64_t i = lane; i < count; i += 32) {
+    const uint64_t o = out_index(a, first + i);
+    float m = __bfloat162float(__ushort_as_bfloat16(a.exp_avg[o]));
+    float v = __bfloat162float(__ushort_as_bfloat16(a.exp_avg_sq[o]));
+    const float x = adamw_element(__bfloat162float(__ushort_as_bfloat16(a.out_bf16[o])),
+                                  __bfloat162float(__ushort_as_bfloat16(a.grad[o])), m, v, a.adam);
+    a.out_bf16[o] = __bfloat16_as_ushort(__float2bfloat16_rn(x));
+    a.exp_avg[o] = __bfloat16_as_ushort(__float2bfloat16_rn(m));
+    a.exp_avg_sq[o] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  }
+}
 __device__ __forceinline__ void finish_sink(DotSink &sk) {
 #pragma unroll
   for (int c = 0; c < kChains; ++c) sk.lane[c].finish();
@@ -656,13 +751,15 @@ __global__ void dot_finish_kernel(const float *__restrict__ partial, uint32_t se
 // batch.unit_list (of the single tensor item[0]) and writes them one after the other.
 // MODE kModeDot: matrix-vector launch -- nothing is written back; every unit's
 // elements are multiplied with the input vector as they are decoded.
-constexpr int kModeTensor = 0, kModeList = 1, kModeDot = 2;
+constexpr int kModeTensor = 0, kModeList = 1, kModeDot = 2, kModeUpdate = 3;
+constexpr int kUpdateMaxWarps = 16;                 // the update's operands want registers
 constexpr int kDotMaxWarps = NZ_DECODE_MAX_WARPS;   // 16 warps and 128 registers measured slower
 template <int S, bool MERGE, int MODE>
-__global__ void __launch_bounds__((MODE == kModeDot ? kDotMaxWarps : NZ_DECODE_MAX_WARPS) * 32, 1)
+__global__ void __launch_bounds__((MODE == kModeDot ? kDotMaxWarps : MODE == kModeUpdate ? kUpdateMaxWarps : NZ_DECODE_MAX_WARPS) * 32, 1)
 decode_kernel(const BatchArgs batch) {
   constexpr bool LIST = MODE == kModeList;
   constexpr bool DOT = MODE == kModeDot;
+  constexpr bool UPDATE = MODE == kModeUpdate;
   extern __shared__ __align__(128) uint8_t smem[];
   // which tensor this CTA works on, and its rank among that tensor's CTAs
   uint32_t ti = 0;
@@ -693,7 +790,11 @@ decode_kernel(const BatchArgs batch) {
   a.partial = DOT ? batch.partial : nullptr;
   a.in = DOT ? batch.in : 0;
   a.seg = DOT ? batch.seg : 0;
-  a.tile_cols = (MODE == kModeTensor && MERGE) ? batch.item[ti].tile_cols : 0;
+  a.tile_cols = ((MODE == kModeTensor || UPDATE) && MERGE) ? batch.item[ti].tile_cols : 0;
+  a.grad = UPDATE ? batch.grad : nullptr;
+  a.exp_avg = UPDATE ? batch.exp_avg : nullptr;
+  a.exp_avg_sq = UPDATE ? batch.exp_avg_sq : nullptr;
+  if (UPDATE) a.adam = batch.adam;
   const uint32_t n_warps = blockDim.x >> 5;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t lut_bytes = 4096u << a.lut_shift;           // 2^pb slots would need 4 << shift each
@@ -829,6 +930,14 @@ decode_kernel(const BatchArgs batch) {
         if (DOT) {
           typename std::conditional<DOT, DotSink, StoreSink>::type sink;
           run(sink);
+        } else if (UPDATE) {
+          if (a.tile_cols) {
+            typename std::conditional<UPDATE, UpdateSinkT<64>, StoreSink>::type sink;
+            run(sink);
+          } else {
+            typename std::conditional<UPDATE, UpdateSinkT<256>, StoreSink>::type sink;
+            run(sink);
+          }
         } else if (MODE == kModeTensor && MERGE && a.tile_cols) {
           typename std::conditional<DOT, DotSink, StoreSinkT<64>>::type sink;     // operand order
           run(sink);
@@ -851,6 +960,7 @@ decode_kernel(const BatchArgs batch) {
           const int64_t delta = LIST ? ((int64_t)(u + c) - (int64_t)real[c]) * (int64_t)U : 0;
           decode_single<S, MERGE>(a, pl[c], real[c], delta, slot0 + c * a.slot_bytes, lv, canon,
                                   payload, lenq, lane);
+          if (UPDATE) update_decoded_unit(a, real[c], lane);
         }
       }
     }
@@ -878,6 +988,9 @@ struct HostItem {
   uint32_t flags;              // NZ_ITEM_* of the C interface
   uint32_t tile_cols;          // operand order: row length of the matrix (0 = stream order)
   uint32_t S;                  // lane symbols of this tensor
+  const uint16_t *grad;        // update: gradient and AdamW moments (bf16, else null)
+  uint16_t *exp_avg, *exp_avg_sq;
+  AdamArgs adam;
 };
 
 // Units a launch decodes for an item.
@@ -911,7 +1024,8 @@ static int decode_geometry(const HostItem *items, uint32_t count, uint32_t ring_
   b.slot_bytes = (uint32_t)((unit_bytes + 32 + 15) & ~uint64_t(15));
   const uint32_t guard = ((S + 8) * 2 + 127) & ~127u;
   const uint32_t sm_smem = 227u * 1024u;
-  const uint32_t kMaxWarps = items[0].gx ? (uint32_t)kDotMaxWarps : (uint32_t)NZ_DECODE_MAX_WARPS;
+  const uint32_t kMaxWarps = items[0].gx ? (uint32_t)kDotMaxWarps
+                             : items[0].grad ? (uint32_t)kUpdateMaxWarps : (uint32_t)NZ_DECODE_MAX_WARPS;
   const uint32_t per_warp = kChains * b.slot_bytes + ring_bytes;
   const uint32_t min_fixed = 16 * 1024 + 1024 + guard;
   if (min_fixed + per_warp > sm_smem) {
@@ -1064,6 +1178,11 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
     b.partial = live[0].partial;
     b.in = live[0].in;
     b.seg = live[0].seg;
+    const bool update = live[0].grad != nullptr;        // and update calls
+    b.grad = live[0].grad;
+    b.exp_avg = live[0].exp_avg;
+    b.exp_avg_sq = live[0].exp_avg_sq;
+    b.adam = live[0].adam;
     b.inputs_stable = 1;
     for (uint32_t t = 0; t < n_live; ++t)
       if (!(live[t].flags & NZ_ITEM_INPUTS_STABLE)) b.inputs_stable = 0;
@@ -1074,6 +1193,14 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
         case 1: return launch_decode<1, true, kModeList>(b, warps, smem_bytes, st);
         case 3: return launch_decode<3, true, kModeList>(b, warps, smem_bytes, st);
         default: return launch_decode<7, true, kModeList>(b, warps, smem_bytes, st);
+      }
+    }
+    if (update) {
+      switch (precision) {
+        case 0: return launch_decode<0, true, kModeUpdate>(b, warps, smem_bytes, st);
+        case 1: return launch_decode<1, true, kModeUpdate>(b, warps, smem_bytes, st);
+        case 3: return launch_decode<3, true, kModeUpdate>(b, warps, smem_bytes, st);
+        default: return launch_decode<7, true, kModeUpdate>(b, warps, smem_bytes, st);
       }
     }
     if (dot) {
@@ -1130,6 +1257,8 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   it.flags = 0;
   it.tile_cols = 0;
   it.S = 0;
+  it.grad = nullptr;
+  it.exp_avg = it.exp_avg_sq = nullptr;
   return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
@@ -1146,6 +1275,28 @@ int decode_operand(const void *container, uint64_t container_bytes, const void *
   it.max_unit_words = max_unit_words;
   it.out_bf16 = out_bf16;
   it.tile_cols = (uint32_t)cols;
+  return decode_many(&it, 1, precision, S, canon, true, status, st);
+}
+
+// Decode a tensor and apply an AdamW step to it on the way out: out_bf16 receives the
+// updated (row-major) weights, the moments (bf16) are updated in place.
+int decode_update(const void *container, uint64_t container_bytes, const void *frac, uint64_t n,
+                  uint64_t operand_cols, int precision, uint32_t S, uint32_t max_unit_words,
+                  int canon, const void *grad, void *exp_avg, void *exp_avg_sq, const AdamArgs &adam,
+                  void *out_bf16, void *status, cudaStream_t st) {
+  HostItem it;
+  memset(&it, 0, sizeof(it));
+  it.container = container;
+  it.container_bytes = container_bytes;
+  it.frac = frac;
+  it.n = n;
+  it.max_unit_words = max_unit_words;
+  it.out_bf16 = out_bf16;
+  it.tile_cols = (uint32_t)operand_cols;
+  it.grad = (const uint16_t *)grad;
+  it.exp_avg = (uint16_t *)exp_avg;
+  it.exp_avg_sq = (uint16_t *)exp_avg_sq;
+  it.adam = adam;
   return decode_many(&it, 1, precision, S, canon, true, status, st);
 }
 
@@ -1241,6 +1392,8 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
       host[i].flags = it.flags;
       host[i].tile_cols = 0;
       host[i].S = 0;
+      host[i].grad = nullptr;
+      host[i].exp_avg = host[i].exp_avg_sq = nullptr;
       if (it.lane_symbols) {
         if (!nz::valid_lane_symbols(it.lane_symbols)) {
           nz::set_error("nz_decompress_bf16_batch: item %u: lane_symbols must be a multiple of 8 "
@@ -1306,6 +1459,8 @@ extern "C" int nz_decompress_bf16_units(const void *container, uint64_t containe
   it.flags = 0;
   it.tile_cols = 0;
   it.S = 0;
+  it.grad = nullptr;
+  it.exp_avg = it.exp_avg_sq = nullptr;
   return nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                          (cudaStream_t)stream);
 }
@@ -1501,6 +1656,8 @@ extern "C" int nz_linear_vec_bf16(const void *container, uint64_t container_byte
   it.flags = 0;
   it.tile_cols = 0;
   it.S = 0;
+  it.grad = nullptr;
+  it.exp_avg = it.exp_avg_sq = nullptr;
   rc = nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                        (cudaStream_t)stream);
   if (rc) return rc;

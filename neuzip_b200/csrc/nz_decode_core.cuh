@@ -290,6 +290,10 @@ struct DecodeArgs {
   uint32_t in;                 //   row length of the [out, in] matrix, a multiple of 256
   uint32_t seg;                //   rows a unit can touch
   uint32_t tile_cols;          // operand order: row length of the matrix (0 = the stream is the tensor)
+  // update launches: gradient (bf16) and AdamW moments (bf16), indexed like the output tensor
+  const uint16_t *grad;
+  uint16_t *exp_avg, *exp_avg_sq;
+  AdamArgs adam;
 };
 
 // Operand order.  A [rows, cols] matrix (rows % 4 == 0, cols % 64 == 0) may be stored

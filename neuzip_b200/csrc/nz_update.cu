@@ -8,10 +8,6 @@
 
 namespace nz {
 
-struct AdamArgs {
-  float lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale;
-};
-
 __device__ __forceinline__ float load_state(const float *p, uint64_t i) { return p[i]; }
 __device__ __forceinline__ float load_state(const __nv_bfloat16 *p, uint64_t i) {
   return __bfloat162float(p[i]);
@@ -36,30 +32,20 @@ adamw_kernel(__nv_bfloat16 *__restrict__ w, const __nv_bfloat16 *__restrict__ g,
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const uint64_t e = i * 8 + k;
-      const float grad = __bfloat162float(gp[k]) * a.grad_scale;
       float mm = load_state(m, e), vv = load_state(v, e);
-      mm = a.beta1 * mm + (1.0f - a.beta1) * grad;
-      vv = a.beta2 * vv + (1.0f - a.beta2) * grad * grad;
+      const float x = adamw_element(__bfloat162float(wp[k]), __bfloat162float(gp[k]), mm, vv, a);
       store_state(m, e, mm);
       store_state(v, e, vv);
-      float x = __bfloat162float(wp[k]);
-      x *= 1.0f - a.lr * a.weight_decay;
-      x -= (a.lr / a.bias1) * mm / (sqrtf(vv / a.bias2) + a.eps);
       wp[k] = __float2bfloat16_rn(x);
     }
     reinterpret_cast<uint4 *>(w)[i] = wv;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     for (uint64_t e = n_vec * 8; e < n; ++e) {
-      const float grad = __bfloat162float(g[e]) * a.grad_scale;
       float mm = load_state(m, e), vv = load_state(v, e);
-      mm = a.beta1 * mm + (1.0f - a.beta1) * grad;
-      vv = a.beta2 * vv + (1.0f - a.beta2) * grad * grad;
+      const float x = adamw_element(__bfloat162float(w[e]), __bfloat162float(g[e]), mm, vv, a);
       store_state(m, e, mm);
       store_state(v, e, vv);
-      float x = __bfloat162float(w[e]);
-      x *= 1.0f - a.lr * a.weight_decay;
-      x -= (a.lr / a.bias1) * mm / (sqrtf(vv / a.bias2) + a.eps);
       w[e] = __float2bfloat16_rn(x);
     }
   }
@@ -104,4 +90,92 @@ extern "C" int nz_adamw_bf16(void *weight_bf16, const void *grad_bf16, void *exp
         (float *)exp_avg_sq, n, a);
   NZ_LAUNCH_CHECK("adamw_kernel");
   return NZ_OK;
+}
+
+namespace nz {
+int decode_update(const void *container, uint64_t container_bytes, const void *frac, uint64_t n,
+                  uint64_t operand_cols, int precision, uint32_t S, uint32_t max_unit_words,
+                  int canon, const void *grad, void *exp_avg, void *exp_avg_sq, const AdamArgs &adam,
+                  void *out_bf16, void *status, cudaStream_t st);
+int compress_bf16_fused(const void *in, uint64_t n, int precision, uint32_t LS, uint32_t cols,
+                        void *frac_out, void *container, uint64_t container_cap, void *scratch,
+                        uint64_t scratch_bytes, cudaStream_t st);
+uint64_t compress_fused_scratch_bytes(uint64_t n, uint32_t LS);
+}  // namespace nz
+
+extern "C" uint64_t nz_adamw_compressed_scratch_bytes(uint64_t n, uint32_t lane_symbols) {
+  if (!nz::valid_lane_symbols(lane_symbols)) return 0;
+  // the updated bf16 weights, then the compressor's own scratch
+  return nz::align16(2 * n) + nz::compress_fused_scratch_bytes(n, lane_symbols);
+}
+
+extern "C" int nz_adamw_compressed_bf16(const void *container, uint64_t container_bytes,
+                                        const void *frac_in, uint64_t n, uint64_t operand_cols,
+                                        int precision, uint32_t lane_symbols,
+                                        uint32_t max_unit_words, int canonical_nan,
+                                        const void *grad_bf16, void *exp_avg_bf16,
+                                        void *exp_avg_sq_bf16, float lr, float beta1, float beta2,
+                                        float eps, float weight_decay, uint32_t step,
+                                        float grad_scale, void *frac_out, void *container_out,
+                                        uint64_t container_cap, void *scratch,
+                                        uint64_t scratch_bytes, void *status, void *stream) {
+  if (!nz::valid_precision(precision) || !nz::valid_lane_symbols(lane_symbols)) {
+    nz::set_error("nz_adamw_compressed_bf16: bad precision %d or lane_symbols %u", precision,
+                  lane_symbols);
+    return NZ_E_ARG;
+  }
+  if (n == 0 || n >= (1ull << 32) || step == 0) {
+    nz::set_error("nz_adamw_compressed_bf16: between 1 and 2^32 - 1 elements, step >= 1");
+    return NZ_E_ARG;
+  }
+  if (operand_cols) {
+    const uint64_t c = operand_cols;
+    if (c % 64 || n % (4 * c) || (c / 64) % (lane_symbols / 8) || c >= (1ull << 31)) {
+      nz::set_error("nz_adamw_compressed_bf16: %llu elements in rows of %llu are not in operand "
+                    "order for lane_symbols %u", (unsigned long long)n, (unsigned long long)c,
+                    lane_symbols);
+      return NZ_E_ARG;
+    }
+  } else if (n % 8) {
+    // the fused path moves 8 elements (16 bytes) of gradient and moments per lane
+    nz::set_error("nz_adamw_compressed_bf16: the element count must be a multiple of 8");
+    return NZ_E_ARG;
+  }
+  if (!container || ((uintptr_t)container & 15) || !frac_in || ((uintptr_t)frac_in & 7) ||
+      !grad_bf16 || ((uintptr_t)grad_bf16 & 15) || !exp_avg_bf16 || ((uintptr_t)exp_avg_bf16 & 15) ||
+      !exp_avg_sq_bf16 || ((uintptr_t)exp_avg_sq_bf16 & 15) || !frac_out || ((uintptr_t)frac_out & 7) ||
+      !container_out || ((uintptr_t)container_out & 15) || !scratch || ((uintptr_t)scratch & 15)) {
+    nz::set_error("nz_adamw_compressed_bf16: null or misaligned pointer (containers, gradient, "
+                  "moments and scratch 16-byte, fractions 8-byte aligned)");
+    return NZ_E_ARG;
+  }
+  const uint64_t need = nz_adamw_compressed_scratch_bytes(n, lane_symbols);
+  if (scratch_bytes < need) {
+    nz::set_error("nz_adamw_compressed_bf16: scratch of %llu bytes is smaller than the %llu required",
+                  (unsigned long long)scratch_bytes, (unsigned long long)need);
+    return NZ_E_CAPACITY;
+  }
+  if (container_bytes < nz::payload_offset(nz::unit_count(n, lane_symbols))) {
+    nz::set_error("nz_adamw_compressed_bf16: container too short");
+    return NZ_E_FORMAT;
+  }
+  nz::AdamArgs a;
+  a.lr = lr;
+  a.beta1 = beta1;
+  a.beta2 = beta2;
+  a.eps = eps;
+  a.weight_decay = weight_decay;
+  a.bias1 = 1.0f - powf(beta1, (float)step);
+  a.bias2 = 1.0f - powf(beta2, (float)step);
+  a.grad_scale = grad_scale;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t *w_new = (uint8_t *)scratch;
+  uint8_t *rest = w_new + nz::align16(2 * n);
+  int rc = nz::decode_update(container, container_bytes, frac_in, n, operand_cols, precision,
+                             lane_symbols, max_unit_words, canonical_nan, grad_bf16, exp_avg_bf16,
+                             exp_avg_sq_bf16, a, w_new, status, st);
+  if (rc) return rc;
+  return nz::compress_bf16_fused(w_new, n, precision, lane_symbols, (uint32_t)operand_cols, frac_out,
+                                 container_out, container_cap, rest, scratch_bytes - nz::align16(2 * n),
+                                 st);
 }

@@ -34,7 +34,7 @@ class CompressedAdamW:
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-4,
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  process_group=None, overlap_allreduce: bool = True,
-                 state_dtype: torch.dtype = torch.float32) -> None:
+                 state_dtype: torch.dtype = torch.float32, fused_update: bool = True) -> None:
         params = list(params)
         self.compressed: List[Parameter] = [p for p in params if isinstance(p, Parameter)]
         plain = [p for p in params if not isinstance(p, Parameter) and p.requires_grad]
@@ -46,6 +46,7 @@ class CompressedAdamW:
         self.state: Dict[int, dict] = {}
         self.steps = 0
         self.state_dtype = state_dtype
+        self.fused_update = fused_update      # bf16 moments: the step runs inside the decode kernel
         from . import _lib
         self._lib_mod = _lib
         self._lib = _lib.load()
@@ -117,6 +118,15 @@ class CompressedAdamW:
                 st = {"m": torch.zeros(g.shape, dtype=self.state_dtype, device=g.device),
                       "v": torch.zeros(g.shape, dtype=self.state_dtype, device=g.device)}
                 self.state[id(p)] = st
+            fused = getattr(getattr(p._manager, "_be", None), "adamw_update", None)
+            if (fused is not None and self.fused_update and self.state_dtype == torch.bfloat16
+                    and fused(p._handle, g, st["m"], st["v"], self.lr, b1, b2, self.eps,
+                              self.weight_decay, self.steps, 1.0 / self.world)):
+                # decode, step and recompress in one library call (the step runs inside the
+                # decode kernel); same bits as the three separate calls below
+                p._gradient = None
+                p.grad = None
+                continue
             w = p()                                                    # decode (bf16, contiguous)
             self._lib_mod.check(self._lib.nz_adamw_bf16(
                 w.data_ptr(), g.data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(), w.numel(),

@@ -564,3 +564,40 @@ def test_layerwise_hooks_follow_weight_updates_and_loaded_checkpoints():
         plain = model(ids).logits.float()
     assert torch.equal(hooked, plain)
     m.check()
+
+
+@pytest.mark.parametrize("precision,shape,operand", ((7, (256, 2048), True), (3, (128, 4096), True),
+                                                     (7, (96, 1000), False), (1, (33, 520), False)))
+def test_fused_update_equals_read_adamw_write_bit_for_bit(precision, shape, operand):
+    """nz_adamw_compressed_bf16 (the AdamW step inside the decode kernel, then the
+    compressor) against read -> nz_adamw_bf16 -> write: same containers, fractions and
+    moments, three steps in a row; stream order with a ragged last unit, and operand order."""
+    from neuzip_b200 import _lib
+    L = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(precision + shape[0])
+    w = weights(shape, 5).cuda()
+    ma, mb = neuzip.Manager(precision=precision), neuzip.Manager(precision=precision)
+    ha, hb = ma.write(w, operand=operand), mb.write(w, operand=operand)
+    assert (ma._be.entry(ha).operand_cols > 0) == operand
+    n = w.numel()
+    m1 = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    v1 = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    m2, v2 = m1.clone(), v1.clone()
+    for step in range(1, 4):
+        g = (torch.randn(shape, device="cuda") * 1e-2).to(torch.bfloat16).contiguous()
+        # a: the single fused call
+        assert ma._be.adamw_update(ha, g.view(-1), m1, v1, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, 0.5)
+        # b: read, stand-alone update kernel, write
+        wb = mb.read(hb).contiguous()
+        _lib.check(L.nz_adamw_bf16(wb.data_ptr(), g.data_ptr(), m2.data_ptr(), v2.data_ptr(), n, 1,
+                                   1e-2, 0.9, 0.999, 1e-8, 0.1, step, 0.5, st))
+        mb.write(wb, hb)
+        ea, eb = ma._be.entry(ha), mb._be.entry(hb)
+        assert ea.operand_cols == eb.operand_cols
+        assert torch.equal(m1, m2) and torch.equal(v1, v2), step
+        assert torch.equal(ea.fractions, eb.fractions), step
+        assert torch.equal(ea.container, eb.container), step
+    assert not torch.equal(ma.read(ha), w)            # the weights did move
+    ma.check()
+    mb.check()
