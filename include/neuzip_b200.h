@@ -251,7 +251,12 @@ typedef struct nz_decompress_item {
                                 the output is row-major either way          */
   uint32_t lane_symbols;     /* 0 = the call's lane_symbols; else this
                                 tensor's own (tensors of one call may differ) */
-  uint32_t reserved;         /* 0                                           */
+  uint32_t normalizer_group; /* group size of the block normaliser, when
+                                `normalizers` is set (a power of two <= 1024) */
+  const void *normalizers;   /* NULL, or the bytes nz_normalize_bf16 wrote:
+                                the decoder multiplies every group by its
+                                scale as it writes it (stream order only),
+                                which replaces nz_denormalize_bf16          */
 } nz_decompress_item;
 
 /* nz_decompress_bf16 for several tensors of the same precision (for instance the
@@ -298,6 +303,19 @@ int nz_gather_rows_bf16(const void *container, uint64_t container_bytes,
                         int canonical_nan, uint64_t row_len, const void *rows_i64,
                         uint32_t n_rows_out, void *out_bf16, void *scratch,
                         uint64_t scratch_bytes, void *status, void *stream);
+
+/* nz_gather_rows_bf16 for a table written with a block normaliser: the rows come
+ * out multiplied by their groups' scales (normalizers = the bytes
+ * nz_normalize_bf16 wrote for the whole table, normalizer_group its group size;
+ * NULL / 0 = none).
+ * Reference: cuda/kernels.cuh:208-216 inside Embedding.forward's full read. */
+int nz_gather_rows_normalized_bf16(const void *container, uint64_t container_bytes,
+                                   const void *frac_in, uint64_t n, int precision,
+                                   uint32_t lane_symbols, uint32_t max_unit_words,
+                                   int canonical_nan, uint64_t row_len, const void *rows_i64,
+                                   uint32_t n_rows_out, const void *normalizers,
+                                   uint32_t normalizer_group, void *out_bf16, void *scratch,
+                                   uint64_t scratch_bytes, void *status, void *stream);
 
 /* y = W x (+ bias) for one input vector, with W the compressed [out, in]
  * row-major bf16 matrix of n = out * in elements: the weights are multiplied as

@@ -59,7 +59,8 @@ class DecompressItem(ctypes.Structure):
     """struct nz_decompress_item"""
     _fields_ = [("container", _vp), ("container_bytes", _u64), ("frac_in", _vp), ("n", _u64),
                 ("max_unit_words", _u32), ("flags", _u32), ("out_bf16", _vp),
-                ("operand_cols", _u64), ("lane_symbols", _u32), ("reserved", _u32)]
+                ("operand_cols", _u64), ("lane_symbols", _u32), ("normalizer_group", _u32),
+                ("normalizers", _vp)]
 
 
 _f32 = ctypes.c_float
@@ -70,6 +71,9 @@ SIGNATURES["nz_decompress_bf16_units"] = (
 SIGNATURES["nz_gather_scratch_bytes"] = (_u64, [_u32, _u64, _u32])
 SIGNATURES["nz_gather_rows_bf16"] = (
     _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _u64, _vp, _u32, _vp, _vp, _u64, _vp, _vp])
+SIGNATURES["nz_gather_rows_normalized_bf16"] = (
+    _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _u64, _vp, _u32, _vp, _u32, _vp, _vp, _u64, _vp,
+           _vp])
 SIGNATURES["nz_linear_vec_scratch_bytes"] = (_u64, [_u64, _u64, _u32])
 SIGNATURES["nz_linear_vec_bf16"] = (
     _int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp])

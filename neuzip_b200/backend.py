@@ -332,10 +332,10 @@ class CodecBackend:
         item[0].out_bf16 = _ptr(out)
         item[0].operand_cols = entry.operand_cols
         item[0].lane_symbols = entry.lane_symbols
+        self._set_normalizer(item[0], entry)
         _lib.check(self._lib.nz_decompress_bf16_batch(
             item, 1, self.precision, entry.lane_symbols, int(self.canonical_nan),
             _ptr(self._status), _stream()))
-        self._denormalize(entry, out)
 
     def read_rows(self, name: str, rows: torch.Tensor, row_len: int) -> torch.Tensor:
         """Rows ``rows`` (any integer tensor) of the stored tensor seen as a
@@ -353,9 +353,8 @@ class CodecBackend:
         k = rows.numel()
         if k == 0:
             return torch.empty(0, row_len, dtype=torch.bfloat16, device="cuda")
-        if entry.normalizers is not None or entry.operand_cols:
-            # group scales follow the flat element index, and a matrix in operand order
-            # interleaves four rows per block: decode everything, then pick
+        if entry.operand_cols:
+            # a matrix in operand order interleaves four rows per block: decode everything
             return self.read(name).view(-1, row_len)[rows]
         U = 32 * entry.lane_symbols
         per_row = 1 if U % row_len == 0 else (row_len // U if row_len % U == 0
@@ -367,17 +366,23 @@ class CodecBackend:
         L = self._lib
         scratch_bytes = int(L.nz_gather_scratch_bytes(k, row_len, entry.lane_symbols))
         scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device="cuda")
-        _lib.check(L.nz_gather_rows_bf16(
+        _lib.check(L.nz_gather_rows_normalized_bf16(
             _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), entry.numel,
             self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
-            row_len, _ptr(rows), k, _ptr(out), _ptr(scratch), scratch_bytes, _ptr(self._status),
-            _stream()))
+            row_len, _ptr(rows), k, _ptr(entry.normalizers),
+            self.normalizer_size if entry.normalizers is not None else 0, _ptr(out), _ptr(scratch),
+            scratch_bytes, _ptr(self._status), _stream()))
         return out
 
-    def _denormalize(self, entry: _Entry, out: torch.Tensor) -> None:
+    def _set_normalizer(self, item, entry: _Entry) -> None:
+        """Tensors written with a block normaliser are scaled back by the decoder itself
+        (cuda/kernels.cuh:208-216 of the reference does it in its merge kernel)."""
         if entry.normalizers is not None:
-            _lib.check(self._lib.nz_denormalize_bf16(_ptr(out), entry.numel, self.normalizer_size,
-                                                     _ptr(entry.normalizers), _stream()))
+            item.normalizers = _ptr(entry.normalizers)
+            item.normalizer_group = self.normalizer_size
+        else:
+            item.normalizers = None
+            item.normalizer_group = 0
 
     def read_many(self, names: Sequence[str]) -> List[torch.Tensor]:
         """Decompress several tensors (for instance all matrices of one layer) with
@@ -405,11 +410,10 @@ class CodecBackend:
                 items[k].out_bf16 = _ptr(outs[k])
                 items[k].operand_cols = e.operand_cols
                 items[k].lane_symbols = e.lane_symbols
+                self._set_normalizer(items[k], e)
             _lib.check(self._lib.nz_decompress_bf16_batch(
                 items, len(entries), self.precision, entries[0].lane_symbols,
                 int(self.canonical_nan), _ptr(self._status), _stream()))
-        for e, out in zip(entries, outs):
-            self._denormalize(e, out)
         return outs
 
     def make_batch(self, names: Sequence[str], outs: Sequence[torch.Tensor]) -> _Batch:
@@ -444,6 +448,7 @@ class CodecBackend:
                 items[k].out_bf16 = _ptr(out)
                 items[k].operand_cols = e.operand_cols
                 items[k].lane_symbols = e.lane_symbols
+                self._set_normalizer(items[k], e)
             blocks.append(items)
         # the entries keep their tensors alive as long as the batch refers to them
         batch.entries, batch.blocks, batch.lane_symbols = entries, blocks, entries[0].lane_symbols
@@ -463,9 +468,6 @@ class CodecBackend:
                                                 _ptr(self._status), _stream())
         if rc:
             _lib.check(rc)
-        if self.normalizer_size:
-            for e, out in zip(batch.entries, batch.outs):
-                self._denormalize(e, out)
 
     def size(self, name: str) -> int:
         """cuda/high_level.cu:208-221: stored bytes, 0 for an unknown name."""

@@ -65,6 +65,8 @@ struct BatchItem {
   uint32_t cta_begin;     // first CTA of this tensor
   uint32_t tile_cols;     // operand order: row length (0 = stream order)
   uint32_t S;             // lane symbols of this tensor
+  const uint8_t *norm;    // block normaliser bytes (null = none), log2 of the group size
+  uint32_t norm_lg;
 };
 struct BatchArgs {
   BatchItem item[kMaxBatch];
@@ -160,8 +162,9 @@ __device__ __forceinline__ void emit_guarded(uint32_t sym, uint64_t e, int64_t d
     const uint64_t bit = e * (S + 1);
     const uint32_t shift = 7 - S - (uint32_t)(bit & 7);
     const uint32_t field = ((uint32_t)a.frac[bit >> 3] >> shift) & ((2u << S) - 1u);
-    a.out_bf16[out_index(a, e) + delta] =
-        (uint16_t)merge_pair_generic<S>(sym << kEntSymShift, 0, field, 0, a.canon != 0);
+    uint32_t v = merge_pair_generic<S>(sym << kEntSymShift, 0, field, 0, a.canon != 0) & 0xFFFFu;
+    if (a.norm) v = scale_bf16_bits(v, norm_scale(a.norm[e >> a.norm_lg]));
+    a.out_bf16[out_index(a, e) + delta] = (uint16_t)v;
   } else {
     a.out_exp[e + delta] = (uint8_t)sym;
   }
@@ -261,6 +264,45 @@ struct DotSink {
   __device__ __forceinline__ void begin(int c) { lane[c].begin(); }
   __device__ __forceinline__ void put(int c, int, const uint32_t (&w)[4]) { lane[c].put(w); }
   __device__ __forceinline__ void advance(int) {}
+};
+
+// A sink in front of another: tensors written with a block normaliser are multiplied by
+// their group's scale as they are produced (8 elements of a lane share one stored byte for
+// groups of 8 and more, else each run of `group` elements has its own).
+template <class Inner>
+struct NormSink {
+  Inner inner;
+  const uint8_t *norm;
+  uint32_t lg;
+  uint32_t e0[kChains];       // tensor index of the lane's first element of the unit
+  int blk[kChains];
+  uint64_t bytes[kChains];
+  __device__ __forceinline__ void begin(int c) {
+    inner.begin(c);
+    const uint32_t e = e0[c] + ((uint32_t)blk[c] << 8);
+    if (lg >= 3) {
+      bytes[c] = __ldg(norm + (e >> lg));
+    } else {
+      const uint8_t *p = norm + (e >> lg);
+      uint64_t b = 0;
+      const int count = 8 >> lg;
+      for (int i = 0; i < count; ++i) b |= (uint64_t)__ldg(p + i) << (8 * i);
+      bytes[c] = b;
+    }
+  }
+  __device__ __forceinline__ void put(int c, int k, const uint32_t (&w)[4]) {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t i0 = 2 * j, i1 = 2 * j + 1;
+      const float s0 = norm_scale((uint32_t)(bytes[c] >> (lg >= 3 ? 0 : 8 * (i0 >> lg))) & 0xFFu);
+      const float s1 = norm_scale((uint32_t)(bytes[c] >> (lg >= 3 ? 0 : 8 * (i1 >> lg))) & 0xFFu);
+      o[j] = scale_bf16_bits(w[j] & 0xFFFFu, s0) | (scale_bf16_bits(w[j] >> 16, s1) << 16);
+    }
+    inner.put(c, k, o);
+    ++blk[c];
+  }
+  __device__ __forceinline__ void advance(int n) { inner.advance(n); }
 };
 
 // Update launches: the four decoded words of a block (8 weights of one row) take an
@@ -585,8 +627,20 @@ __device__ __forceinline__ void decode_single(const DecodeArgs &a, const UnitPla
     if (lane == 0) raise(a.status, NZ_STATUS_BAD_LANES);
     return;
   }
-  const uint32_t full_blocks = (uint32_t)(count / 256);
   const uint64_t e_lane = first + lane * 8;
+  if (MERGE && a.norm) {
+    // a unit decoded on its own in a tensor with a block normaliser: element by element
+    const uint32_t blocks = (uint32_t)((count + 255) / 256);
+    for (uint32_t b = 0; b < blocks; ++b)
+      for (int t = 0; t < 8; ++t) {
+        const uint32_t ent = decode_step<0>(st, lv);
+        emit_guarded<S, MERGE>(entry_symbol(ent), e_lane + (uint64_t)b * 256 + t, delta, a);
+      }
+    if (count == U && __any_sync(0xFFFFFFFFu, st.x != kStateLow) && lane == 0)
+      raise(a.status, NZ_STATUS_BAD_STATE);
+    return;
+  }
+  const uint32_t full_blocks = (uint32_t)(count / 256);
   const uint8_t *frac_lane = MERGE ? a.frac + e_lane * (S + 1) / 8 : nullptr;
   // in operand order a lane's blocks are 64 elements apart in its row (units never
   // straddle a row group); the exponent-only output is always in stream order
@@ -636,6 +690,17 @@ __device__ __forceinline__ void init_sink(UpdateSinkT<ADV> &sk, int c, const Dec
 }
 template <int ADV>
 __device__ __forceinline__ void finish_sink(UpdateSinkT<ADV> &) {}
+template <class Inner>
+__device__ __forceinline__ void init_sink(NormSink<Inner> &sk, int c, const DecodeArgs &a,
+                                          uint32_t unit, uint64_t out_elem, uint32_t lane) {
+  init_sink(sk.inner, c, a, unit, out_elem, lane);
+  sk.norm = a.norm;
+  sk.lg = a.norm_lg;
+  sk.e0[c] = unit * (32u * a.S) + lane * 8;
+  sk.blk[c] = 0;
+}
+template <class Inner>
+__device__ __forceinline__ void finish_sink(NormSink<Inner> &sk) { finish_sink(sk.inner); }
 
 // Update launches, units that do not take the fast path: the unit has just been decoded
 // into the output tensor the ordinary way; its elements take their step there.
@@ -791,6 +856,8 @@ decode_kernel(const BatchArgs batch) {
   a.in = DOT ? batch.in : 0;
   a.seg = DOT ? batch.seg : 0;
   a.tile_cols = ((MODE == kModeTensor || UPDATE) && MERGE) ? batch.item[ti].tile_cols : 0;
+  a.norm = (MERGE && (MODE == kModeTensor || LIST)) ? batch.item[ti].norm : nullptr;
+  a.norm_lg = batch.item[ti].norm_lg;
   a.grad = UPDATE ? batch.grad : nullptr;
   a.exp_avg = UPDATE ? batch.exp_avg : nullptr;
   a.exp_avg_sq = UPDATE ? batch.exp_avg_sq : nullptr;
@@ -941,6 +1008,9 @@ decode_kernel(const BatchArgs batch) {
         } else if (MODE == kModeTensor && MERGE && a.tile_cols) {
           typename std::conditional<DOT, DotSink, StoreSinkT<64>>::type sink;     // operand order
           run(sink);
+        } else if (MERGE && !UPDATE && a.norm) {
+          typename std::conditional<DOT || UPDATE || !MERGE, StoreSink, NormSink<StoreSink>>::type sink;
+          run(sink);
         } else {
           typename std::conditional<DOT, DotSink, StoreSink>::type sink;
           run(sink);
@@ -991,6 +1061,8 @@ struct HostItem {
   const uint16_t *grad;        // update: gradient and AdamW moments (bf16, else null)
   uint16_t *exp_avg, *exp_avg_sq;
   AdamArgs adam;
+  const uint8_t *norm;         // block normaliser bytes (else null) and log2 of the group size
+  uint32_t norm_lg;
 };
 
 // Units a launch decodes for an item.
@@ -1169,6 +1241,8 @@ int decode_many(const HostItem *items, uint32_t count, int precision, uint32_t S
       b.item[t].n_units = (uint32_t)unit_count(live[t].n, live[t].S);
       b.item[t].tile_cols = live[t].tile_cols;
       b.item[t].S = live[t].S;
+      b.item[t].norm = live[t].norm;
+      b.item[t].norm_lg = live[t].norm_lg;
     }
     const bool gather = live[0].unit_list != nullptr;   // gather calls pass a single item
     b.unit_list = live[0].unit_list;
@@ -1259,6 +1333,8 @@ int decode_common(const void *container, uint64_t container_bytes, const void *f
   it.S = 0;
   it.grad = nullptr;
   it.exp_avg = it.exp_avg_sq = nullptr;
+  it.norm = nullptr;
+  it.norm_lg = 0;
   return decode_many(&it, 1, precision, S, canon, out_bf16 != nullptr, status, st);
 }
 
@@ -1394,6 +1470,18 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
       host[i].S = 0;
       host[i].grad = nullptr;
       host[i].exp_avg = host[i].exp_avg_sq = nullptr;
+      host[i].norm = nullptr;
+      host[i].norm_lg = 0;
+      if (it.normalizers) {
+        const uint32_t g = it.normalizer_group;
+        if (g == 0 || g > 1024 || (g & (g - 1)) || it.operand_cols) {
+          nz::set_error("nz_decompress_bf16_batch: item %u: the normaliser group must be a power "
+                        "of two in [1, 1024] (got %u) and the tensor in stream order", base + i, g);
+          return NZ_E_ARG;
+        }
+        host[i].norm = (const uint8_t *)it.normalizers;
+        while ((1u << host[i].norm_lg) < g) ++host[i].norm_lg;
+      }
       if (it.lane_symbols) {
         if (!nz::valid_lane_symbols(it.lane_symbols)) {
           nz::set_error("nz_decompress_bf16_batch: item %u: lane_symbols must be a multiple of 8 "
@@ -1421,11 +1509,27 @@ extern "C" int nz_decompress_bf16_batch(const nz_decompress_item *items, uint32_
   return NZ_OK;
 }
 
+static int decompress_units(const void *container, uint64_t container_bytes, const void *frac_in,
+                            uint64_t n, int precision, uint32_t lane_symbols,
+                            uint32_t max_unit_words, int canonical_nan, const void *unit_ids,
+                            uint32_t n_ids, const void *normalizers, uint32_t group, void *out_bf16,
+                            void *status, void *stream);
+
 extern "C" int nz_decompress_bf16_units(const void *container, uint64_t container_bytes,
                                         const void *frac_in, uint64_t n, int precision,
                                         uint32_t lane_symbols, uint32_t max_unit_words,
                                         int canonical_nan, const void *unit_ids, uint32_t n_ids,
                                         void *out_bf16, void *status, void *stream) {
+  return decompress_units(container, container_bytes, frac_in, n, precision, lane_symbols,
+                          max_unit_words, canonical_nan, unit_ids, n_ids, nullptr, 0, out_bf16, status,
+                          stream);
+}
+
+static int decompress_units(const void *container, uint64_t container_bytes, const void *frac_in,
+                            uint64_t n, int precision, uint32_t lane_symbols,
+                            uint32_t max_unit_words, int canonical_nan, const void *unit_ids,
+                            uint32_t n_ids, const void *normalizers, uint32_t group, void *out_bf16,
+                            void *status, void *stream) {
   if (!nz::valid_precision(precision)) {
     nz::set_error("nz_decompress_bf16_units: precision must be 0, 1, 3 or 7 (got %d)", precision);
     return NZ_E_ARG;
@@ -1461,6 +1565,16 @@ extern "C" int nz_decompress_bf16_units(const void *container, uint64_t containe
   it.S = 0;
   it.grad = nullptr;
   it.exp_avg = it.exp_avg_sq = nullptr;
+  it.norm = nullptr;
+  it.norm_lg = 0;
+  if (normalizers) {
+    if (group == 0 || group > 1024 || (group & (group - 1))) {
+      nz::set_error("gather: the normaliser group must be a power of two in [1, 1024] (got %u)", group);
+      return NZ_E_ARG;
+    }
+    it.norm = (const uint8_t *)normalizers;
+    while ((1u << it.norm_lg) < group) ++it.norm_lg;
+  }
   return nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                          (cudaStream_t)stream);
 }
@@ -1530,6 +1644,20 @@ extern "C" int nz_gather_rows_bf16(const void *container, uint64_t container_byt
                                    int canonical_nan, uint64_t row_len, const void *rows_i64,
                                    uint32_t n_rows_out, void *out_bf16, void *scratch,
                                    uint64_t scratch_bytes, void *status, void *stream) {
+  return nz_gather_rows_normalized_bf16(container, container_bytes, frac_in, n, precision,
+                                        lane_symbols, max_unit_words, canonical_nan, row_len,
+                                        rows_i64, n_rows_out, nullptr, 0, out_bf16, scratch,
+                                        scratch_bytes, status, stream);
+}
+
+extern "C" int nz_gather_rows_normalized_bf16(const void *container, uint64_t container_bytes,
+                                              const void *frac_in, uint64_t n, int precision,
+                                              uint32_t lane_symbols, uint32_t max_unit_words,
+                                              int canonical_nan, uint64_t row_len,
+                                              const void *rows_i64, uint32_t n_rows_out,
+                                              const void *normalizers, uint32_t normalizer_group,
+                                              void *out_bf16, void *scratch, uint64_t scratch_bytes,
+                                              void *status, void *stream) {
   if (!nz::valid_precision(precision)) {
     nz::set_error("nz_gather_rows_bf16: precision must be 0, 1, 3 or 7 (got %d)", precision);
     return NZ_E_ARG;
@@ -1570,9 +1698,9 @@ extern "C" int nz_gather_rows_bf16(const void *container, uint64_t container_byt
   nz::gather_plan_kernel<<<(unsigned)((n_list + 255) / 256), 256, 0, st>>>(
       (const int64_t *)rows_i64, n_rows_out, row_len, table_rows, U, n_units, per_row, units);
   NZ_LAUNCH_CHECK("gather_plan_kernel");
-  rc = nz_decompress_bf16_units(container, container_bytes, frac_in, n, precision, lane_symbols,
-                                max_unit_words, canonical_nan, units, (uint32_t)n_list, staging,
-                                status, stream);
+  rc = decompress_units(container, container_bytes, frac_in, n, precision, lane_symbols,
+                        max_unit_words, canonical_nan, units, (uint32_t)n_list, normalizers,
+                        normalizer_group, staging, status, stream);
   if (rc) return rc;
   const bool vec = row_len % 8 == 0 && ((uintptr_t)out_bf16 & 15) == 0;
   const uint64_t threads = vec ? (uint64_t)n_rows_out * (row_len / 8) : (uint64_t)n_rows_out * row_len;
@@ -1658,6 +1786,8 @@ extern "C" int nz_linear_vec_bf16(const void *container, uint64_t container_byte
   it.S = 0;
   it.grad = nullptr;
   it.exp_avg = it.exp_avg_sq = nullptr;
+  it.norm = nullptr;
+  it.norm_lg = 0;
   rc = nz::decode_many(&it, 1, precision, lane_symbols, canonical_nan, true, status,
                        (cudaStream_t)stream);
   if (rc) return rc;

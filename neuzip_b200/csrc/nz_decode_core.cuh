@@ -290,6 +290,9 @@ struct DecodeArgs {
   uint32_t in;                 //   row length of the [out, in] matrix, a multiple of 256
   uint32_t seg;                //   rows a unit can touch
   uint32_t tile_cols;          // operand order: row length of the matrix (0 = the stream is the tensor)
+  // block normaliser: one stored byte per group of 2^norm_lg elements (null = none)
+  const uint8_t *norm;
+  uint32_t norm_lg;
   // update launches: gradient (bf16) and AdamW moments (bf16), indexed like the output tensor
   const uint16_t *grad;
   uint16_t *exp_avg, *exp_avg_sq;
@@ -312,6 +315,19 @@ __device__ __forceinline__ uint64_t operand_index(uint64_t e, uint32_t cols) {
   const uint64_t g = block / spr;
   const uint32_t kb = (uint32_t)(block - g * spr);
   return (4 * g + (w >> 6)) * cols + kb * 64u + (w & 63u);
+}
+// Block normaliser on the way out (cuda/kernels.cuh:208-216 of the reference): a decoded
+// bf16 value times the scale 1.<8 stored mantissa bits> of its group, rounded to bf16
+// (nearest even) -- the arithmetic of nz_denormalize_bf16.
+__device__ __forceinline__ float norm_scale(uint32_t stored_byte) {
+  return __uint_as_float(0x3F800000u | (stored_byte << 15));
+}
+__device__ __forceinline__ uint32_t scale_bf16_bits(uint32_t bits16, float scale) {
+  const float f = scale * __uint_as_float(bits16 << 16);
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7F800000u) == 0x7F800000u && (u & 0x007FFFFFu)) return 0x7FFFu;    // NaN
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return u >> 16;
 }
 // Where stream element e goes in the output tensor.
 __device__ __forceinline__ uint64_t out_index(const DecodeArgs &a, uint64_t e) {
