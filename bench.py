@@ -46,12 +46,13 @@ LAYER_SHAPES = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
 METRIC = "lossless bf16 decompress throughput (decoded bytes out + compressed bytes in)"
 UNIT = "GB/s"
 
-# DRAM traffic of one decode launch on the largest matrix (4096x11008, precision 7),
+# DRAM traffic of one decode launch over a layer set (7 matrices, precision 7),
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture summarised in
-# profiles/kernels_precision7_4096x11008.md; scaled to the average launch by elements.
-NCU_TRAFFIC_BYTES_45M = 60.49e6 + 31.9e6   # read + written by kernel end; the rest of the
-# 90 MB output is still in L2 then and is written back while the next launch runs
-NCU_TRAFFIC_ELEMENTS = 4096 * 11008
+# profiles/decode_kernel_precision7_layer_set.md; scaled to the average launch by elements.
+NCU_TRAFFIC_BYTES = 271.26e6 + 347.1e6   # read (= the compressed bytes, no re-reads) + written
+# by kernel end; the rest of the 404.8 MB output is still in L2 then and is written back
+# while the next launch runs
+NCU_TRAFFIC_ELEMENTS = 4 * 4096 * 4096 + 3 * 4096 * 11008
 
 
 def parse_args():
@@ -829,7 +830,7 @@ def run_ours(args):
         n_items = len(layer_ids) * len(LAYER_SHAPES)
         elements = sum(a * b for a, b in LAYER_SHAPES) * len(layer_ids)
         avg_launch_bytes = bytes_pass / launches_per_pass
-        traffic = NCU_TRAFFIC_BYTES_45M * (elements / launches_per_pass) / NCU_TRAFFIC_ELEMENTS
+        traffic = NCU_TRAFFIC_BYTES * (elements / launches_per_pass) / NCU_TRAFFIC_ELEMENTS
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": scaling,
