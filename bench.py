@@ -154,6 +154,9 @@ def bind_to_gpu_numa(local_rank):
     """Restrict this process to the CPUs NVML names as local to its GPU, so that the
     pinned buffers allocated afterwards (first touch) and the copy threads sit on the
     GPU's NUMA node.  Reads settings only.  Returns a description for the report."""
+    if os.environ.get("NZ_BENCH_NO_BIND"):
+        return {"gpu": None, "cpus": None, "n_cpus": len(os.sched_getaffinity(0)),
+                "note": "not bound (NZ_BENCH_NO_BIND)"}
     try:
         import pynvml
         pynvml.nvmlInit()
