@@ -631,6 +631,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # the launcher of multi-rank runs sets OMP_NUM_THREADS=1 for every rank; this arm is the
+    # only work on the host, so it takes all the cores it is allowed (before OpenMP starts)
+    os.environ["OMP_NUM_THREADS"] = str(max(1, omp_threads()))
     import torch
     torch.set_num_threads(max(1, omp_threads()))
     from oracle import oracle as O
@@ -816,6 +819,7 @@ def run_ours(args):
             extras["linear_fused"] = linear_leg(L, torch, index)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
+        os.environ.setdefault("OMP_NUM_THREADS", str(max(1, omp_threads())))
         from oracle import oracle as O
         O.build()
         mats = cpu_sample(torch, n_layers=1)[3:7:3]      # one 4096x4096 and the 4096x11008
