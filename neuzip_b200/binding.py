@@ -116,6 +116,13 @@ class Manager:
             tp = (tp_rank, tp_world, tp_plan, tp_group)
         return _convert(self, module, tp=tp)
 
+    def load_converted(self, module: torch.nn.Module, state_dict, device=None) -> torch.nn.Module:
+        """Load the state_dict of a converted model into an unconverted `module` (which may
+        be on the meta device): compressed Linears are built from the stored bytes, nothing
+        is compressed and no dense weight is materialised.  Not in the reference."""
+        from .utils import load_converted
+        return load_converted(self, module, state_dict, device=device)
+
     def split(self, tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         exp, frac = self._be.split(tensor)
         return exp.reshape(tensor.shape), frac.reshape(tensor.shape)

@@ -32,6 +32,24 @@ class Linear(torch.nn.Module):
     def weight(self) -> Parameter:
         return self._p
 
+    @classmethod
+    def from_compressed(cls, manager, state, bias=None, device=None):
+        """A compressed Linear straight from stored bytes (`state` = what get_extra_state
+        returned): no dense weight is ever built, so a checkpoint of a converted model loads
+        into a model that was never materialised."""
+        self = cls.__new__(cls)
+        torch.nn.Module.__init__(self)
+        self.manager = manager
+        self.reduce_group = None
+        self.reduce_output = bool(state.get("reduce_output", False))
+        self._p = Parameter.from_entry(manager, state, device=device)
+        self.out_features, self.in_features = int(self._p._shape[0]), int(self._p._shape[1])
+        if bias is None:
+            self.register_parameter("bias", None)
+        else:
+            self.bias = torch.nn.Parameter(bias.to(self._p.device))
+        return self
+
     def forward(self, x):
         y = self._forward_local(x)
         if self.reduce_output:
@@ -61,7 +79,9 @@ class Linear(torch.nn.Module):
     # compressed bytes travel as the module's extra state: a checkpoint of a converted
     # model holds containers + fractions and loads without a bf16 staging copy.
     def get_extra_state(self):
-        return self._p._manager.export_entry(self._p._handle)
+        state = self._p._manager.export_entry(self._p._handle)
+        state["reduce_output"] = self.reduce_output      # a row-parallel shard (tensor parallelism)
+        return state
 
     def set_extra_state(self, state):
         if state is None:

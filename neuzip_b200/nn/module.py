@@ -20,6 +20,23 @@ class Parameter(torch.nn.Parameter):
         self._stage_tag = None     # (stage, block number): the view is valid while they agree
         return self
 
+    @classmethod
+    def from_entry(cls, manager, blob, device=None):
+        """A parameter for bytes that are already compressed (an entry made by
+        ``Manager.export_entry``, e.g. out of a checkpoint): registered under a new handle,
+        nothing is decompressed or compressed.  Not in the reference, which cannot load a
+        converted model at all (its state_dict holds only the empty placeholder)."""
+        device = device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+        placeholder = torch.zeros(0, dtype=torch.bfloat16, device=device)
+        self = torch.nn.Parameter.__new__(cls, placeholder, True)
+        self._manager = manager
+        self._shape = torch.Size(blob["shape"])
+        self._gradient = None
+        self._handle = manager.import_entry(blob)
+        self._staged = None
+        self._stage_tag = None
+        return self
+
     def staged(self):
         """The already decoded weight, if a layer-wise prefetch holds it right now."""
         tag = self._stage_tag

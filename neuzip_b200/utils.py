@@ -74,3 +74,37 @@ def _convert(manager, module, prefix="", tp=None):
         else:
             _convert(manager, child, full_name, tp)
     return module
+
+
+def load_converted(manager, module, state_dict, prefix="", device=None):
+    """Load a checkpoint of a *converted* model (compressed bytes as module extra state)
+    into `module`, which may live on the meta device and must not have been converted:
+    every ``nn.Linear`` whose ``<name>._extra_state`` is in the checkpoint becomes a
+    compressed Linear built from those bytes (nothing is compressed, no dense copy of
+    the weight exists at any time); all other tensors of the checkpoint are assigned.
+    The reference cannot do this: a converted model's state_dict loses the weights
+    (neuzip/nn/module.py:13)."""
+    consumed = set()
+
+    def walk(mod, pre):
+        for name, child in list(mod.named_children()):
+            full = f"{pre}{name}"
+            key = f"{full}._extra_state"
+            if isinstance(child, torch.nn.Linear) and key in state_dict:
+                bias = state_dict.get(f"{full}.bias")
+                setattr(mod, name, Linear.from_compressed(manager, state_dict[key], bias, device))
+                consumed.update({key, f"{full}.bias", f"{full}._p"})
+            else:
+                walk(child, f"{full}.")
+
+    walk(module, prefix)
+    rest = {k[len(prefix):]: v for k, v in state_dict.items()
+            if k.startswith(prefix) and k not in consumed}
+    if device is not None:
+        rest = {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in rest.items()}
+    missing, unexpected = module.load_state_dict(rest, strict=False, assign=True)
+    missing = [k for k in missing if not k.endswith(("._p", "._extra_state", ".bias"))
+               or k in rest]
+    if missing or unexpected:
+        raise RuntimeError(f"load_converted: missing keys {missing}, unexpected keys {unexpected}")
+    return module

@@ -614,3 +614,28 @@ def test_fused_update_equals_read_adamw_write_bit_for_bit(precision, shape, oper
     assert not torch.equal(ma.read(ha), w)            # the weights did move
     ma.check()
     mb.check()
+
+
+def test_converted_checkpoint_loads_into_a_meta_model_on_gpu(tmp_path):
+    def make():
+        return torch.nn.Sequential(torch.nn.Linear(2048, 256, bias=True), torch.nn.ReLU(),
+                                   torch.nn.Linear(256, 64, bias=False)).to(torch.bfloat16)
+    torch.manual_seed(8)
+    src = make()
+    m1 = neuzip.Manager(precision=7)
+    m1.convert(src)
+    src.cuda()
+    x = torch.randn(4, 2048, device="cuda", dtype=torch.bfloat16)
+    expect = src(x)
+    assert m1._be.entry(src[0]._p._handle).operand_cols == 2048     # stored in operand order
+    torch.save(src.state_dict(), tmp_path / "c.pt")
+    with torch.device("meta"):
+        skeleton = make()
+    m2 = neuzip.Manager(precision=7)
+    m2.load_converted(skeleton, torch.load(tmp_path / "c.pt", weights_only=False), device="cuda")
+    assert m2._be.entry(skeleton[0]._p._handle).operand_cols == 2048
+    assert torch.equal(skeleton(x), expect)
+    m2.fuse_linear(64)
+    fused = skeleton(x)
+    assert (fused.float() - expect.float()).abs().max().item() <= 2.0 ** -6 * expect.float().abs().max().item()
+    m2.check()

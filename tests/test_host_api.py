@@ -309,3 +309,34 @@ def test_layerwise_hooks_follow_writes_and_loaded_state_on_cpu():
         assert torch.equal(model(x), first)
     for h in hooks:
         h.remove()
+
+
+def test_checkpoint_of_a_converted_model_loads_into_a_meta_model_without_compressing(tmp_path):
+    """A converted model's checkpoint loads into a model that was never materialised:
+    the skeleton lives on the meta device, compressed Linears are built from the stored
+    bytes, and the backend is never asked to compress anything."""
+    torch.manual_seed(5)
+    src = Tiny().to(torch.bfloat16)
+    ids = torch.randint(0, 20, (2, 5))
+    m1 = cpu_manager()
+    m1.convert(src)
+    expect = src(ids)
+    path = tmp_path / "converted.pt"
+    torch.save(src.state_dict(), path)
+
+    with torch.device("meta"):
+        skeleton = Tiny().to(torch.bfloat16)
+    m2 = cpu_manager()
+    writes = []
+    real_write = m2._be.write
+    m2._be.write = lambda *a, **k: (writes.append(a[0]), real_write(*a, **k))[1]
+    m2.load_converted(skeleton, torch.load(path, weights_only=False), device="cpu")
+    assert not writes                                   # nothing was compressed
+    assert all(not p.is_meta for p in skeleton.parameters())
+    assert isinstance(skeleton.block[0], neuzip.nn.Linear)
+    assert torch.equal(skeleton(ids), expect)
+    # and it saves again to the same bytes
+    again = skeleton.state_dict()
+    first = src.state_dict()
+    assert torch.equal(again["block.0._extra_state"]["container"],
+                       first["block.0._extra_state"]["container"])
