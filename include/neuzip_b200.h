@@ -393,6 +393,51 @@ int nz_linear_bf16(const void *container, uint64_t container_bytes, const void *
                    uint64_t m_tokens, const void *bias_bf16, void *y_bf16, void *workspace,
                    uint64_t workspace_bytes, void *status, void *stream);
 
+/* ---- the fused linear with a tensor-parallel all-reduce in its epilogue ------ */
+
+/* Row-parallel Linears of a tensor-parallel model (each rank holds a block of
+ * input columns) produce partial sums that have to be added over the ranks.
+ * nz_linear_allreduce_bf16 is nz_linear_bf16 with that all-reduce fused in: the
+ * kernel's epilogue writes its fp32 partial tiles straight from tensor memory
+ * into EVERY rank's workspace with plain peer stores over NVLink (slot [source
+ * rank][segment][row of x][row of W]), fences at system scope and adds one
+ * arrival per CTA to every rank's arrival counters; a second kernel on each rank
+ * waits (bounded: about a second, then NZ_STATUS_TIMEOUT) until every rank's CTAs
+ * of the call have arrived and adds the partial sums rank by rank, segment by
+ * segment, so every rank obtains the same bits.  No multicast, no library
+ * collective.  All ranks must make the same sequence of calls (same shapes);
+ * arrival counters only grow: pass the value *arrivals_after of the previous
+ * call on the same buffers as arrivals_before (0 at first).  A buffer set may be
+ * reused by the call after next at the earliest, so alternate two sets.  The
+ * bias, if any, is given on ONE rank only (it joins that rank's partial sums).
+ * Reference: none - the reference has no tensor parallelism (survey section 2,
+ * row 18); the baseline is nz_linear_bf16 followed by an NCCL all-reduce. */
+typedef struct nz_peer_group {
+  uint32_t world, rank;       /* 2..8 ranks, this rank's number                */
+  void *workspace[8];         /* every rank's workspace as seen from this GPU  */
+  void *arrivals[8];          /* every rank's u32[8] arrival counters          */
+  uint64_t workspace_bytes;   /* size of each workspace                        */
+} nz_peer_group;
+
+uint64_t nz_linear_allreduce_workspace_bytes(uint64_t rows, uint64_t cols, uint32_t lane_symbols,
+                                             uint64_t m_tokens, uint32_t world);
+int nz_linear_allreduce_bf16(const void *container, uint64_t container_bytes, const void *frac_in,
+                             uint64_t rows, uint64_t cols, int precision, uint32_t lane_symbols,
+                             uint32_t max_unit_words, int canonical_nan, const void *x_bf16,
+                             uint64_t m_tokens, const void *bias_bf16, void *y_bf16,
+                             const nz_peer_group *peers, uint32_t arrivals_before,
+                             uint32_t *arrivals_after, void *status, void *stream);
+
+/* Peer-visible device memory for the call above (these four allocate or map
+ * memory and synchronise; call them at set-up).  nz_peer_alloc: cudaMalloc,
+ * zero, and export a 64-byte inter-process handle; nz_peer_open: map a peer's
+ * handle into this process (peer access is enabled on demand).
+ * Reference: none. */
+int nz_peer_alloc(uint64_t bytes, void **ptr, void *handle64);
+int nz_peer_open(const void *handle64, void **ptr);
+int nz_peer_close(void *ptr);
+int nz_peer_free(void *ptr);
+
 #ifdef __cplusplus
 }
 #endif

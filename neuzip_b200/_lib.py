@@ -96,6 +96,23 @@ SIGNATURES["nz_adamw_compressed_bf16"] = (
     _int, [_vp, _u64, _vp, _u64, _u64, _int, _u32, _u32, _int, _vp, _vp, _vp, _f32, _f32, _f32, _f32,
            _f32, _u32, _f32, _vp, _vp, _u64, _vp, _u64, _vp, _vp])
 
+
+
+class PeerGroup(ctypes.Structure):
+    """struct nz_peer_group"""
+    _fields_ = [("world", _u32), ("rank", _u32), ("workspace", _vp * 8), ("arrivals", _vp * 8),
+                ("workspace_bytes", _u64)]
+
+
+SIGNATURES["nz_linear_allreduce_workspace_bytes"] = (_u64, [_u64, _u64, _u32, _u64, _u32])
+SIGNATURES["nz_linear_allreduce_bf16"] = (
+    _int, [_vp, _u64, _vp, _u64, _u64, _int, _u32, _u32, _int, _vp, _u64, _vp, _vp,
+           ctypes.POINTER(PeerGroup), _u32, ctypes.POINTER(_u32), _vp, _vp])
+SIGNATURES["nz_peer_alloc"] = (_int, [_u64, ctypes.POINTER(_vp), _vp])
+SIGNATURES["nz_peer_open"] = (_int, [_vp, ctypes.POINTER(_vp)])
+SIGNATURES["nz_peer_close"] = (_int, [_vp])
+SIGNATURES["nz_peer_free"] = (_int, [_vp])
+
 _lock = threading.Lock()
 _lib = None
 

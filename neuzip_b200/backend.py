@@ -16,6 +16,8 @@ import enum
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -500,8 +502,18 @@ class CodecBackend:
         weight = self.read(name).view(*shape)
         return torch.matmul(input, weight.t())
 
+    def linear_allreduce(self, name: str, input: torch.Tensor, shape: Sequence[int],
+                         bias: Optional[torch.Tensor], reducer) -> Optional[torch.Tensor]:
+        """`all_reduce(input @ W^T) (+ bias on the rank that has it)` for a row-parallel shard,
+        the sum over the ranks done by the fused linear kernel's epilogue over peer memory
+        (``nz_linear_allreduce_bf16``) instead of a collective after it.  Every rank must
+        make the same calls; returns None (on every rank alike: the test only looks at
+        shapes, types and the storage order) when the call does not qualify, and the caller
+        falls back to `linear` + all-reduce."""
+        return self._linear_fused(name, input, shape, bias, reducer)
+
     def _linear_fused(self, name: str, input: torch.Tensor, shape: Sequence[int],
-                      bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+                      bias: Optional[torch.Tensor], reducer=None) -> Optional[torch.Tensor]:
         """`input @ W^T (+ bias)` with the weight decoded straight into tensor-core operand
         tiles (``nz_linear_bf16``): no bf16 copy of the weight is written or read back.
         Returns None when the call does not qualify (weight not in operand order, input not
@@ -533,6 +545,26 @@ class CodecBackend:
                 return None
         L = self._lib
         y = torch.empty(input.shape[:-1] + (out_f,), dtype=torch.bfloat16, device="cuda")
+        if reducer is not None:
+            need = int(L.nz_linear_allreduce_workspace_bytes(out_f, in_f, entry.lane_symbols, m,
+                                                             reducer.world))
+            if not need or not reducer.fits(need):
+                return None
+            turn, group, before = reducer.next_set()
+            after = ctypes.c_uint32(0)
+            _next_op()
+            rc = L.nz_linear_allreduce_bf16(
+                _ptr(entry.container), entry.container.numel(), _ptr(entry.fractions), out_f, in_f,
+                self.precision, entry.lane_symbols, entry.max_unit_words, int(self.canonical_nan),
+                _ptr(x), m, _ptr(bias.contiguous() if bias is not None else None), _ptr(y),
+                ctypes.byref(group), before, ctypes.byref(after), _ptr(self._status), _stream())
+            if rc == _lib.NZ_E_CAPACITY:
+                # the peers cannot know: a silent fallback here would leave them waiting
+                raise RuntimeError("this rank's shard has units too long for the fused linear; "
+                                   "switch the fused all-reduce off (fuse_tp_allreduce(None))")
+            _lib.check(rc)
+            reducer.advance(turn, after.value)
+            return y
         need = int(L.nz_linear_workspace_bytes(out_f, in_f, entry.lane_symbols, m))
         if self._lin_ws is None or self._lin_ws.numel() < need:
             self._lin_ws = torch.empty(need, dtype=torch.uint8, device="cuda")

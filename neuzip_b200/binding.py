@@ -167,6 +167,34 @@ class Manager:
         if hasattr(self._be, "fused_linear_max_rows"):
             self._be.fused_linear_max_rows = int(max_rows)
 
+    def fuse_tp_allreduce(self, group=None, max_rows: int = 256,
+                          workspace_bytes: int = 64 << 20) -> None:
+        """Tensor parallelism on one node: let row-parallel Linears with at most `max_rows`
+        input rows add their partial outputs inside the fused linear kernel, which stores them
+        into every rank's memory over NVLink, instead of an all-reduce after it.  Collective:
+        every rank of `group` calls it (it exchanges memory handles over the group);
+        `group=None` with `max_rows=0` switches it off again."""
+        old = getattr(self, "_reducer", None)
+        if old is not None:
+            old.close()
+        self._reducer, self._reducer_rows = None, 0
+        if max_rows and hasattr(self._be, "linear_allreduce"):
+            from .tpcomm import PeerReducer
+            self._reducer = PeerReducer(group, workspace_bytes)
+            self._reducer_rows = int(max_rows)
+
+    def linear_allreduce(self, handle: str, inputs: torch.Tensor, bias=None):
+        """The summed output of a row-parallel shard, or None when the fused path is off or
+        the call does not qualify (then: `linear` and an all-reduce)."""
+        reducer = getattr(self, "_reducer", None)
+        if reducer is None:
+            return None
+        limit, self._be.fused_linear_max_rows = self._be.fused_linear_max_rows, self._reducer_rows
+        try:
+            return self._be.linear_allreduce(handle, inputs, self.meta_dict[handle], bias, reducer)
+        finally:
+            self._be.fused_linear_max_rows = limit
+
     def export_entry(self, handle: str) -> dict:
         """Stored bytes + metadata of a handle (for checkpoints)."""
         blob = self._be.export_entry(handle)

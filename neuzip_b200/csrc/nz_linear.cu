@@ -48,6 +48,7 @@ constexpr uint32_t kTileRows = 128;
 constexpr uint32_t kTileBytes = kTileRows * 128;    // 128 rows x 64 bf16
 constexpr uint32_t kMaxTokensPerLaunch = 256;       // MMA N and tensor-memory columns
 constexpr uint32_t kLinMaxStages = 4;
+constexpr uint32_t kMaxPeers = 8;                   // ranks of a tensor-parallel group
 
 struct LinearArgs {
   const uint8_t *container;
@@ -70,6 +71,12 @@ struct LinearArgs {
   uint16_t *y;                // bf16[m_total, rows]
   float *partial;             // fp32[segs, m_total, rows] when segs > 1
   uint32_t *status;
+  // tensor-parallel all-reduce fused into the epilogue (tp_world > 1): every rank's partial
+  // sums go, by plain peer stores, into every rank's workspace [src rank][segment][token][row];
+  // a CTA then adds 1 (system scope) to counter `tp_rank` of every rank's arrival counters
+  uint32_t tp_world, tp_rank;
+  float *peer_partial[kMaxPeers];
+  uint32_t *peer_arrivals[kMaxPeers];
 };
 
 // ------------------------------------------------------------------ PTX
@@ -460,7 +467,10 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
       tc_fence_after();
       const uint32_t sub = warp & 3;                       // tensor-memory lanes 32 sub .. +31
       const uint32_t r = tile_id * kTileRows + 32 * sub + lane;
-      const float bias = (p.bias && r < p.rows && p.segs == 1)
+      // the bias rides on the direct store, or (tensor parallel: on the one rank that was
+      // given it) on the partial sums of segment 0
+      const bool bias_here = p.tp_world > 1 ? seg == 0 : p.segs == 1;
+      const float bias = (p.bias && r < p.rows && bias_here)
                              ? __uint_as_float((uint32_t)p.bias[r] << 16) : 0.f;
       for (uint32_t c0 = (warp >> 2) * 16; c0 < p.n_pad; c0 += 64) {
         uint32_t v[16];
@@ -472,10 +482,15 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
             const uint32_t t = c0 + i;
             if (t >= p.n_tok) break;
             const uint64_t tok = p.tok0 + t;
-            if (p.segs == 1)
+            if (p.tp_world > 1) {
+              const uint64_t at = (((uint64_t)p.tp_rank * p.segs + seg) * p.m_total + tok) * p.rows + r;
+              const float part = __uint_as_float(v[i]) + bias;
+              for (uint32_t q = 0; q < p.tp_world; ++q) p.peer_partial[q][at] = part;
+            } else if (p.segs == 1) {
               p.y[tok * p.rows + r] = f32_to_bf16_rn(__uint_as_float(v[i]) + bias);
-            else
+            } else {
               p.partial[((uint64_t)seg * p.m_total + tok) * p.rows + r] = __uint_as_float(v[i]);
+            }
           }
         }
       }
@@ -536,7 +551,15 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
   // ---- common exit: everybody is done with tensor memory, then it is freed
   __syncwarp();
   tc_fence_before();
+  if (p.tp_world > 1) __threadfence_system();       // this thread's peer stores, before the signal
   __syncthreads();
+  if (p.tp_world > 1 && threadIdx.x == 0) {
+    // one arrival per CTA and rank, also when the CTA gave up: the peers' waits are bounded
+    // either way, and their status words tell them when the sums cannot be trusted.  The
+    // fence is cumulative over the CTA's stores that the barrier made visible to this thread.
+    __threadfence_system();
+    for (uint32_t q = 0; q < p.tp_world; ++q) atomicAdd_system(p.peer_arrivals[q] + p.tp_rank, 1u);
+  }
   if (is_mma) {
     __syncwarp();
     tc_fence_after();
@@ -558,6 +581,44 @@ __global__ void linear_finish_kernel(const float *__restrict__ partial, uint32_t
   for (uint32_t s = 0; s < segs; ++s) sum += partial[(uint64_t)s * plane + i];
   if (bias) sum += __uint_as_float((uint32_t)bias[i % rows] << 16);
   y[i] = f32_to_bf16_rn(sum);
+}
+
+// The same for a tensor-parallel group: the partial sums of every rank and segment lie in
+// this rank's workspace; wait (bounded) until every rank's CTAs of this call have arrived,
+// then add rank by rank, segment by segment -- the same order on every rank, so all ranks
+// get the same bits.  `expected` = arrivals per rank up to and including this call.
+__global__ void linear_allreduce_finish_kernel(const float *__restrict__ partial,
+                                               const uint32_t *arrivals, uint32_t expected,
+                                               uint32_t world, uint32_t segs, uint64_t plane,
+                                               uint32_t rows, const uint16_t *__restrict__ bias,
+                                               uint16_t *__restrict__ y, uint32_t *status) {
+  __shared__ uint32_t ok_sh;
+  if (threadIdx.x == 0) {
+    uint32_t ok = 1;
+    for (uint32_t q = 0; q < world && ok; ++q) {
+      uint32_t it = 0;
+      for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrivals + q) : "memory");
+        if ((int32_t)(seen - expected) >= 0) break;
+        if (++it > (1u << 21)) {            // about a second
+          ok = 0;
+          break;
+        }
+        __nanosleep(400);
+      }
+    }
+    if (!ok && status) atomicOr(status, NZ_STATUS_TIMEOUT);
+    ok_sh = ok;
+  }
+  __syncthreads();
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= plane) return;
+  float sum = 0.f;
+  for (uint32_t k = 0; k < world * segs; ++k) sum += __ldcv(partial + (uint64_t)k * plane + i);
+  if (bias) sum += __uint_as_float((uint32_t)bias[i % rows] << 16);
+  y[i] = f32_to_bf16_rn(sum);
+  (void)ok_sh;
 }
 
 // --------------------------------------------------------------------- host
@@ -659,13 +720,28 @@ extern "C" uint64_t nz_linear_workspace_bytes(uint64_t rows, uint64_t cols, uint
   return nz::align16((uint64_t)segs * m_tokens * rows * 4);
 }
 
-extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, const void *frac_in,
-                              uint64_t rows, uint64_t cols, int precision, uint32_t lane_symbols,
-                              uint32_t max_unit_words, int canonical_nan, const void *x_bf16,
-                              uint64_t m_tokens, const void *bias_bf16, void *y_bf16,
-                              void *workspace, uint64_t workspace_bytes, void *status,
-                              void *stream) {
+static int linear_impl(const void *container, uint64_t container_bytes, const void *frac_in,
+                       uint64_t rows, uint64_t cols, int precision, uint32_t lane_symbols,
+                       uint32_t max_unit_words, int canonical_nan, const void *x_bf16,
+                       uint64_t m_tokens, const void *bias_bf16, void *y_bf16, void *workspace,
+                       uint64_t workspace_bytes, void *status, void *stream,
+                       const nz_peer_group *peers, uint32_t arrivals_before, uint32_t *arrivals_after) {
   using namespace nz;
+  const uint32_t world = peers ? peers->world : 1;
+  if (peers) {
+    if (world < 2 || world > kMaxPeers || peers->rank >= world) {
+      set_error("nz_linear_allreduce_bf16: a peer group has 2 to %u ranks (got %u, rank %u)",
+                kMaxPeers, world, peers->rank);
+      return NZ_E_ARG;
+    }
+    for (uint32_t q = 0; q < world; ++q)
+      if (!peers->workspace[q] || ((uintptr_t)peers->workspace[q] & 15) || !peers->arrivals[q]) {
+        set_error("nz_linear_allreduce_bf16: null or misaligned peer pointer for rank %u", q);
+        return NZ_E_ARG;
+      }
+    workspace = peers->workspace[peers->rank];
+    workspace_bytes = peers->workspace_bytes;
+  }
   if (!valid_precision(precision)) {
     set_error("nz_linear_bf16: precision must be 0, 1, 3 or 7 (got %d)", precision);
     return NZ_E_ARG;
@@ -696,8 +772,9 @@ extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, c
               (unsigned long long)container_bytes, (unsigned long long)nu);
     return NZ_E_FORMAT;
   }
-  if (segs > 1) {
-    const uint64_t need = nz_linear_workspace_bytes(rows, cols, lane_symbols, m_tokens);
+  if (segs > 1 || peers) {
+    const uint64_t need = peers ? align16((uint64_t)world * segs * m_tokens * rows * 4)
+                                : nz_linear_workspace_bytes(rows, cols, lane_symbols, m_tokens);
     if (!workspace || ((uintptr_t)workspace & 15) || workspace_bytes < need) {
       set_error("nz_linear_bf16: workspace of %llu bytes is smaller than the %llu required "
                 "(or misaligned)", (unsigned long long)workspace_bytes, (unsigned long long)need);
@@ -755,6 +832,14 @@ extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, c
   p.y = (uint16_t *)y_bf16;
   p.partial = (float *)workspace;
   p.status = (uint32_t *)status;
+  if (peers) {
+    p.tp_world = world;
+    p.tp_rank = peers->rank;
+    for (uint32_t q = 0; q < world; ++q) {
+      p.peer_partial[q] = (float *)peers->workspace[q];
+      p.peer_arrivals[q] = (uint32_t *)peers->arrivals[q];
+    }
+  }
 
   void (*kern)(const LinearArgs, const CUtensorMap) = nullptr;
   switch (precision) {
@@ -778,7 +863,9 @@ extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, c
   }
   cudaStream_t st = (cudaStream_t)stream;
   const uint32_t tiles = (uint32_t)((rows + kTileRows - 1) / kTileRows);
+  uint32_t launches = 0;
   for (uint64_t tok0 = 0; tok0 < m_tokens; tok0 += per_launch) {
+    ++launches;
     p.tok0 = (uint32_t)tok0;
     p.n_tok = (uint32_t)(m_tokens - tok0 < per_launch ? m_tokens - tok0 : per_launch);
     cudaLaunchConfig_t cfg = {};
@@ -787,6 +874,22 @@ extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, c
     cfg.dynamicSmemBytes = g.smem_bytes;
     cfg.stream = st;
     NZ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, x_map));
+  }
+  if (peers) {
+    // every CTA of every rank's launches adds one arrival per rank
+    const uint32_t expected = arrivals_before + launches * tiles * segs;
+    if (arrivals_after) *arrivals_after = expected;
+    const uint64_t plane = m_tokens * rows;
+    const uint64_t blocks = (plane + 255) / 256;
+    if (blocks >= (1ull << 31)) {
+      set_error("nz_linear_allreduce_bf16: output too large for one call");
+      return NZ_E_ARG;
+    }
+    linear_allreduce_finish_kernel<<<(unsigned)blocks, 256, 0, st>>>(
+        (const float *)workspace, (const uint32_t *)peers->arrivals[peers->rank], expected, world,
+        segs, plane, (uint32_t)rows, nullptr, (uint16_t *)y_bf16, (uint32_t *)status);
+    NZ_LAUNCH_CHECK("linear_allreduce_finish_kernel");
+    return NZ_OK;
   }
   if (segs > 1) {
     const uint64_t plane = m_tokens * rows;
@@ -811,4 +914,40 @@ extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, c
                                    (uint16_t *)y_bf16));
   }
   return NZ_OK;
+}
+
+extern "C" int nz_linear_bf16(const void *container, uint64_t container_bytes, const void *frac_in,
+                              uint64_t rows, uint64_t cols, int precision, uint32_t lane_symbols,
+                              uint32_t max_unit_words, int canonical_nan, const void *x_bf16,
+                              uint64_t m_tokens, const void *bias_bf16, void *y_bf16,
+                              void *workspace, uint64_t workspace_bytes, void *status,
+                              void *stream) {
+  return linear_impl(container, container_bytes, frac_in, rows, cols, precision, lane_symbols,
+                     max_unit_words, canonical_nan, x_bf16, m_tokens, bias_bf16, y_bf16, workspace,
+                     workspace_bytes, status, stream, nullptr, 0, nullptr);
+}
+
+extern "C" uint64_t nz_linear_allreduce_workspace_bytes(uint64_t rows, uint64_t cols,
+                                                        uint32_t lane_symbols, uint64_t m_tokens,
+                                                        uint32_t world) {
+  const uint32_t segs = nz::operand_segments(cols, lane_symbols);
+  if (segs == 0 || world < 2) return 0;
+  return nz::align16((uint64_t)world * segs * m_tokens * rows * 4);
+}
+
+extern "C" int nz_linear_allreduce_bf16(const void *container, uint64_t container_bytes,
+                                        const void *frac_in, uint64_t rows, uint64_t cols,
+                                        int precision, uint32_t lane_symbols,
+                                        uint32_t max_unit_words, int canonical_nan,
+                                        const void *x_bf16, uint64_t m_tokens,
+                                        const void *bias_bf16, void *y_bf16,
+                                        const nz_peer_group *peers, uint32_t arrivals_before,
+                                        uint32_t *arrivals_after, void *status, void *stream) {
+  if (!peers) {
+    nz::set_error("nz_linear_allreduce_bf16: null peer group");
+    return NZ_E_ARG;
+  }
+  return linear_impl(container, container_bytes, frac_in, rows, cols, precision, lane_symbols,
+                     max_unit_words, canonical_nan, x_bf16, m_tokens, bias_bf16, y_bf16, nullptr, 0,
+                     status, stream, peers, arrivals_before, arrivals_after);
 }

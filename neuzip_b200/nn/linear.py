@@ -51,6 +51,11 @@ class Linear(torch.nn.Module):
         return self
 
     def forward(self, x):
+        if self.reduce_output and not torch.is_grad_enabled():
+            # one kernel multiplies and adds over the ranks (peer stores), when switched on
+            y = self._p.linear_allreduce(x, self.bias)
+            if y is not None:
+                return y
         y = self._forward_local(x)
         if self.reduce_output:
             # partial sums of a row-parallel Linear: one all-reduce over the ranks

@@ -52,6 +52,13 @@ class Parameter(torch.nn.Parameter):
         w = self._manager.read(self._handle).reshape(self._shape)
         return w.to(self.device).requires_grad_(False)
 
+    def linear_allreduce(self, inputs, bias=None):
+        """Row-parallel shard: the output summed over the ranks by the fused kernel, or None."""
+        fn = getattr(self._manager, "linear_allreduce", None)
+        if fn is None or self.staged() is not None:
+            return None
+        return fn(self._handle, inputs, bias)
+
     def linear(self, inputs, bias=None):
         staged = self.staged()
         if staged is not None:
