@@ -415,9 +415,80 @@ def tp_leg(n_layers=80, full_layers=80, shape="70b", batch=1, prompt_len=512, ne
     return res
 
 
+def tp_linear_leg(n_layers=0, full_layers=0, shape="70b", batch=16, precision=7, iters=30, **_):
+    """The row-parallel Linears of one layer (o_proj, down_proj) as operators, `batch` input
+    rows, three ways: (a) decode to bf16, library GEMM, NCCL all-reduce -- the default path;
+    (b) the fused decode -> tensor-core linear, then NCCL all-reduce; (c) the fused linear whose
+    epilogue stores the partial sums into every rank's memory and adds them (no collective
+    call).  Device time per call (CUDA events around `iters` calls, max over ranks); every
+    shard is larger than L2, so each call streams it from HBM."""
+    import torch.distributed as dist
+    import neuzip
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    cfg = SHAPES[shape]
+    res = {"workload": f"row-parallel Linears of a {shape}-shape layer, TP={world}, {batch} input rows, "
+                       f"precision {precision}", "tp": world, "rows": batch, "cases": []}
+    if world < 2:
+        res["skipped"] = "needs at least two ranks"
+        return res
+    manager = neuzip.Manager(precision=precision)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            y = fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters * 1e3], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return y, round(t.item(), 1)
+
+    for name, out_f, in_f in (("o_proj", cfg["d"], cfg["d"]),
+                              ("down_proj", cfg["d"], cfg["ffn"])):
+        shard = in_f // world
+        lin = torch.nn.Linear(shard, out_f, bias=False, device="cuda", dtype=torch.bfloat16)
+        lin.weight.data.normal_(0, 0.02, generator=gen)
+        layer = neuzip.nn.Linear(manager, lin, tp=("row", 0, 1, None))     # already this rank's block
+        layer.reduce_output = True
+        del lin
+        x = torch.randn(batch, shard, device="cuda", dtype=torch.bfloat16, generator=gen)
+        case = {"linear": name, "shard": [out_f, shard]}
+        with torch.no_grad():
+            manager.fuse_linear(0)
+            manager.fuse_tp_allreduce(None, max_rows=0)
+            layer.reduce_output = False
+            _, case["decode_gemm_only_us"] = timed(lambda: layer(x))
+            layer.reduce_output = True
+            y0, case["decode_gemm_nccl_us"] = timed(lambda: layer(x))
+            manager.fuse_linear(256)
+            layer.reduce_output = False
+            _, case["fused_linear_only_us"] = timed(lambda: layer(x))
+            layer.reduce_output = True
+            y1, case["fused_linear_nccl_us"] = timed(lambda: layer(x))
+            manager.fuse_tp_allreduce(None, max_rows=256)
+            y2, case["fused_linear_allreduce_us"] = timed(lambda: layer(x))
+            manager.check()
+            manager.fuse_tp_allreduce(None, max_rows=0)
+            manager.fuse_linear(0)
+        want = y2.float()
+        case["max_abs_diff_vs_default"] = round((y0.float() - want).abs().max().item(), 5)
+        case["output_abs_max"] = round(want.abs().max().item(), 3)
+        res["cases"].append(case)
+        del layer
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("leg", choices=["decode", "train", "tp"])
+    ap.add_argument("leg", choices=["decode", "train", "tp", "tp_linear"])
     ap.add_argument("--layers", type=int, default=0, help="0 = the configuration's own count")
     ap.add_argument("--shape", default=None)
     ap.add_argument("--batch", type=int, default=0)
@@ -437,9 +508,9 @@ def main():
         kw["precision"] = args.precision
     if args.new and args.leg != "train":
         kw["new_tokens"] = args.new
-    shape = args.shape or {"decode": "7b", "train": "1.3b", "tp": "70b"}[args.leg]
+    shape = args.shape or {"decode": "7b", "train": "1.3b", "tp": "70b", "tp_linear": "70b"}[args.leg]
     full = SHAPES[shape]["layers"]
-    fn = {"decode": decode_leg, "train": train_leg, "tp": tp_leg}[args.leg]
+    fn = {"decode": decode_leg, "train": train_leg, "tp": tp_leg, "tp_linear": tp_linear_leg}[args.leg]
     res = fn(n_layers=args.layers or full, full_layers=full, shape=shape, **kw)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(res))

@@ -398,20 +398,21 @@ int nz_linear_bf16(const void *container, uint64_t container_bytes, const void *
 /* Row-parallel Linears of a tensor-parallel model (each rank holds a block of
  * input columns) produce partial sums that have to be added over the ranks.
  * nz_linear_allreduce_bf16 is nz_linear_bf16 with that all-reduce fused in: the
- * kernel's epilogue writes its fp32 partial tiles straight from tensor memory
- * into EVERY rank's workspace with plain peer stores over NVLink (slot [source
- * rank][segment][row of x][row of W]), fences at system scope and adds one
- * arrival per CTA to every rank's arrival counters; a second kernel on each rank
- * waits (bounded: about a second, then NZ_STATUS_TIMEOUT) until every rank's CTAs
- * of the call have arrived and adds the partial sums rank by rank, segment by
- * segment, so every rank obtains the same bits.  No multicast, no library
- * collective.  All ranks must make the same sequence of calls (same shapes);
+ * kernel's epilogue writes its fp32 sums straight from tensor memory into EVERY
+ * rank's workspace with plain peer stores over NVLink (plane [source rank][row of
+ * x][row of W]; when the shard has several column segments, the CTAs of a row
+ * tile first add their partial sums locally, in segment order, and the last one
+ * to arrive does the peer stores), fences at system scope and adds one arrival
+ * per CTA to every rank's arrival counters; a second kernel on each rank waits
+ * (bounded: about a second, then NZ_STATUS_TIMEOUT) until every rank's CTAs of
+ * the call have arrived and adds the planes rank by rank, so every rank obtains
+ * the same bits.  No multicast, no library collective.  All ranks must make the same sequence of calls (same shapes);
  * arrival counters only grow: pass the value *arrivals_after of the previous
  * call on the same buffers as arrivals_before (0 at first).  A buffer set may be
  * reused by the call after next at the earliest, so alternate two sets.  The
  * bias, if any, is given on ONE rank only (it joins that rank's partial sums).
- * Reference: none - the reference has no tensor parallelism (survey section 2,
- * row 18); the baseline is nz_linear_bf16 followed by an NCCL all-reduce. */
+ * Reference: none - the reference has no tensor parallelism; the baseline is
+ * nz_linear_bf16 followed by an NCCL all-reduce. */
 typedef struct nz_peer_group {
   uint32_t world, rank;       /* 2..8 ranks, this rank's number                */
   void *workspace[8];         /* every rank's workspace as seen from this GPU  */

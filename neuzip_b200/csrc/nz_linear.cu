@@ -49,6 +49,7 @@ constexpr uint32_t kTileBytes = kTileRows * 128;    // 128 rows x 64 bf16
 constexpr uint32_t kMaxTokensPerLaunch = 256;       // MMA N and tensor-memory columns
 constexpr uint32_t kLinMaxStages = 4;
 constexpr uint32_t kMaxPeers = 8;                   // ranks of a tensor-parallel group
+constexpr uint32_t kTileCounterBytes = 4096;        // head of a peer workspace: u32 per row tile
 
 struct LinearArgs {
   const uint8_t *container;
@@ -71,12 +72,16 @@ struct LinearArgs {
   uint16_t *y;                // bf16[m_total, rows]
   float *partial;             // fp32[segs, m_total, rows] when segs > 1
   uint32_t *status;
-  // tensor-parallel all-reduce fused into the epilogue (tp_world > 1): every rank's partial
-  // sums go, by plain peer stores, into every rank's workspace [src rank][segment][token][row];
-  // a CTA then adds 1 (system scope) to counter `tp_rank` of every rank's arrival counters
+  // tensor-parallel all-reduce fused into the epilogue (tp_world > 1): the rank's sums over
+  // its columns go, by plain peer stores, into plane `tp_rank` of every rank's exchange area
+  // [src rank][token][row]; every CTA then adds 1 (system scope) to counter `tp_rank` of every
+  // rank's arrival counters.  With several column segments the CTAs of a row tile first put
+  // their partial sums into `partial` (local); the one that arrives last at the tile's
+  // counter adds them in segment order and does the peer stores.
   uint32_t tp_world, tp_rank;
   float *peer_partial[kMaxPeers];
   uint32_t *peer_arrivals[kMaxPeers];
+  uint32_t *tile_counters;    // u32[row tiles], zero between launches
 };
 
 // ------------------------------------------------------------------ PTX
@@ -284,6 +289,7 @@ constexpr uint32_t kBarEmpty = 192;
 constexpr uint32_t kBarDone = 224;
 constexpr uint32_t kTmemSlot = 232;      // u32: tensor-memory base address
 constexpr uint32_t kAbortSlot = 236;     // u32: abort flag
+constexpr uint32_t kLastSlot = 240;      // u32: this CTA arrived last at its row tile's counter
 constexpr uint32_t kCumOff = 256;        // u16[257]
 constexpr uint32_t kFlagOff = 256 + 520; // u32[3]
 
@@ -469,8 +475,7 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
       const uint32_t r = tile_id * kTileRows + 32 * sub + lane;
       // the bias rides on the direct store, or (tensor parallel: on the one rank that was
       // given it) on the partial sums of segment 0
-      const bool bias_here = p.tp_world > 1 ? seg == 0 : p.segs == 1;
-      const float bias = (p.bias && r < p.rows && bias_here)
+      const float bias = (p.bias && r < p.rows && p.segs == 1)
                              ? __uint_as_float((uint32_t)p.bias[r] << 16) : 0.f;
       for (uint32_t c0 = (warp >> 2) * 16; c0 < p.n_pad; c0 += 64) {
         uint32_t v[16];
@@ -482,8 +487,10 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
             const uint32_t t = c0 + i;
             if (t >= p.n_tok) break;
             const uint64_t tok = p.tok0 + t;
-            if (p.tp_world > 1) {
-              const uint64_t at = (((uint64_t)p.tp_rank * p.segs + seg) * p.m_total + tok) * p.rows + r;
+            if (p.segs > 1) {
+              p.partial[((uint64_t)seg * p.m_total + tok) * p.rows + r] = __uint_as_float(v[i]);
+            } else if (p.tp_world > 1) {
+              const uint64_t at = ((uint64_t)p.tp_rank * p.m_total + tok) * p.rows + r;
               const float part = __uint_as_float(v[i]) + bias;
               for (uint32_t q = 0; q < p.tp_world; ++q) p.peer_partial[q][at] = part;
             } else if (p.segs == 1) {
@@ -551,20 +558,69 @@ linear_kernel(const LinearArgs p, const __grid_constant__ CUtensorMap x_map) {
   // ---- common exit: everybody is done with tensor memory, then it is freed
   __syncwarp();
   tc_fence_before();
-  if (p.tp_world > 1) __threadfence_system();       // this thread's peer stores, before the signal
   __syncthreads();
-  if (p.tp_world > 1 && threadIdx.x == 0) {
-    // one arrival per CTA and rank, also when the CTA gave up: the peers' waits are bounded
-    // either way, and their status words tell them when the sums cannot be trusted.  The
-    // fence is cumulative over the CTA's stores that the barrier made visible to this thread.
-    __threadfence_system();
-    for (uint32_t q = 0; q < p.tp_world; ++q) atomicAdd_system(p.peer_arrivals[q] + p.tp_rank, 1u);
-  }
   if (is_mma) {
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(p.tmem_cols)
                  : "memory");
+  }
+  if (p.tp_world > 1) {
+    if (p.segs > 1) {
+      // the last of the row tile's CTAs adds the segments' partial sums, in segment order
+      // whoever it is, and hands the sums to every rank
+      volatile uint32_t *last_sh = reinterpret_cast<volatile uint32_t *>(misc + kLastSlot);
+      if (threadIdx.x == 0) {
+        __threadfence();                     // cumulative: the CTA's partial sums, then the count
+        const uint32_t before = atomicAdd(p.tile_counters + tile_id, 1u);
+        const bool last = before == p.segs - 1;
+        if (last) atomicExch(p.tile_counters + tile_id, 0u);     // ready for the next launch
+        *last_sh = last;
+      }
+      __syncthreads();
+      if (*last_sh && is_dec) {
+        __threadfence();
+        const uint32_t r = tile_id * kTileRows + 32 * (warp & 3) + lane;
+        if (r < p.rows) {
+          const float bias = p.bias ? __uint_as_float((uint32_t)p.bias[r] << 16) : 0.f;
+          // 8 tokens at a time: the loads of a pass are independent, only the adds are in order
+          constexpr uint32_t kStep = kLinDecWarps / 4, kBatch = 8;
+          for (uint32_t t0 = warp >> 2; t0 < p.n_tok; t0 += kStep * kBatch) {
+            float sum[kBatch];
+#pragma unroll
+            for (uint32_t k = 0; k < kBatch; ++k) sum[k] = 0.f;
+            for (uint32_t s = 0; s < p.segs; ++s) {
+              const float *plane = p.partial + ((uint64_t)s * p.m_total + p.tok0) * p.rows + r;
+              float part[kBatch];
+#pragma unroll
+              for (uint32_t k = 0; k < kBatch; ++k) {
+                const uint32_t t = t0 + k * kStep;
+                part[k] = t < p.n_tok ? __ldcg(plane + (uint64_t)t * p.rows) : 0.f;
+              }
+#pragma unroll
+              for (uint32_t k = 0; k < kBatch; ++k) sum[k] += part[k];
+            }
+#pragma unroll
+            for (uint32_t k = 0; k < kBatch; ++k) {
+              const uint32_t t = t0 + k * kStep;
+              if (t >= p.n_tok) break;
+              const uint64_t at = ((uint64_t)p.tp_rank * p.m_total + p.tok0 + t) * p.rows + r;
+              const float total = sum[k] + bias;
+              for (uint32_t q = 0; q < p.tp_world; ++q) p.peer_partial[q][at] = total;
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0 && (p.segs == 1 || *reinterpret_cast<volatile uint32_t *>(misc + kLastSlot))) {
+      // one arrival per row tile and rank, from the CTA that did the tile's peer stores, also
+      // when a CTA gave up: the peers' waits are bounded either way, and their status words
+      // tell them when the sums cannot be trusted.  The fence is cumulative over the CTA's
+      // stores that the barrier made visible to this thread.
+      __threadfence_system();
+      for (uint32_t q = 0; q < p.tp_world; ++q) atomicAdd_system(p.peer_arrivals[q] + p.tp_rank, 1u);
+    }
   }
 }
 
@@ -583,16 +639,17 @@ __global__ void linear_finish_kernel(const float *__restrict__ partial, uint32_t
   y[i] = f32_to_bf16_rn(sum);
 }
 
-// The same for a tensor-parallel group: the partial sums of every rank and segment lie in
-// this rank's workspace; wait (bounded) until every rank's CTAs of this call have arrived,
-// then add rank by rank, segment by segment -- the same order on every rank, so all ranks
-// get the same bits.  `expected` = arrivals per rank up to and including this call.
+// The last step for a tensor-parallel group: every rank's sums lie in this rank's exchange
+// area [src rank][token][row]; wait (bounded) until every rank's CTAs of this call have
+// arrived, then add rank by rank -- the same order on every rank, so all ranks get the same
+// bits.  `expected` = arrivals per rank up to and including this call.
 __global__ void linear_allreduce_finish_kernel(const float *__restrict__ partial,
                                                const uint32_t *arrivals, uint32_t expected,
-                                               uint32_t world, uint32_t segs, uint64_t plane,
-                                               uint32_t rows, const uint16_t *__restrict__ bias,
+                                               uint32_t world, uint64_t plane,
                                                uint16_t *__restrict__ y, uint32_t *status) {
   __shared__ uint32_t ok_sh;
+  // launched with programmatic stream serialisation: this rank's linear kernel first
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) {
     uint32_t ok = 1;
     for (uint32_t q = 0; q < world && ok; ++q) {
@@ -615,8 +672,7 @@ __global__ void linear_allreduce_finish_kernel(const float *__restrict__ partial
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= plane) return;
   float sum = 0.f;
-  for (uint32_t k = 0; k < world * segs; ++k) sum += __ldcv(partial + (uint64_t)k * plane + i);
-  if (bias) sum += __uint_as_float((uint32_t)bias[i % rows] << 16);
+  for (uint32_t k = 0; k < world; ++k) sum += __ldcv(partial + (uint64_t)k * plane + i);
   y[i] = f32_to_bf16_rn(sum);
   (void)ok_sh;
 }
@@ -773,8 +829,13 @@ static int linear_impl(const void *container, uint64_t container_bytes, const vo
     return NZ_E_FORMAT;
   }
   if (segs > 1 || peers) {
-    const uint64_t need = peers ? align16((uint64_t)world * segs * m_tokens * rows * 4)
+    const uint64_t need = peers ? nz_linear_allreduce_workspace_bytes(rows, cols, lane_symbols,
+                                                                      m_tokens, world)
                                 : nz_linear_workspace_bytes(rows, cols, lane_symbols, m_tokens);
+    if (peers && (rows + kTileRows - 1) / kTileRows > kTileCounterBytes / 4) {
+      set_error("nz_linear_allreduce_bf16: more than %u row tiles", kTileCounterBytes / 4);
+      return NZ_E_ARG;
+    }
     if (!workspace || ((uintptr_t)workspace & 15) || workspace_bytes < need) {
       set_error("nz_linear_bf16: workspace of %llu bytes is smaller than the %llu required "
                 "(or misaligned)", (unsigned long long)workspace_bytes, (unsigned long long)need);
@@ -836,9 +897,12 @@ static int linear_impl(const void *container, uint64_t container_bytes, const vo
     p.tp_world = world;
     p.tp_rank = peers->rank;
     for (uint32_t q = 0; q < world; ++q) {
-      p.peer_partial[q] = (float *)peers->workspace[q];
+      p.peer_partial[q] = (float *)((uint8_t *)peers->workspace[q] + kTileCounterBytes);
       p.peer_arrivals[q] = (uint32_t *)peers->arrivals[q];
     }
+    // this rank's workspace: tile counters, the exchange planes, the segments' partial sums
+    p.tile_counters = (uint32_t *)workspace;
+    p.partial = p.peer_partial[peers->rank] + (uint64_t)world * m_tokens * rows;
   }
 
   void (*kern)(const LinearArgs, const CUtensorMap) = nullptr;
@@ -876,8 +940,8 @@ static int linear_impl(const void *container, uint64_t container_bytes, const vo
     NZ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, x_map));
   }
   if (peers) {
-    // every CTA of every rank's launches adds one arrival per rank
-    const uint32_t expected = arrivals_before + launches * tiles * segs;
+    // every row tile of every rank's launches adds one arrival per rank
+    const uint32_t expected = arrivals_before + launches * tiles;
     if (arrivals_after) *arrivals_after = expected;
     const uint64_t plane = m_tokens * rows;
     const uint64_t blocks = (plane + 255) / 256;
@@ -885,10 +949,19 @@ static int linear_impl(const void *container, uint64_t container_bytes, const vo
       set_error("nz_linear_allreduce_bf16: output too large for one call");
       return NZ_E_ARG;
     }
-    linear_allreduce_finish_kernel<<<(unsigned)blocks, 256, 0, st>>>(
-        (const float *)workspace, (const uint32_t *)peers->arrivals[peers->rank], expected, world,
-        segs, plane, (uint32_t)rows, nullptr, (uint16_t *)y_bf16, (uint32_t *)status);
-    NZ_LAUNCH_CHECK("linear_allreduce_finish_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NZ_CUDA_TRY(cudaLaunchKernelEx(&cfg, linear_allreduce_finish_kernel,
+                                   (const float *)p.peer_partial[peers->rank],
+                                   (const uint32_t *)peers->arrivals[peers->rank], expected, world,
+                                   plane, (uint16_t *)y_bf16, (uint32_t *)status));
     return NZ_OK;
   }
   if (segs > 1) {
@@ -932,7 +1005,7 @@ extern "C" uint64_t nz_linear_allreduce_workspace_bytes(uint64_t rows, uint64_t 
                                                         uint32_t world) {
   const uint32_t segs = nz::operand_segments(cols, lane_symbols);
   if (segs == 0 || world < 2) return 0;
-  return nz::align16((uint64_t)world * segs * m_tokens * rows * 4);
+  return nz::kTileCounterBytes + nz::align16((uint64_t)(world + (segs > 1 ? segs : 0)) * m_tokens * rows * 4);
 }
 
 extern "C" int nz_linear_allreduce_bf16(const void *container, uint64_t container_bytes,
