@@ -478,7 +478,7 @@ __device__ __forceinline__ bool open_unit(const UnitPlan &pl, uint32_t slot, uin
 //   table_scan     warp 0 scans the container's 256 frequencies into cum_sh[257]; one
 //                  other thread checks the header against what the host passed
 //   table_verdict  (after a barrier) every thread computes the same verdict
-//   table_fill     warps take symbols in turn and fill their slot ranges
+//   table_fill     warps take 32 slots in turn, look their symbols up and write the rows
 // flag_sh points at three words: header verdict, probability bits, "a frequency does
 // not fit the table entry".
 __device__ __forceinline__ void table_scan(const DecodeArgs &a, const Header *h, uint64_t pay_off,
@@ -557,12 +557,29 @@ __device__ __forceinline__ void table_fill(uint32_t lut_shift, uint32_t S, uint3
   lv.k64k = S ? 65536u : 0u;        // S is never 0; the compiler cannot know
   uint32_t *lut_w = reinterpret_cast<uint32_t *>(smem);
   const uint32_t wsh = row_shift - 2;                     // log2 of the words per slot row
-  for (uint32_t sym = warp; sym < 256; sym += n_warps) {
-    const uint32_t start = cum_sh[sym], end = cum_sh[sym + 1];
-    const uint32_t hi = (sym << kEntSymShift) | ((end - start) << kEntFreqShift);
-    const uint32_t words = (end - start) << wsh;
-    uint32_t *dst = lut_w + (start << wsh);
-    for (uint32_t k = lane; k < words; k += 32) dst[k] = hi | (k >> wsh);
+  // A warp takes 32 slots at a time: lane l finds the symbol that owns slot s0 + l (the
+  // largest symbol whose cumulative count is not above the slot; symbols that do not occur
+  // share their successor's count and are skipped by "largest"), then the warp writes the
+  // 32 rows with whole-warp stores.  The cost does not depend on how the counts are spread
+  // over the symbols, and a CTA of few warps is not held up by the 256-symbol walk.
+  const uint32_t n_slots = 1u << pb;
+  for (uint32_t s0 = warp * 32; s0 < n_slots; s0 += n_warps * 32) {
+    const uint32_t slot = s0 + lane;
+    uint32_t sym = 0;
+#pragma unroll
+    for (uint32_t step = 128; step >= 1; step >>= 1)
+      if (cum_sh[sym + step] <= slot) sym += step;
+    const uint32_t start = cum_sh[sym];
+    const uint32_t entry = (sym << kEntSymShift) | ((cum_sh[sym + 1] - start) << kEntFreqShift) |
+                           (slot - start);
+    uint32_t *dst = lut_w + (s0 << wsh);
+    if (wsh == 5) {
+#pragma unroll 8
+      for (uint32_t j = 0; j < 32; ++j) dst[j * 32 + lane] = __shfl_sync(0xFFFFFFFFu, entry, j);
+    } else {
+      for (uint32_t k = lane; k < (32u << wsh); k += 32)
+        dst[k] = __shfl_sync(0xFFFFFFFFu, entry, k >> wsh);
+    }
   }
 }
 
