@@ -64,14 +64,16 @@ extern "C" uint64_t nz_frac_bytes(uint64_t n, int precision) {
 }
 
 extern "C" uint32_t nz_default_lane_symbols(int precision) {
-  // Short lane streams decode with more parallelism, long ones cost fewer
-  // bytes of per-lane state.  Lossy modes store fewer bytes in total, so the
-  // same absolute overhead weighs more there: they get the longer streams.
+  // Short lane streams decode with more parallelism (and leave a warp's units of the
+  // compressor and the decoder more shared memory), long ones cost fewer bytes of per-lane
+  // state.  Lossy modes store fewer bytes in total, so the same absolute overhead weighs
+  // more there: the two coarsest get longer streams, as long as the decoder keeps its rate
+  // (on a B200 it falls by a quarter from 512 to 640 symbols: fewer resident warps).
   switch (precision) {
     case 7: return 256;
-    case 3: return 384;
-    case 1: return 512;
-    case 0: return 640;
+    case 3: return 256;
+    case 1: return 384;
+    case 0: return 512;
     default: return 0;
   }
 }

