@@ -25,16 +25,19 @@ _COUNTER_BYTES = 256
 class PeerReducer:
     """Two peer-mapped buffer sets of `workspace_bytes` each for the ranks of `group`."""
 
-    def __init__(self, group=None, workspace_bytes: int = 64 << 20) -> None:
+    def __init__(self, group=None, workspace_bytes: int = 64 << 20, lib=None,
+                 device: Optional[int] = None) -> None:
+        """`lib` and `device` default to the CUDA library and the current device (tests pass
+        stand-ins to exercise the bookkeeping without a GPU)."""
         import torch.distributed as dist
-        self._lib = _lib.load()
+        self._lib = lib if lib is not None else _lib.load()
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if not 2 <= self.world <= 8:
             raise ValueError(f"a peer group has 2 to 8 ranks, got {self.world}")
         self.workspace_bytes = (int(workspace_bytes) + 255) // 256 * 256
-        self.device = torch.cuda.current_device()
+        self.device = torch.cuda.current_device() if device is None else int(device)
         self._own: List[Tuple[int, int]] = []
         self._mapped: List[int] = []
         mine = []
@@ -88,7 +91,8 @@ class PeerReducer:
         own: a peer must not be storing into a buffer that is freed)."""
         if self._lib is None:
             return
-        torch.cuda.synchronize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
         for ptr in self._mapped:
             self._lib.nz_peer_close(ptr)
         for ws, arr in self._own:
