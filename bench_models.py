@@ -315,11 +315,11 @@ def train_leg(n_layers=6, full_layers=24, shape="1.3b", batch=8, seq=1024, steps
     manager.check()
     res["neuzip_tok_s"] = round(tokens / t, 1)
     res["neuzip_loss"] = loss
-    # the same with the optimiser's three separate calls per weight (decode, update kernel,
-    # compress) instead of the update fused into the decode kernel
-    opt.fused_update = False
+    # the same with the update fused into the decode kernel (one library call per weight)
+    # instead of the optimiser's three separate calls (decode, update kernel, compress)
+    opt.fused_update = True
     t, _ = run(model, opt, warmup=1)
-    res["neuzip_unfused_update_tok_s"] = round(tokens / t, 1)
+    res["neuzip_fused_update_tok_s"] = round(tokens / t, 1)
     res["neuzip_peak_bytes"] = torch.cuda.max_memory_allocated()
     res["ratio_vs_dense_tok_s"] = round(res["neuzip_tok_s"] / res["dense_tok_s"], 3)
     if world > 1:

@@ -162,6 +162,16 @@ int nz_encode_exponents_static_scratch(const void *exp_in, uint64_t n,
 int nz_container_bytes(const void *container, uint64_t *total_bytes,
                        uint32_t *max_unit_words, void *stream);
 
+/* The same without the synchronisation: enqueues the copy of the 64-byte header
+ * into `host_header64` (pinned host memory, 8-byte aligned) on the stream and
+ * returns; once the stream has passed that point (an event the caller
+ * records), nz_parse_header reads length and largest unit from the copy.  This
+ * is how a write avoids stalling the host.  nz_parse_header is a host function
+ * and returns NZ_E_FORMAT when the bytes are not a header.
+ * Reference: none (the reference blocks, cuda/high_level.cu:114-115). */
+int nz_container_header_async(const void *container, void *host_header64, void *stream);
+int nz_parse_header(const void *host_header64, uint64_t *total_bytes, uint32_t *max_unit_words);
+
 /* Decode the container into n exponent bytes.  `status` is a device u32 the
  * kernel ORs NZ_STATUS_* bits into (may be NULL).  max_unit_words is the
  * value nz_container_bytes returned (0 = assume the worst case).
@@ -198,8 +208,9 @@ int nz_decompress_bf16(const void *container, uint64_t container_bytes,
  * bf16 arrays of n elements (state_is_bf16), `step` counts from 1, the gradient
  * is multiplied by grad_scale first (1/world_size after a sum all-reduce).
  * w <- w*(1 - lr*wd) - lr/(1-b1^t) * m / (sqrt(v/(1-b2^t)) + eps), all in fp32,
- * rounded to bf16 once.  It is the update between the read and the write of
- * the reference's in-backward step, which uses plain SGD there.
+ * rounded to bf16 once.  All four arrays 16-byte aligned.  It is the update
+ * between the read and the write of the reference's in-backward step, which
+ * uses plain SGD there.
  * Reference: compressed_lomo_hook, neuzip/__init__.py:25-35. */
 int nz_adamw_bf16(void *weight_bf16, const void *grad_bf16, void *exp_avg,
                   void *exp_avg_sq, uint64_t n, int state_is_bf16, float lr,

@@ -48,6 +48,8 @@ SIGNATURES = {
     "nz_static_scratch_bytes": (_u64, []),
     "nz_encode_exponents_static_scratch": (_int, [_vp, _u64, _u32, _vp, _u64, _vp]),
     "nz_container_bytes": (_int, [_vp, ctypes.POINTER(_u64), ctypes.POINTER(_u32), _vp]),
+    "nz_container_header_async": (_int, [_vp, _vp, _vp]),
+    "nz_parse_header": (_int, [_vp, ctypes.POINTER(_u64), ctypes.POINTER(_u32)]),
     "nz_decode_exponents": (_int, [_vp, _u64, _u64, _u32, _u32, _vp, _vp, _vp]),
     "nz_compress_bf16": (_int, [_vp, _u64, _int, _u32, _vp, _vp, _u64, _vp, _u64, _vp]),
     "nz_decompress_bf16": (_int, [_vp, _u64, _vp, _u64, _int, _u32, _u32, _int, _vp, _vp, _vp]),

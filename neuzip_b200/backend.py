@@ -47,7 +47,7 @@ class _Entry:
     stamp: int = 0            # number of the library operation that wrote these bytes
     operand_cols: int = 0     # > 0: a [numel / operand_cols, operand_cols] matrix in operand order
     # While a write is still in flight the container sits in its worst-case-sized buffer;
-    # `pending` = (pinned copy of the header, event after that copy).  Once the event has
+    # `pending` = (slot of the pinned header copy, event after that copy).  Once the event has
     # completed the entry is settled: right-sized container, real max_unit_words.
     pending: Optional[tuple] = None
     version: int = 0          # bumped when the container tensor is replaced
@@ -144,6 +144,11 @@ class CodecBackend:
         # (nz_linear_bf16) on operand-order weights; 0 = always decode, then library GEMM
         self.fused_linear_max_rows = 0
         self._lin_ws: Optional[torch.Tensor] = None
+        # pinned header slots and events of writes that have not been right-sized yet
+        self._hdr_chunks: List[torch.Tensor] = []
+        self._hdr_base: List[int] = []
+        self._hdr_free: List[int] = []
+        self._event_pool: list = []
         # True: `write` waits for the compressed size like the reference does
         self.sync_writes = False
 
@@ -210,7 +215,7 @@ class CodecBackend:
                                                   _ptr(frac), _ptr(staging), cap, _ptr(scratch),
                                                   scratch.numel(), st))
             self._cache[name] = self._finish_write(
-                _Entry(n, tensor.dtype, S, 0, staging, frac, None, _next_op(), cols))
+                _Entry(n, tensor.dtype, S, 0, staging, frac, None, _next_op(), cols), previous)
             return
         normalizers = None
         if self.normalizer_size:
@@ -229,7 +234,7 @@ class CodecBackend:
         _lib.check(L.nz_compress_bf16(_ptr(flat), n, self.precision, S, _ptr(frac), _ptr(staging),
                                       cap, _ptr(scratch), scratch.numel(), st))
         self._cache[name] = self._finish_write(
-            _Entry(n, tensor.dtype, S, 0, staging, frac, normalizers, _next_op()))
+            _Entry(n, tensor.dtype, S, 0, staging, frac, normalizers, _next_op()), previous)
 
     def adamw_update(self, name: str, grad: torch.Tensor, exp_avg: torch.Tensor,
                      exp_avg_sq: torch.Tensor, lr: float, beta1: float, beta2: float, eps: float,
@@ -260,40 +265,63 @@ class CodecBackend:
             grad_scale, _ptr(frac), _ptr(staging), cap, _ptr(scratch), scratch.numel(),
             _ptr(self._status), _stream()))
         self._cache[name] = self._finish_write(
-            _Entry(n, entry.dtype, S, 0, staging, frac, None, _next_op(), entry.operand_cols))
+            _Entry(n, entry.dtype, S, 0, staging, frac, None, _next_op(), entry.operand_cols), entry)
         return True
 
     # -- settling a write without stalling the host ----------------------------
-    def _finish_write(self, entry: _Entry) -> _Entry:
+    def _finish_write(self, entry: _Entry, replaced: Optional[_Entry] = None) -> _Entry:
         """The reference reads the compressed size back right after compressing, which
         blocks the host (cuda/high_level.cu:114-115).  Here the 64-byte container header
         is copied to pinned memory asynchronously; the entry is usable at once (decoding
         from the worst-case-sized buffer) and is right-sized the first time it is touched
-        after that copy has completed.  `sync_writes = True` restores the blocking form."""
-        header = torch.empty(64, dtype=torch.uint8).pin_memory()
-        header.copy_(entry.container[:64], non_blocking=True)
-        event = torch.cuda.Event()
+        after that copy has completed.  `sync_writes = True` restores the blocking form.
+        Header slots (one pinned buffer, 64 bytes each) and events are pooled: a write
+        allocates no pinned memory and creates no event once the pools are warm."""
+        if replaced is not None and replaced.pending is not None:
+            # overwritten before it was ever settled: its slot and event go back (a copy
+            # still in flight into the slot lands before the next one, same stream)
+            self._release_pending(replaced)
+        if not self._hdr_free:
+            self._grow_header_pool()
+        slot = self._hdr_free.pop()
+        event = self._event_pool.pop() if self._event_pool else torch.cuda.Event()
+        _lib.check(self._lib.nz_container_header_async(
+            _ptr(entry.container), self._hdr_base[slot >> 8] + 64 * (slot & 255), _stream()))
         event.record()
-        entry.pending = (header, event)
+        entry.pending = (slot, event)
         if self.sync_writes:
             self._settle(entry, block=True)
         return entry
 
+    def _grow_header_pool(self) -> None:
+        chunk = torch.empty(256 * 64, dtype=torch.uint8).pin_memory()
+        index = len(self._hdr_chunks)
+        self._hdr_chunks.append(chunk)
+        self._hdr_base.append(chunk.data_ptr())
+        self._hdr_free.extend(range(256 * index + 255, 256 * index - 1, -1))
+
+    def _release_pending(self, entry: _Entry) -> None:
+        slot, event = entry.pending
+        self._hdr_free.append(slot)
+        self._event_pool.append(event)
+        entry.pending = None
+
     def _settle(self, entry: _Entry, block: bool) -> None:
         if entry.pending is None:
             return
-        header, event = entry.pending
+        slot, event = entry.pending
         if block:
             event.synchronize()
         elif not event.query():
             return
-        words = header.view(torch.int32)
-        if int(words[0]) != 0x31525A4E:
+        total, words = ctypes.c_uint64(0), ctypes.c_uint32(0)
+        rc = self._lib.nz_parse_header(self._hdr_base[slot >> 8] + 64 * (slot & 255),
+                                       ctypes.byref(total), ctypes.byref(words))
+        self._release_pending(entry)
+        if rc:
             raise _lib.NeuzipError("write produced no NZR1 container")
-        total = int(header.view(torch.int64)[6])
-        entry.max_unit_words = int(words[15])
-        entry.container = entry.container[:total].clone()     # enqueued after the write
-        entry.pending = None
+        entry.max_unit_words = words.value
+        entry.container = entry.container[:total.value].clone()     # enqueued after the write
         entry.version += 1
 
     def settle_all(self) -> None:
@@ -662,13 +690,18 @@ class CodecBackend:
         normalizers = blob.get("normalizers")
         if normalizers is not None:
             normalizers = normalizers.to(device="cuda", dtype=torch.uint8).contiguous()
+        replaced = self._cache.get(name)
+        if replaced is not None and replaced.pending is not None:
+            self._release_pending(replaced)
         self._cache[name] = _Entry(n, torch.bfloat16, int(blob["lane_symbols"]),
                                    int(blob["max_unit_words"]), container, fractions, normalizers,
                                    _next_op(), int(blob.get("operand_cols", 0)))
 
     # -- extras -----------------------------------------------------------
     def erase(self, name: str) -> None:
-        self._cache.pop(name, None)
+        gone = self._cache.pop(name, None)
+        if gone is not None and gone.pending is not None:
+            self._release_pending(gone)
 
     def entry(self, name: str) -> _Entry:
         entry = self._cache[name]

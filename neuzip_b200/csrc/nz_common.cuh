@@ -115,11 +115,14 @@ struct AdamArgs {
 };
 __device__ __forceinline__ float adamw_element(float w, float g, float &m, float &v,
                                                const AdamArgs &a) {
-  const float grad = g * a.grad_scale;
-  m = a.beta1 * m + (1.0f - a.beta1) * grad;
-  v = a.beta2 * v + (1.0f - a.beta2) * grad * grad;
-  w *= 1.0f - a.lr * a.weight_decay;
-  w -= (a.lr / a.bias1) * m / (sqrtf(v / a.bias2) + a.eps);
+  // every operation is spelled out with its rounding, so that the compiler cannot contract
+  // multiplies and adds differently in the kernels that share the formula
+  const float grad = __fmul_rn(g, a.grad_scale);
+  m = __fmaf_rn(a.beta1, m, __fmul_rn(__fsub_rn(1.0f, a.beta1), grad));
+  v = __fmaf_rn(a.beta2, v, __fmul_rn(__fmul_rn(__fsub_rn(1.0f, a.beta2), grad), grad));
+  w = __fmul_rn(w, __fsub_rn(1.0f, __fmul_rn(a.lr, a.weight_decay)));
+  const float denom = __fadd_rn(__fsqrt_rn(__fdiv_rn(v, a.bias2)), a.eps);
+  w = __fsub_rn(w, __fdiv_rn(__fmul_rn(__fdiv_rn(a.lr, a.bias1), m), denom));
   return w;
 }
 

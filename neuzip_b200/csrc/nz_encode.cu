@@ -16,6 +16,8 @@
 //   [4096, 4096+4*(nu+1))           u32 unit_words[nu]  (bit 31 = raw)
 //   [.., + 64*nu)                   u16 lane_len[nu][32]   (words; 0 = unit raw)
 //   [.., + nu*32*cap*2)             u16 lane_words[nu][32][cap]   cap = lane_cap_words(S)
+#include <string.h>
+
 #include <mutex>
 
 #include "nz_common.cuh"
@@ -836,12 +838,18 @@ __device__ __forceinline__ void encode_step_sh(uint32_t &x, int32_t &idx, uint32
 // minus frequency, cumulative count), as bf16_encode_kernel lays the table out.
 __device__ __forceinline__ void encode_apply(uint32_t &x, int32_t &idx, const uint4 e,
                                              uint32_t slice, uint32_t pow_m) {
-  if (x >= e.x) {
-    const uint32_t at = slice + 2u * (uint32_t)max(idx, 1);
-    asm volatile("st.shared.u16 [%0], %1;" ::"r"(at), "h"((uint16_t)x) : "memory");
-    x >>= 16;
-    --idx;
-  }
+  // renormalisation without a branch: the store is predicated, shift and count are selects
+  const uint32_t full = x >= e.x;
+  const uint32_t at = slice + 2u * (uint32_t)max(idx, 1);
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.u32 p, %2, 0;\n\t"
+      "@p st.shared.u16 [%0], %1;\n\t"
+      "}" ::"r"(at), "h"((uint16_t)x), "r"(full)
+      : "memory");
+  x = full ? x >> 16 : x;
+  idx -= (int32_t)full;
   uint32_t q = __umulhi(x, e.y);
   uint32_t r0 = q * e.z + x;                 // x - q * freq
   const uint32_t r1 = r0 + e.z;
@@ -1413,6 +1421,34 @@ extern "C" int nz_container_bytes(const void *container, uint64_t *total_bytes,
   NZ_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
   if (h.magic != nz::kMagic || h.version != 1) {
     nz::set_error("nz_container_bytes: not an NZR1 container");
+    return NZ_E_FORMAT;
+  }
+  *total_bytes = h.total_bytes;
+  if (max_unit_words) *max_unit_words = h.max_coded_unit_words;
+  return NZ_OK;
+}
+
+extern "C" int nz_container_header_async(const void *container, void *host_header64, void *stream) {
+  if (!container || !host_header64) {
+    nz::set_error("nz_container_header_async: null pointer");
+    return NZ_E_ARG;
+  }
+  static_assert(sizeof(nz::Header) == 64, "header size");
+  NZ_CUDA_TRY(cudaMemcpyAsync(host_header64, container, sizeof(nz::Header), cudaMemcpyDeviceToHost,
+                              (cudaStream_t)stream));
+  return NZ_OK;
+}
+
+extern "C" int nz_parse_header(const void *host_header64, uint64_t *total_bytes,
+                               uint32_t *max_unit_words) {
+  if (!host_header64 || !total_bytes) {
+    nz::set_error("nz_parse_header: null pointer");
+    return NZ_E_ARG;
+  }
+  nz::Header h;
+  memcpy(&h, host_header64, sizeof(h));
+  if (h.magic != nz::kMagic || h.version != 1) {
+    nz::set_error("nz_parse_header: not an NZR1 header");
     return NZ_E_FORMAT;
   }
   *total_bytes = h.total_bytes;

@@ -17,7 +17,42 @@ __device__ __forceinline__ void store_state(__nv_bfloat16 *p, uint64_t i, float 
   p[i] = __float2bfloat16_rn(v);
 }
 
-// 8 elements per thread: 128-bit loads of weight and gradient.
+// The 8 moments a thread owns, as 128-bit accesses: one for bf16 moments, two for fp32.
+struct State8 {
+  float f[8];
+};
+__device__ __forceinline__ State8 load_state8(const float *p, uint64_t i) {
+  State8 s;
+  const float4 a = reinterpret_cast<const float4 *>(p)[2 * i];
+  const float4 b = reinterpret_cast<const float4 *>(p)[2 * i + 1];
+  s.f[0] = a.x; s.f[1] = a.y; s.f[2] = a.z; s.f[3] = a.w;
+  s.f[4] = b.x; s.f[5] = b.y; s.f[6] = b.z; s.f[7] = b.w;
+  return s;
+}
+__device__ __forceinline__ State8 load_state8(const __nv_bfloat16 *p, uint64_t i) {
+  State8 s;
+  const uint4 q = reinterpret_cast<const uint4 *>(p)[i];
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    s.f[2 * k] = __uint_as_float(w[k] << 16);
+    s.f[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+  }
+  return s;
+}
+__device__ __forceinline__ void store_state8(float *p, uint64_t i, const State8 &s) {
+  reinterpret_cast<float4 *>(p)[2 * i] = make_float4(s.f[0], s.f[1], s.f[2], s.f[3]);
+  reinterpret_cast<float4 *>(p)[2 * i + 1] = make_float4(s.f[4], s.f[5], s.f[6], s.f[7]);
+}
+__device__ __forceinline__ void store_state8(__nv_bfloat16 *p, uint64_t i, const State8 &s) {
+  __nv_bfloat16 h[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) h[k] = __float2bfloat16_rn(s.f[k]);
+  reinterpret_cast<uint4 *>(p)[i] = *reinterpret_cast<const uint4 *>(h);
+}
+
+// 8 elements per thread: 128-bit loads and stores of weight, gradient and both moments
+// (moment arrays 16-byte aligned: the host checks).
 template <typename StateT>
 __global__ void __launch_bounds__(256)
 adamw_kernel(__nv_bfloat16 *__restrict__ w, const __nv_bfloat16 *__restrict__ g,
@@ -27,17 +62,17 @@ adamw_kernel(__nv_bfloat16 *__restrict__ w, const __nv_bfloat16 *__restrict__ g,
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
     uint4 wv = reinterpret_cast<const uint4 *>(w)[i];
     const uint4 gv = reinterpret_cast<const uint4 *>(g)[i];
+    State8 mm = load_state8(m, i), vv = load_state8(v, i);
     __nv_bfloat16 *wp = reinterpret_cast<__nv_bfloat16 *>(&wv);
     const __nv_bfloat16 *gp = reinterpret_cast<const __nv_bfloat16 *>(&gv);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const uint64_t e = i * 8 + k;
-      float mm = load_state(m, e), vv = load_state(v, e);
-      const float x = adamw_element(__bfloat162float(wp[k]), __bfloat162float(gp[k]), mm, vv, a);
-      store_state(m, e, mm);
-      store_state(v, e, vv);
+      const float x = adamw_element(__bfloat162float(wp[k]), __bfloat162float(gp[k]), mm.f[k],
+                                    vv.f[k], a);
       wp[k] = __float2bfloat16_rn(x);
     }
+    store_state8(m, i, mm);
+    store_state8(v, i, vv);
     reinterpret_cast<uint4 *>(w)[i] = wv;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -62,8 +97,9 @@ extern "C" int nz_adamw_bf16(void *weight_bf16, const void *grad_bf16, void *exp
     nz::set_error("nz_adamw_bf16: null pointer or step 0");
     return NZ_E_ARG;
   }
-  if (((uintptr_t)weight_bf16 & 15) || ((uintptr_t)grad_bf16 & 15)) {
-    nz::set_error("nz_adamw_bf16: weight and gradient must be 16-byte aligned");
+  if (((uintptr_t)weight_bf16 & 15) || ((uintptr_t)grad_bf16 & 15) || ((uintptr_t)exp_avg & 15) ||
+      ((uintptr_t)exp_avg_sq & 15)) {
+    nz::set_error("nz_adamw_bf16: weight, gradient and moments must be 16-byte aligned");
     return NZ_E_ARG;
   }
   nz::AdamArgs a;
