@@ -410,12 +410,14 @@ def linear_leg(L, torch, index):
     sampler = ClockSampler(index).start()
     for rows, cols in ((4096, 11008), (4096, 4096), (11008, 4096)):
         s, n = 7, rows * cols
-        S_op = int(L.nz_operand_lane_symbols(cols, s))
+        S_op = int(L.nz_operand_lane_symbols_for(rows, cols, s))
         S_fl = int(L.nz_default_lane_symbols(s))
         copies = 4
         ops, flats = [], []
         gen = torch.Generator(device="cuda")
-        scratch = torch.empty(int(L.nz_compress_scratch_bytes(n, S_fl)), dtype=torch.uint8, device="cuda")
+        scratch = torch.empty(max(int(L.nz_compress_scratch_bytes(n, S_fl)),
+                                  int(L.nz_compress_operand_scratch_bytes(rows, cols, S_op))),
+                              dtype=torch.uint8, device="cuda")
         for k in range(copies):
             gen.manual_seed(50 + k)
             w = (torch.randn(rows, cols, generator=gen, device="cuda") * 0.02).to(torch.bfloat16)

@@ -365,6 +365,13 @@ int nz_linear_vec_bf16(const void *container, uint64_t container_bytes,
  * cannot be stored in operand order. */
 uint32_t nz_operand_lane_symbols(uint64_t cols, int precision);
 
+/* The same for a matrix whose row count is known: the unit length (16 to 48
+ * blocks of 64 columns) with which nz_linear_bf16 has the fewest decode steps in
+ * sequence on the 148 SMs of a B200 - one work item per 128-row tile and
+ * unit-long column segment, run in waves of 148.  Falls back to the rule above
+ * when cols / 64 has no divisor in that range; rows = 0 means "unknown". */
+uint32_t nz_operand_lane_symbols_for(uint64_t rows, uint64_t cols, int precision);
+
 /* nz_compress_bf16 for a row-major [rows, cols] matrix, stored in operand order.
  * Scratch of nz_compress_operand_scratch_bytes bytes.
  * Reference: Manager::_write_to_cache, cuda/high_level.cu:71-130. */

@@ -83,6 +83,7 @@ SIGNATURES["nz_decompress_bf16_batch"] = (
     _int, [ctypes.POINTER(DecompressItem), _u32, _int, _u32, _int, _vp, _vp])
 
 SIGNATURES["nz_operand_lane_symbols"] = (_u32, [_u64, _int])
+SIGNATURES["nz_operand_lane_symbols_for"] = (_u32, [_u64, _u64, _int])
 SIGNATURES["nz_compress_operand_scratch_bytes"] = (_u64, [_u64, _u64, _u32])
 SIGNATURES["nz_compress_bf16_operand"] = (
     _int, [_vp, _u64, _u64, _int, _u32, _vp, _vp, _u64, _vp, _u64, _vp])

@@ -184,7 +184,7 @@ class CodecBackend:
         rows, cols = int(tensor.shape[0]), int(tensor.shape[1])
         if rows % 4 or cols % 64:
             return None
-        S = int(self._lib.nz_operand_lane_symbols(cols, self.precision))
+        S = int(self._lib.nz_operand_lane_symbols_for(rows, cols, self.precision))
         return (cols, S) if S else None
 
     def write(self, name: str, tensor: torch.Tensor, operand: Optional[bool] = None) -> None:

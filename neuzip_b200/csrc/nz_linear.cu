@@ -769,6 +769,30 @@ extern "C" uint32_t nz_operand_lane_symbols(uint64_t cols, int precision) {
   return best * 8;
 }
 
+extern "C" uint32_t nz_operand_lane_symbols_for(uint64_t rows, uint64_t cols, int precision) {
+  if (rows == 0) return nz_operand_lane_symbols(cols, precision);
+  if (!nz::valid_precision(precision) || cols == 0 || cols % 64 || rows % 4) return 0;
+  // The fused linear has one work item per (128-row tile, unit-long column segment) and a
+  // B200 runs one per SM at a time; an item costs its unit's blocks in decode steps plus
+  // about six steps of set-up.  Take the unit length (16 to 48 blocks: shorter units cost
+  // more than 1 % of the stored bytes, longer ones do not fit beside the operand tiles) with
+  // the fewest steps in sequence, the longer one on a tie.
+  constexpr uint64_t kSMs = 148, kSetupSteps = 6;
+  const uint64_t spr = cols / 64, tiles = (rows + nz::kTileRows - 1) / nz::kTileRows;
+  uint32_t best = 0;
+  uint64_t best_cost = 0;
+  for (uint32_t beta = 16; beta <= 48 && beta <= spr; ++beta) {
+    if (spr % beta) continue;
+    const uint64_t items = tiles * (spr / beta);
+    const uint64_t cost = ((items + kSMs - 1) / kSMs) * (beta + kSetupSteps);
+    if (!best || cost <= best_cost) {
+      best = beta;
+      best_cost = cost;
+    }
+  }
+  return best ? best * 8 : nz_operand_lane_symbols(cols, precision);
+}
+
 extern "C" uint64_t nz_linear_workspace_bytes(uint64_t rows, uint64_t cols, uint32_t lane_symbols,
                                               uint64_t m_tokens) {
   const uint32_t segs = nz::operand_segments(cols, lane_symbols);

@@ -368,6 +368,25 @@ def to_operand_order(bits: np.ndarray, rows: int, cols: int) -> np.ndarray:
         bits.reshape(rows // 4, 4, cols // 64, 64).transpose(0, 2, 1, 3)).reshape(-1)
 
 
+def operand_lane_symbols_for(rows: int, cols: int, s: int) -> int:
+    """The unit length the GPU library picks when the row count is known
+    (nz_operand_lane_symbols_for): fewest decode steps in sequence for one work item per
+    128-row tile and unit-long column segment, 148 at a time; the longer unit on a tie."""
+    if rows == 0:
+        return operand_lane_symbols(cols, s)
+    if cols <= 0 or cols % 64 or rows % 4:
+        return 0
+    spr, tiles = cols // 64, (rows + 127) // 128
+    best, best_cost = 0, 0
+    for beta in range(16, min(48, spr) + 1):
+        if spr % beta:
+            continue
+        cost = -(-(tiles * (spr // beta)) // 148) * (beta + 6)
+        if not best or cost <= best_cost:
+            best, best_cost = beta, cost
+    return best * 8 if best else operand_lane_symbols(cols, s)
+
+
 def from_operand_order(stream: np.ndarray, rows: int, cols: int) -> np.ndarray:
     assert rows % 4 == 0 and cols % 64 == 0 and stream.size == rows * cols
     return np.ascontiguousarray(

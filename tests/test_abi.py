@@ -49,6 +49,24 @@ def test_size_helpers_match_oracle(s):
     assert L.nz_container_bound(10, 12) == 0
 
 
+@pytest.mark.parametrize("s", (0, 1, 3, 7))
+def test_operand_unit_length_rule_matches_the_oracle(s):
+    """The unit length of operand-order matrices is part of the stored format's geometry: the
+    library's choice (a host function) and the oracle's restatement must agree, with and without
+    a known row count; spot values for the Llama shapes at precision 7."""
+    L = _lib.load()
+    for rows in (0, 4, 128, 2048, 4096, 5504, 8192, 11008, 28672, 32000):
+        for cols in (64, 100, 512, 1024, 2048, 4096, 5504, 6144, 8192, 11008, 14336, 28672):
+            assert L.nz_operand_lane_symbols_for(rows, cols, s) == O.operand_lane_symbols_for(rows, cols, s)
+            assert L.nz_operand_lane_symbols(cols, s) == O.operand_lane_symbols(cols, s)
+    if s == 7:
+        want = {(4096, 4096): 128, (11008, 4096): 128, (4096, 11008): 344, (8192, 8192): 256,
+                (8192, 28672): 224, (2048, 2048): 128, (2048, 5504): 344}
+        for (rows, cols), S in want.items():
+            assert L.nz_operand_lane_symbols_for(rows, cols, s) == S, (rows, cols)
+    assert L.nz_operand_lane_symbols_for(6, 4096, s) == 0          # rows not a multiple of 4
+
+
 def test_argument_validation_needs_no_gpu():
     L = _lib.load()
     assert L.nz_split_bf16(0, 16, 4, 0, 0, 0) == _lib.NZ_E_ARG

@@ -189,11 +189,11 @@ def test_manager_stores_linear_weights_in_operand_order_and_reads_them_back():
     w = weights((256, 2048), 21).cuda()
     h = m.write(w, operand=True)
     e = m._be.entry(h)
-    assert e.operand_cols == 2048 and e.lane_symbols == 256
+    assert e.operand_cols == 2048 and e.lane_symbols == O.operand_lane_symbols_for(256, 2048, 7) == 128
     assert torch.equal(m.read(h).view(torch.int16), w.view(torch.int16))
     # the stored bytes are the oracle's for the permuted tensor
     stream = O.to_operand_order(A.to_bits(w), 256, 2048)
-    c_ref, f_ref = O.compress_bf16(stream, 7, 256)
+    c_ref, f_ref = O.compress_bf16(stream, 7, e.lane_symbols)
     assert np.array_equal(e.container.cpu().numpy(), c_ref)
     assert np.array_equal(e.fractions.cpu().numpy(), f_ref)
     # a shape that cannot be in operand order falls back to stream order
@@ -258,7 +258,11 @@ def test_converted_llama_with_fused_linear_matches_dense_logits_and_tokens():
         logits = model(ids).logits                     # prefill: 16 rows per Linear
         tokens = model.generate(ids, max_new_tokens=8, do_sample=False)   # then one row at a time
     m.check()
-    assert (logits.float() - ref_logits.float()).abs().max().item() <= 1e-2
+    # every Linear rounds its fp32 sums to bf16 once, like the library GEMM, but adds the column
+    # segments in its own order: the logits may differ by a bf16 ulp or two of the largest one
+    # (2^-8 relative each), not more
+    scale = max(1.0, ref_logits.float().abs().max().item())
+    assert (logits.float() - ref_logits.float()).abs().max().item() <= 2.0 ** -6 * scale
     assert torch.equal(tokens, ref_tokens)
 
 
