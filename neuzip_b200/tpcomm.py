@@ -87,14 +87,20 @@ class PeerReducer:
         self._turn = (s + 1) % _SETS
 
     def close(self) -> None:
-        """Unmap the peers' buffers and free this rank's (all ranks, after a barrier of their
-        own: a peer must not be storing into a buffer that is freed)."""
+        """Unmap the peers' buffers and free this rank's.  Collective: every rank of the group
+        calls it.  Each rank first waits for its own stream (its last reduction has then seen
+        every peer's stores and arrivals, so nobody still writes here), unmaps what it
+        imported, and only after a barrier -- when no rank holds a mapping any more -- frees
+        what it exported."""
         if self._lib is None:
             return
+        import torch.distributed as dist
         if torch.cuda.is_available():
             torch.cuda.synchronize()
         for ptr in self._mapped:
             self._lib.nz_peer_close(ptr)
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
         for ws, arr in self._own:
             self._lib.nz_peer_free(ws)
             self._lib.nz_peer_free(arr)
