@@ -402,7 +402,7 @@ def tp_leg(n_layers=80, full_layers=80, shape="70b", batch=1, prompt_len=512, ne
     manager._be.release_scratch()
     torch.cuda.empty_cache()
     res["stored_weight_bytes_per_rank"] = manager.total_size()
-    layerwise.attach(model, manager)
+    hooks = layerwise.attach(model, manager)
     dec = Decoder(model, prompt, new_tokens)
     dec.run()
     out, t = dec.run()
@@ -411,6 +411,24 @@ def tp_leg(n_layers=80, full_layers=80, shape="70b", batch=1, prompt_len=512, ne
     res["neuzip_eager_tok_s"] = round(batch / t, 2)
     res["ratio_vs_dense_tok_s"] = round(res["neuzip_eager_tok_s"] / res["dense_eager_tok_s"], 3)
     res["tokens_identical_to_dense"] = bool(torch.equal(out, ref))       # lossy: may differ
+    if world > 1:
+        # the same with o_proj left out of the per-block decode: its row-parallel shard adds
+        # over the ranks inside the fused linear kernel (peer stores) instead of NCCL
+        for h in hooks:
+            h.remove()
+        for block in model.layers:
+            for lin in block.modules():
+                if isinstance(lin, neuzip.nn.Linear):
+                    lin._p._staged, lin._p._stage_tag = None, None
+        manager.fuse_tp_allreduce(None, max_rows=256)
+        layerwise.attach(model, manager, exclude=lambda lin: any(lin is b.o_proj for b in model.layers))
+        dec = Decoder(model, prompt, new_tokens)
+        dec.run()
+        out2, t = dec.run()
+        manager.check()
+        res["neuzip_fused_allreduce_o_proj_tok_s"] = round(batch / t, 2)
+        res["fused_allreduce_tokens_equal_fraction"] = round(float((out2 == out).float().mean().item()), 4)
+        manager.fuse_tp_allreduce(None, max_rows=0)
     res["peak_memory_bytes"] = torch.cuda.max_memory_allocated()
     return res
 

@@ -20,8 +20,9 @@ import torch
 from .nn import Linear
 
 
-def _compressed_linears(module: torch.nn.Module) -> List[Linear]:
-    return [m for m in module.modules() if isinstance(m, Linear)]
+def _compressed_linears(module: torch.nn.Module, exclude=None) -> List[Linear]:
+    return [m for m in module.modules()
+            if isinstance(m, Linear) and not (exclude is not None and exclude(m))]
 
 
 def default_block_filter(module: torch.nn.Module) -> bool:
@@ -60,8 +61,13 @@ def _single_vector(args, kwargs) -> bool:
 
 def attach(model: torch.nn.Module, manager,
            is_block: Optional[Callable[[torch.nn.Module], bool]] = None,
-           fuse_single_token: bool = False) -> List:
+           fuse_single_token: bool = False,
+           exclude: Optional[Callable[[Linear], bool]] = None) -> List:
     """Install the hooks; returns the hook handles (call .remove() on each to undo).
+
+    Linears for which ``exclude`` is true are left out of their block's batched decode and
+    keep decoding on their own - for instance row-parallel shards that add over the ranks
+    inside the fused linear kernel (``Manager.fuse_tp_allreduce``).
 
     With ``fuse_single_token`` a block that is called with a single token (the
     decode step of batch-1 generation) is not decoded ahead: its Linears multiply
@@ -80,20 +86,22 @@ def attach(model: torch.nn.Module, manager,
     # shared decode buffers: slot k is as large as the k-th Linear of the largest block
     sizes: List[int] = []
     for block in blocks:
-        for k, lin in enumerate(_compressed_linears(block)):
+        for k, lin in enumerate(_compressed_linears(block, exclude)):
             n = int(torch.Size(lin._p._shape).numel())
             if k == len(sizes):
                 sizes.append(n)
             else:
                 sizes[k] = max(sizes[k], n)
     batched = hasattr(backend, "make_batch")
-    device = next((lin._p.device for b in blocks for lin in _compressed_linears(b)), "cuda")
+    device = next((lin._p.device for b in blocks for lin in _compressed_linears(b, exclude)), "cuda")
     buffers = [torch.empty(n, dtype=torch.bfloat16, device=device) for n in sizes] if batched else []
     stage = _Stage()
     handles = []
     for number, block in enumerate(blocks):
-        params = [lin._p for lin in _compressed_linears(block)]
+        params = [lin._p for lin in _compressed_linears(block, exclude)]
         names = [p._handle for p in params]
+        if not params:
+            continue
         if batched:
             # The Linears keep their views of the shared buffers for good; a view counts
             # only while `stage.current` names its block, so staging a block is one

@@ -278,6 +278,28 @@ def test_layerwise_hooks_stage_one_block_at_a_time_on_cpu():
         assert torch.equal(model(x), ref)
 
 
+def test_layerwise_exclude_leaves_a_linear_to_decode_on_its_own():
+    """attach(exclude=...) keeps the named Linears out of the per-block decode (they are never
+    staged and decode themselves, e.g. through a fused kernel); results are unchanged."""
+    from neuzip_b200 import layerwise
+    torch.manual_seed(0)
+    model = TwoBlocks().to(torch.bfloat16)
+    m = cpu_manager()
+    m.convert(model)
+    x = torch.randn(3, 16).to(torch.bfloat16)
+    with torch.no_grad():
+        ref = model(x)
+    layerwise.attach(model, m, exclude=lambda lin: any(lin is blk.b for blk in model.blocks))
+    seen = []
+    for blk in model.blocks:
+        blk.b.register_forward_pre_hook(
+            lambda mod, args, blk=blk: seen.append((blk.a._p.staged() is not None,
+                                                     blk.b._p.staged() is not None)))
+    with torch.no_grad():
+        assert torch.equal(model(x), ref)
+    assert seen == [(True, False), (True, False)]
+
+
 def test_layerwise_hooks_follow_writes_and_loaded_state_on_cpu():
     """A handle that is written again after attach() (an optimiser step, a loaded
     checkpoint) must be decoded from its new bytes by the block's batched decode."""
