@@ -1,6 +1,6 @@
-"""Two ranks on two GPUs: the fused linear whose epilogue adds the ranks' partial outputs over
-peer memory (nz_linear_allreduce_bf16) against an fp64 product of the unsharded weight.
-Checks: both ranks obtain the same bits; the error stays within bf16 rounding of an fp32
+"""Two ranks on two GPUs (four on four, where the box has them): the fused linear whose epilogue
+adds the ranks' partial outputs over peer memory (nz_linear_allreduce_bf16) against an fp64
+product of the unsharded weight.  Checks: all ranks obtain the same bits; the error stays within bf16 rounding of an fp32
 sum; a sequence of calls on alternating buffer sets and different shapes keeps working (the
 arrival counters only grow); the bias given on rank 0 is added once; the status word stays 0.
 Host side over gloo; no library collective touches the GPUs here.  Skipped with fewer than
@@ -62,7 +62,7 @@ def _worker(rank, world, port, out_q):
             scale = want.abs().max().item()
             both = [None] * world
             dist.all_gather_object(both, got.view(torch.int16).numpy().tobytes())
-            report.append((call, m, err, scale, both[0] == both[1]))
+            report.append((call, m, err, scale, all(b == both[0] for b in both)))
     status = manager._be.status()
     dist.barrier()
     manager.fuse_tp_allreduce(None, max_rows=0)
@@ -72,13 +72,14 @@ def _worker(rank, world, port, out_q):
 
 
 @pytest.mark.timeout(600)
-def test_fused_linear_allreduce_over_peer_memory_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", (2, 4))
+def test_fused_linear_allreduce_over_peer_memory(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out_q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out_q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [out_q.get(timeout=500) for _ in procs]
